@@ -1,0 +1,98 @@
+/* C-ABI of libmpsa.so: B200 (sm_100a) kernels for the diagonal-tiled mixed-precision attention
+ * path.  Plain pointers and sizes only; every pointer is a DEVICE pointer unless stated
+ * otherwise; nothing here allocates or frees device memory; every call is asynchronous on
+ * `stream` (a cudaStream_t passed as void*).  Return value: 0 on success, negative on error
+ * (MPSA_ERR_*); the message is available from mpsa_last_error() on the calling thread.
+ *
+ * Each entry names the reference function it replaces (paths relative to the reference
+ * project root).
+ */
+#ifndef MPSA_H_
+#define MPSA_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MPSA_OK 0
+#define MPSA_ERR_BAD_ARG (-1)
+#define MPSA_ERR_UNSUPPORTED (-2)
+#define MPSA_ERR_LAUNCH (-3)
+#define MPSA_ERR_TIMEOUT (-4)
+
+/* input dtypes: 0 bf16, 1 fp16, 2 fp32.  output dtypes: 0 fp32, 1 fp16, 2 bf16, 3 fp8 e5m2 (GEMM only) */
+/* fp8 element formats of the quantizer: 1 E5M2 (the reference's), 2 E4M3 */
+/* precision-map cells: 0 skip, 1 FP8 tile, 2 FP4 tile */
+
+int mpsa_version(void);
+
+/* Copies the calling thread's last error message (NUL terminated) into buf[0..n). HOST pointer. */
+int mpsa_last_error(char* buf, unsigned long long n);
+
+/* MX block quantizer, one side (Q or K) per call.
+ * Replaces quant_mxfp4 / quant_mxfp8e5 and their Triton kernels (ours/quant_mxint8.py:276-351,
+ * :453-512 and :164-272) and the scale relayout (ours/mxfp_attn_kernel.py:56-57).
+ *   x                [B,H,L,D] logical shape, element strides xs_b/xs_h/xs_l, inner stride 1
+ *   s                fp32 scalar multiplied in before quantising (softmax scale * log2e for Q, 1 for K)
+ *   Any output pointer may be NULL (that output is not produced).
+ *   fp8_codes            one byte per element, byte strides o8_*   (reference output format)
+ *   fp4_codes_unpacked   one E2M1 code per byte, byte strides o4_* (reference output format)
+ *   fp8_scales_rm / fp4_scales_rm   E8M0 [B,H,L,D/32]              (reference output format)
+ *   fp4_codes_packed     [B,H,L,D/2], two codes per byte, low nibble first
+ *   fp8_scales_tiled / fp4_scales_tiled   [B,H,ceil(L/128),ceil(D/128),512]: 128x4 scale tiles,
+ *                        element (row r, block c) at byte (r%32)*16 + (r/32)*4 + c%4, padding = 127
+ */
+int mpsa_quant_mx(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b, long long xs_h,
+                  long long xs_l, float s, int fp8_fmt, void* fp8_codes, long long o8_b, long long o8_h,
+                  long long o8_l, void* fp4_codes_unpacked, long long o4_b, long long o4_h, long long o4_l,
+                  void* fp8_scales_rm, void* fp4_scales_rm, void* fp4_codes_packed, void* fp8_scales_tiled,
+                  void* fp4_scales_tiled, void* stream);
+
+/* Per-32 int8 quantizer, one side per call.  Replaces quant_fpxint8 (ours/quant_mxint8.py:21-114).
+ *   codes int8 with byte strides o_*; scales fp32 [B,H,L,D/32]. */
+int mpsa_quant_int8(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b, long long xs_h,
+                    long long xs_l, float s, void* codes, long long o_b, long long o_h, long long o_l,
+                    void* scales, void* stream);
+
+/* V [B,H,Skv,D] (strided) -> fp16 V^T [B,H,D,Skv_pad], keys >= Skv zero.  Replaces the host-side
+ * v.to(float16) of the wrapper (ours/mxfp_attn_kernel.py:27-31) and makes V the K-major operand of P.V. */
+int mpsa_prepare_vt(const void* v, int in_dtype, void* vt, int B, int H, int Skv, int D, int Skv_pad,
+                    long long vs_b, long long vs_h, long long vs_l, void* stream);
+
+/* Band-rule precision map uint8 [nq, nk] over tile x tile cells: FP8 iff the cell is within
+ * `band` tiles of the (end-aligned) diagonal, else FP4; causal cells entirely above the diagonal
+ * are SKIP.  The reference has no per-tile precision selection; the causal tile range follows
+ * ours/online_routing.py:68-77. */
+int mpsa_route_band(void* map, int nq, int nk, int tile, int causal, int band, int S, int Skv, void* stream);
+
+/* Fused attention forward.  Replaces block_scaled_batched_attn (ours/mxfp_attn_kernel.py:362-423)
+ * and its kernel (:103-359).
+ *   q8/q4, k8/k4   codes from mpsa_quant_mx with D padded to 128: fp8 [B,H,L,128], fp4 packed [B,H,L,64]
+ *   *_sf           tiled scales [B,H,ceil(L/128),512]
+ *   vt             from mpsa_prepare_vt
+ *   map            uint8 [.., ceil(S/128), ceil(Skv/128)] with batch / head strides map_sb / map_sh (0 = shared)
+ *   out            [B,Hq,S,D] contiguous
+ *   fp8_fmt        descriptor format of the fp8 codes: 0 E4M3, 1 E5M2
+ *   status         one int32, must be 0 on entry; a kernel whose bounded waits expire stores a
+ *                  non-zero code here (1 TMA, 2 MMA, 3 pipeline) and unwinds
+ */
+int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
+                  const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* map,
+                  long long map_sb, long long map_sh, void* out, int out_dtype, int B, int Hq, int Hkv, int S,
+                  int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int* status, void* stream);
+
+/* C[M,N] = alpha * (A . sa)(B . sb)^T.  Replaces block_scaled_matmul (ours/block_scaled_matmul.py:271-296)
+ * and its kernel (:154-267).
+ *   a [M, K/epb] and b [N, K/epb] bytes with row pitches lda_bytes / ldb_bytes (K-major)
+ *   a_scale [ceil(M/128), K/vec/4, 32,4,4], b_scale [ceil(N/128), K/vec/4, 32,4,4]
+ *   mode 0 MXFP8 (a_fmt/b_fmt: 0 E4M3, 1 E5M2; vec 32, E8M0), 1 MXFP4 (vec 32, E8M0),
+ *        2 NVFP4 (vec 16, E4M3 scales; pass the product of the two tensor scales as alpha)
+ *   c [M, ldc] of out_dtype;  status as in mpsa_attn_fwd */
+int mpsa_gemm_block_scaled(const void* a, const void* a_scale, const void* b, const void* b_scale, void* c, int M,
+                           int N, int K, long long lda_bytes, long long ldb_bytes, long long ldc, int mode,
+                           int a_fmt, int b_fmt, int out_dtype, float alpha, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MPSA_H_ */

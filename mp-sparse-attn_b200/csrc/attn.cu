@@ -1,0 +1,500 @@
+// Fused diagonal-tiled mixed-precision attention forward for sm_100a.
+//
+// Counterpart of block_scaled_batched_attn_kernel (ours/mxfp_attn_kernel.py:103-359) with the parts
+// the reference leaves out: causal masking and GQA (taken from its INT8 sibling,
+// ours/online_routing.py:68-77, :113-118, :160) and a per-tile precision map.
+//
+// One CTA owns one 128-row query tile of one (batch, q-head) and walks the 128-key tiles the
+// precision map enables for it:
+//   S = Q.K^T   tcgen05.mma block-scaled: kind::mxf8f6f4 (MXFP8 x MXFP8, 4 x K=32) on FP8 tiles,
+//               kind::mxf4 (MXFP4 x MXFP4, 2 x K=64) on FP4 tiles; Q is resident in shared memory
+//               in both formats, K tiles arrive by TMA in the format the map asks for; E8M0 scale
+//               tiles go to TMEM with tcgen05.cp.  The softmax scale * log2(e) is already folded
+//               into Q by the quantizer (ours/quant_mxint8.py:494), so S is in the log2 domain.
+//   softmax     one thread per query row reads its S row from TMEM (tcgen05.ld), keeps running
+//               max / sum (ours/mxfp_attn_kernel.py:320-328), writes P as fp16 back into TMEM over S
+//               (:339).  The accumulator is rescaled only when the running max grows by more than
+//               2^8, which leaves the result O = sum(P.V) / sum(P) unchanged.
+//   O += P.V    tcgen05.mma kind::f16 with P read from TMEM and V^T (fp16, [D, keys]) from shared
+//               memory, fp32 accumulation in TMEM (:340 accumulates each tile in fp16 first).
+// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 4-7 softmax/correction/epilogue.  S is
+// double-buffered in TMEM so that Q.K^T of tile t+1 overlaps the softmax of tile t.
+// TMEM columns: S0/P0 [0,128) S1/P1 [128,256) O [256,384) Q scales [384,392) K scales [392,400).
+#include "api_internal.h"
+#include "common.cuh"
+#include "tma_host.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace mpsa {
+
+constexpr int ATT_BM = 128, ATT_BN = 128, ATT_DQK = 128;
+constexpr int ATT_KSTAGES = 3, ATT_VSTAGES = 2;
+constexpr int ATT_Q8_BYTES = ATT_BM * 128, ATT_Q4_BYTES = ATT_BM * 64;
+constexpr int ATT_K_BYTES = ATT_BN * 128;             // slot sized for the FP8 tile; FP4 uses half
+constexpr int ATT_V_BYTES = 128 * ATT_BN * 2;         // V^T tile, up to D=128 rows of 128 fp16
+constexpr int ATT_OFF_Q8 = 0;
+constexpr int ATT_OFF_Q4 = ATT_OFF_Q8 + ATT_Q8_BYTES;
+constexpr int ATT_OFF_K = ATT_OFF_Q4 + ATT_Q4_BYTES;
+constexpr int ATT_OFF_V = ATT_OFF_K + ATT_KSTAGES * ATT_K_BYTES;
+constexpr int ATT_OFF_SF = ATT_OFF_V + ATT_VSTAGES * ATT_V_BYTES;   // Q8, Q4, K[stages] scale tiles
+constexpr int ATT_OFF_BAR = ATT_OFF_SF + (2 + ATT_KSTAGES) * 512;
+constexpr int ATT_SMEM = ATT_OFF_BAR + 256 + 1024;
+constexpr int ATT_THREADS = 256;
+constexpr uint32_t ATT_TMEM_COLS = 512;
+constexpr uint32_t ATT_COL_S = 0, ATT_COL_O = 256, ATT_COL_SFQ8 = 384, ATT_COL_SFQ4 = 388, ATT_COL_SFK = 392;
+constexpr float ATT_RESCALE_LOG2 = 8.0f;
+
+constexpr int TILE_SKIP = 0, TILE_FP8 = 1, TILE_FP4 = 2;
+
+struct AttnParams {
+  int B, Hq, Hkv, S, Skv, D;        // D = value head dim (64 or 128); Q/K depth is padded to 128
+  int causal;
+  int fp8_fmt;                       // descriptor format field: 0 E4M3, 1 E5M2
+  const uint8_t* q8_sf; const uint8_t* q4_sf;   // [B,Hq,nq,512]
+  const uint8_t* k8_sf; const uint8_t* k4_sf;   // [B,Hkv,nk,512]
+  const uint8_t* map; long long map_sb, map_sh; // [.., nq, nk], strides may be 0 (broadcast)
+  void* out; int out_dtype;          // [B,Hq,S,D] contiguous; 0 f32, 1 f16, 2 bf16
+  int* status;
+};
+
+__device__ __forceinline__ void tmem_ld32p(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32p(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant__ CUtensorMap tm_q4,
+                const __grid_constant__ CUtensorMap tm_k8, const __grid_constant__ CUtensorMap tm_k4,
+                const __grid_constant__ CUtensorMap tm_vt, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024 - (raw & 1023)) & 1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_OFF_BAR);
+  uint64_t* q_full = bars;                         // 1
+  uint64_t* k_full = bars + 1;                     // KSTAGES
+  uint64_t* k_empty = k_full + ATT_KSTAGES;        // KSTAGES
+  uint64_t* v_full = k_empty + ATT_KSTAGES;        // VSTAGES
+  uint64_t* v_empty = v_full + ATT_VSTAGES;        // VSTAGES
+  uint64_t* s_full = v_empty + ATT_VSTAGES;        // 2
+  uint64_t* p_ready = s_full + 2;                  // 2
+  uint64_t* pv_done = p_ready + 2;                 // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (p.S + ATT_BM - 1) / ATT_BM, nk = (p.Skv + ATT_BN - 1) / ATT_BN;
+  const int qi = nq - 1 - (int)blockIdx.x;          // heavy (late) causal rows first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const uint8_t* map_row = p.map + (long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk;
+  const int off = p.Skv - p.S;                      // queries are aligned to the end of the keys
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < ATT_KSTAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < ATT_VSTAGES; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 128); mbar_init(&pv_done[s], 1); }
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, ATT_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  uint8_t* sQ8 = smem + ATT_OFF_Q8;
+  uint8_t* sQ4 = smem + ATT_OFF_Q4;
+  uint8_t* sK = smem + ATT_OFF_K;
+  uint8_t* sV = smem + ATT_OFF_V;
+  uint8_t* sSF = smem + ATT_OFF_SF;                 // [0] Q8, [1] Q4, [2+s] K stage s
+  const int v_half_bytes = p.D * 128;               // one 64-key half of a V^T tile
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_q4); tma_prefetch_desc(&tm_k8);
+      tma_prefetch_desc(&tm_k4); tma_prefetch_desc(&tm_vt);
+      const int q_row = (b * p.Hq + h) * p.S + qi * ATT_BM;
+      const long long qsf = ((long long)(b * p.Hq + h) * nq + qi) * 512;
+      mbar_arrive_expect_tx(q_full, ATT_Q8_BYTES + ATT_Q4_BYTES + 1024);
+      tma_load_2d(sQ8, &tm_q8, q_full, 0, q_row);
+      tma_load_2d(sQ4, &tm_q4, q_full, 0, q_row);
+      bulk_load(sSF, p.q8_sf + qsf, 512, q_full);
+      bulk_load(sSF + 512, p.q4_sf + qsf, 512, q_full);
+
+      const int k_row0 = (b * p.Hkv + hk) * p.Skv;
+      const long long ksf0 = (long long)(b * p.Hkv + hk) * nk * 512;
+      const int v_row = (b * p.Hkv + hk) * p.D;
+      bool ok = true;
+      int tk = 0, tv = 0;                          // tiles issued on the K and V rings
+      int jk = 0, jv = 0;                          // next key-tile index to examine for each ring
+      auto issue_k = [&]() {                       // returns false when no tile is left
+        while (jk < nk && map_row[jk] == TILE_SKIP) ++jk;
+        if (jk >= nk) return false;
+        const int s = tk % ATT_KSTAGES;
+        if (tk >= ATT_KSTAGES) ok = mbar_wait(&k_empty[s], ((tk / ATT_KSTAGES) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
+        if (!ok) return false;
+        const bool f8 = map_row[jk] == TILE_FP8;
+        mbar_arrive_expect_tx(&k_full[s], (f8 ? ATT_K_BYTES : ATT_K_BYTES / 2) + 512);
+        tma_load_2d(sK + s * ATT_K_BYTES, f8 ? &tm_k8 : &tm_k4, &k_full[s], 0, k_row0 + jk * ATT_BN);
+        bulk_load(sSF + (2 + s) * 512, (f8 ? p.k8_sf : p.k4_sf) + ksf0 + (long long)jk * 512, 512, &k_full[s]);
+        ++tk; ++jk;
+        return true;
+      };
+      auto issue_v = [&]() {
+        while (jv < nk && map_row[jv] == TILE_SKIP) ++jv;
+        if (jv >= nk) return false;
+        const int s = tv % ATT_VSTAGES;
+        if (tv >= ATT_VSTAGES) ok = mbar_wait(&v_empty[s], ((tv / ATT_VSTAGES) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
+        if (!ok) return false;
+        mbar_arrive_expect_tx(&v_full[s], 2 * v_half_bytes);
+        tma_load_2d(sV + s * ATT_V_BYTES, &tm_vt, &v_full[s], jv * ATT_BN, v_row);
+        tma_load_2d(sV + s * ATT_V_BYTES + v_half_bytes, &tm_vt, &v_full[s], jv * ATT_BN + 64, v_row);
+        ++tv; ++jv;
+        return true;
+      };
+      // consumption order of the MMA warp: K0, K1, V0, K2, V1, ...
+      bool more_k = issue_k();
+      while (ok && more_k) {
+        more_k = issue_k();
+        if (!ok) break;
+        issue_v();
+      }
+      while (ok && issue_v()) {}
+      if (!ok) {
+        // unwind: give copies in flight a chance to land before shared memory is released
+        mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
+        for (int t = max(0, tk - ATT_KSTAGES); t < tk; ++t)
+          mbar_wait(&k_full[t % ATT_KSTAGES], (t / ATT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
+        for (int t = max(0, tv - ATT_VSTAGES); t < tv; ++t)
+          mbar_wait(&v_full[t % ATT_VSTAGES], (t / ATT_VSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc8 = idesc_block_scaled(p.fp8_fmt, p.fp8_fmt, ATT_BM, ATT_BN, 1);
+      const uint32_t idesc4 = idesc_block_scaled(1, 1, ATT_BM, ATT_BN, 1);
+      const uint32_t idesc_pv = idesc_f16(0, 0, ATT_BM, p.D);
+      const uint64_t q8d = sdesc_kmajor_sw128(smem_u32(sQ8));
+      const uint64_t q4d = sdesc_kmajor_sw64(smem_u32(sQ4));
+      bool ok = mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
+      if (ok) {
+        tc_fence_after();
+        tc_cp_32x128b_warpx4(tmem + ATT_COL_SFQ8, sdesc_sf_tile(smem_u32(sSF)));
+        tc_cp_32x128b_warpx4(tmem + ATT_COL_SFQ4, sdesc_sf_tile(smem_u32(sSF + 512)));
+      }
+      int jq = 0;                                  // next key tile for Q.K^T
+      int tq = 0, tp = 0;                          // tiles issued: Q.K^T and P.V
+      auto issue_qk = [&]() {
+        while (jq < nk && map_row[jq] == TILE_SKIP) ++jq;
+        if (jq >= nk) return false;
+        const int s = tq % ATT_KSTAGES;
+        ok = mbar_wait(&k_full[s], (tq / ATT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
+        if (!ok) return false;
+        tc_fence_after();
+        const bool f8 = map_row[jq] == TILE_FP8;
+        const uint32_t sfk = tmem + ATT_COL_SFK + (tq & 1) * 4;
+        tc_cp_32x128b_warpx4(sfk, sdesc_sf_tile(smem_u32(sSF + (2 + s) * 512)));
+        const uint32_t d = tmem + ATT_COL_S + (tq & 1) * 128;
+        const uint32_t kaddr = smem_u32(sK + s * ATT_K_BYTES);
+        if (f8) {
+          const uint64_t kd = sdesc_kmajor_sw128(kaddr);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            mma_mxf8f6f4(d, q8d + 2 * j, kd + 2 * j, idesc_with_sf_id(idesc8, j, j), tmem + ATT_COL_SFQ8, sfk, j > 0);
+        } else {
+          const uint64_t kd = sdesc_kmajor_sw64(kaddr);
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            mma_mxf4(d, q4d + 2 * j, kd + 2 * j, idesc_with_sf_id(idesc4, 2 * j, 2 * j), tmem + ATT_COL_SFQ4, sfk, j > 0);
+        }
+        tc_commit(&k_empty[s]);
+        tc_commit(&s_full[tq & 1]);
+        ++tq; ++jq;
+        return true;
+      };
+      bool more = ok && issue_qk();
+      while (ok && tp < tq) {
+        if (more) more = issue_qk();
+        if (!ok) break;
+        // P.V of tile tp
+        const int bsel = tp & 1, s = tp % ATT_VSTAGES;
+        ok = mbar_wait(&p_ready[bsel], (tp >> 1) & 1, p.status, KS_TIMEOUT_PIPE);
+        if (!ok) break;
+        ok = mbar_wait(&v_full[s], (tp / ATT_VSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t ptm = tmem + ATT_COL_S + bsel * 128;     // P: 64 columns of packed fp16
+        const uint32_t vaddr = smem_u32(sV + s * ATT_V_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t vd = sdesc_kmajor_sw128(vaddr + (ks >> 2) * v_half_bytes) + 2 * (ks & 3);
+          mma_f16_ts(tmem + ATT_COL_O, ptm + ks * 8, vd, idesc_pv, (tp > 0 || ks > 0) ? 1u : 0u);
+        }
+        tc_commit(&v_empty[s]);
+        tc_commit(&pv_done[bsel]);
+        ++tp;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ softmax / correction / epilogue -----------
+    const int q = warp & 3;
+    const int r_in = q * 32 + lane;                 // row inside the tile == TMEM lane
+    const int m_glob = qi * ATT_BM + r_in;
+    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    float m_used = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+    int t = 0;
+    for (int j = 0; j < nk && ok; ++j) {
+      if (map_row[j] == TILE_SKIP) continue;
+      const int bsel = t & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[bsel], (t >> 1) & 1, p.status, KS_TIMEOUT_MMA));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t s_addr = tmem + lane_base + ATT_COL_S + bsel * 128;
+      uint32_t sr[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32p(s_addr + c * 32, sr + c * 32);
+      tmem_ld_wait();
+      const int n0 = j * ATT_BN;
+      const bool need_mask = (p.causal && (n0 + ATT_BN - 1 > qi * ATT_BM + off)) || (n0 + ATT_BN > p.Skv);
+      float mx = -INFINITY;
+      if (need_mask) {
+        const int lim = p.causal ? min(p.Skv - 1, m_glob + off) : (p.Skv - 1);   // last visible key
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          float v = (n0 + c <= lim) ? __uint_as_float(sr[c]) : -INFINITY;
+          sr[c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+      }
+      // running max with deferred rescale of the accumulator
+      const float m_new = fmaxf(m_used, mx);
+      const bool grow = (t > 0) && (m_new > m_used + ATT_RESCALE_LOG2);
+      if (t == 0) {
+        m_used = m_new;
+      } else if (__any_sync(0xffffffffu, grow)) {
+        // the accumulator must be quiescent: P.V of the previous tile finished
+        ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1, p.status, KS_TIMEOUT_MMA));
+        if (!ok) break;
+        tc_fence_after();
+        const float alpha = grow ? ex2(m_used - m_new) : 1.0f;
+        if (grow) { m_used = m_new; l_run *= alpha; }
+        for (int c = 0; c < p.D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32p(tmem + lane_base + ATT_COL_O + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32p(tmem + lane_base + ATT_COL_O + c * 32, o);
+        }
+        tmem_st_wait();
+      }
+      const float mref = (m_used == -INFINITY) ? 0.0f : m_used;   // row with no visible key so far
+      float lsum = 0.0f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float p0 = ex2(__uint_as_float(sr[2 * c]) - mref);
+        const float p1 = ex2(__uint_as_float(sr[2 * c + 1]) - mref);
+        lsum += p0 + p1;
+        pk[c] = pack_f16x2(p0, p1);
+      }
+      l_run += lsum;
+      tmem_st32p(s_addr, pk);
+      tmem_st32p(s_addr + 32, pk + 32);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&p_ready[bsel]);
+      ++t;
+    }
+    // epilogue: O / l
+    if (ok && t > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1, p.status, KS_TIMEOUT_MMA));
+      tc_fence_after();
+    }
+    if (ok) {
+      const float inv_l = (t > 0 && l_run > 0.0f) ? 1.0f / l_run : 0.0f;
+      const long long o_off = ((long long)(b * p.Hq + h) * p.S + m_glob) * p.D;
+      for (int c = 0; c < p.D / 32; ++c) {
+        uint32_t o[32];
+        if (t > 0) {
+          tmem_ld32p(tmem + lane_base + ATT_COL_O + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0;
+        }
+        if (m_glob < p.S) {
+          if (p.out_dtype == 0) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o_off + c * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(o[4 * i]) * inv_l, __uint_as_float(o[4 * i + 1]) * inv_l,
+                                   __uint_as_float(o[4 * i + 2]) * inv_l, __uint_as_float(o[4 * i + 3]) * inv_l);
+          } else {
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float a = __uint_as_float(o[2 * i]) * inv_l, c2 = __uint_as_float(o[2 * i + 1]) * inv_l;
+              if (p.out_dtype == 1) {
+                w[i] = pack_f16x2(a, c2);
+              } else {
+                __nv_bfloat162 hb = __floats2bfloat162_rn(a, c2);
+                w[i] = *reinterpret_cast<uint32_t*>(&hb);
+              }
+            }
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + o_off + c * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, ATT_TMEM_COLS);
+}
+
+// ---- V^T preparation: V [B,Hkv,Skv,D] (any 16-bit/32-bit float, strided) -> fp16 [B,Hkv,D,Skv_pad],
+// keys beyond Skv zero-filled.  The reference casts V to fp16 on the host (ours/mxfp_attn_kernel.py:29-31);
+// the transpose makes V the K-major B operand of P.V.
+template <typename T>
+__global__ void __launch_bounds__(256) prepare_vt_kernel(const T* v, __half* vt, int H, int Skv, int D, int Skv_pad,
+                                                         long long vs_b, long long vs_h, long long vs_l) {
+  __shared__ float tile[64][65];
+  const int bh = blockIdx.z, b = bh / H, h = bh % H;
+  const int s0 = blockIdx.x * 64, d0 = blockIdx.y * 64;
+  const T* src = v + (long long)b * vs_b + (long long)h * vs_h;
+  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+    const int sl = i >> 6, dl = i & 63;
+    const int s = s0 + sl, d = d0 + dl;
+    tile[sl][dl] = (s < Skv && d < D) ? (float)src[(long long)s * vs_l + d] : 0.0f;
+  }
+  __syncthreads();
+  __half* dst = vt + (long long)bh * D * Skv_pad;
+  for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+    const int dl = i >> 6, sl = i & 63;
+    const int s = s0 + sl, d = d0 + dl;
+    if (d < D && s < Skv_pad) dst[(long long)d * Skv_pad + s] = __float2half_rn(tile[sl][dl]);
+  }
+}
+
+// ---- band-rule precision map: FP8 iff |i + off/T - j| < band, else FP4; causal => tiles entirely above
+// the diagonal are SKIP.  Tiles are T x T; `off` = Skv - S aligns queries to the end of the keys.
+__global__ void route_band_kernel(uint8_t* map, int nq, int nk, int T, int causal, int band, int off, int S) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x, i = blockIdx.y;
+  if (j >= nk) return;
+  uint8_t v = (abs(i + off / T - j) < band) ? TILE_FP8 : TILE_FP4;
+  if (causal) {
+    const int last_q = min(S - 1, i * T + T - 1);       // last query row of the tile
+    if (j * T > last_q + off) v = TILE_SKIP;
+  }
+  map[(long long)i * nk + j] = v;
+}
+
+}  // namespace mpsa
+
+using namespace mpsa;
+
+extern "C" int mpsa_route_band(void* map, int nq, int nk, int tile, int causal, int band, int S, int Skv, void* stream) {
+  if (!map || nq <= 0 || nk <= 0 || tile <= 0 || band < 0) return set_error(MPSA_ERR_BAD_ARG, "route_band: bad argument");
+  if (nq > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "route_band: more than 65535 query tiles");
+  dim3 grid((nk + 127) / 128, nq);
+  route_band_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((uint8_t*)map, nq, nk, tile, causal, band, Skv - S, S);
+  return check_launch("route_band");
+}
+
+extern "C" int mpsa_prepare_vt(const void* v, int in_dtype, void* vt, int B, int H, int Skv, int D, int Skv_pad,
+                               long long vs_b, long long vs_h, long long vs_l, void* stream) {
+  if (!v || !vt || B <= 0 || H <= 0 || Skv <= 0 || D <= 0) return set_error(MPSA_ERR_BAD_ARG, "prepare_vt: bad argument");
+  if (Skv_pad < Skv || Skv_pad % 8) return set_error(MPSA_ERR_BAD_ARG, "prepare_vt: Skv_pad must be >= Skv and a multiple of 8");
+  if (B * H > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "prepare_vt: B*H must be below 65536");
+  dim3 grid((Skv_pad + 63) / 64, (D + 63) / 64, B * H);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (in_dtype == 0) prepare_vt_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)v, (__half*)vt, H, Skv, D, Skv_pad, vs_b, vs_h, vs_l);
+  else if (in_dtype == 1) prepare_vt_kernel<__half><<<grid, 256, 0, st>>>((const __half*)v, (__half*)vt, H, Skv, D, Skv_pad, vs_b, vs_h, vs_l);
+  else if (in_dtype == 2) prepare_vt_kernel<float><<<grid, 256, 0, st>>>((const float*)v, (__half*)vt, H, Skv, D, Skv_pad, vs_b, vs_h, vs_l);
+  else return set_error(MPSA_ERR_BAD_ARG, "prepare_vt: in_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
+  return check_launch("prepare_vt");
+}
+
+extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
+                             const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* map,
+                             long long map_sb, long long map_sh, void* out, int out_dtype, int B, int Hq, int Hkv,
+                             int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int* status, void* stream) {
+  if (!q8 || !q8_sf || !q4 || !q4_sf || !k8 || !k8_sf || !k4 || !k4_sf || !vt || !map || !out || !status)
+    return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: null pointer");
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || Skv <= 0) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: non-positive shape");
+  if (Hq % Hkv) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: Hq must be a multiple of Hkv");
+  if (D != 64 && D != 128) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: head_dim must be 64 or 128");
+  if (out_dtype < 0 || out_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: out_dtype must be 0 (f32), 1 (f16) or 2 (bf16)");
+  if (fp8_fmt != 0 && fp8_fmt != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: fp8_fmt must be 0 (E4M3) or 1 (E5M2)");
+  if (causal && Skv < S) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: causal needs Skv >= S");
+  if (Skv_pad < Skv || Skv_pad % 8) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: Skv_pad must be >= Skv and a multiple of 8");
+  const void* ptrs[] = {q8, q8_sf, q4, q4_sf, k8, k8_sf, k4, k4_sf, vt, out};
+  for (const void* ptr : ptrs)
+    if ((uintptr_t)ptr % 16) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: every tensor base must be 16-byte aligned");
+  if ((long long)B * Hq * S >= (1ll << 31) || (long long)B * Hkv * Skv >= (1ll << 31))
+    return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: B*H*S must fit in 31 bits");
+  CUtensorMap tq8, tq4, tk8, tk4, tvt;
+  const uint64_t qrows = (uint64_t)B * Hq * S, krows = (uint64_t)B * Hkv * Skv;
+  if (make_tmap_2d_bytes(&tq8, q8, ATT_DQK, qrows, ATT_DQK, 128, ATT_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      make_tmap_2d_bytes(&tq4, q4, ATT_DQK / 2, qrows, ATT_DQK / 2, 64, ATT_BM, CU_TENSOR_MAP_SWIZZLE_64B) ||
+      make_tmap_2d_bytes(&tk8, k8, ATT_DQK, krows, ATT_DQK, 128, ATT_BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      make_tmap_2d_bytes(&tk4, k4, ATT_DQK / 2, krows, ATT_DQK / 2, 64, ATT_BN, CU_TENSOR_MAP_SWIZZLE_64B) ||
+      make_tmap_2d_b16(&tvt, vt, Skv_pad, (uint64_t)B * Hkv * D, (uint64_t)Skv_pad * 2, 64, D, CU_TENSOR_MAP_SWIZZLE_128B))
+    return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled failed");
+  AttnParams p;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S = S; p.Skv = Skv; p.D = D; p.causal = causal; p.fp8_fmt = fp8_fmt;
+  p.q8_sf = (const uint8_t*)q8_sf; p.q4_sf = (const uint8_t*)q4_sf;
+  p.k8_sf = (const uint8_t*)k8_sf; p.k4_sf = (const uint8_t*)k4_sf;
+  p.map = (const uint8_t*)map; p.map_sb = map_sb; p.map_sh = map_sh;
+  p.out = out; p.out_dtype = out_dtype; p.status = status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess)
+      return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
+    attr_set = true;
+  }
+  const int nq = (S + ATT_BM - 1) / ATT_BM;
+  if (Hq > 65535 || B > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: Hq and B must be below 65536");
+  dim3 grid(nq, Hq, B);
+  attn_fwd_kernel<<<grid, ATT_THREADS, ATT_SMEM, (cudaStream_t)stream>>>(tq8, tq4, tk8, tk4, tvt, p);
+  return check_launch("attn_fwd");
+}

@@ -1,0 +1,265 @@
+// Standalone block-scaled GEMM  C[M,N] = alpha * (A . sa) (B . sb)^T  for sm_100a.
+//
+// Counterpart of block_scaled_matmul_kernel (ours/block_scaled_matmul.py:154-267): A is [M, K] and
+// B is [N, K], both K-major, quantised along K; the scales arrive as 512-byte 128x4 tiles
+// [rows/128, K/vec/4, 32, 4, 4] (:45-66, :382-384).
+//
+// Design: one CTA per 128x256 output tile.  A TMA producer warp streams 128-byte-wide K slabs of
+// A and B into a 4-stage shared-memory ring (128-byte swizzle) together with the scale tiles
+// (untiled bulk copies); one thread of the MMA warp moves each scale tile into TMEM with
+// tcgen05.cp and issues tcgen05.mma block-scaled instructions that accumulate 128x256 fp32 in
+// TMEM; four epilogue warps read the accumulator back with tcgen05.ld, apply alpha, convert and
+// store.  All hand-offs go through mbarriers with bounded waits.
+//
+//   mode 0  MXFP8  kind::mxf8f6f4  K=32 per instruction, one E8M0 scale per 32 elements
+//   mode 1  MXFP4  kind::mxf4      K=64 per instruction, two E8M0 scales
+//   mode 2  NVFP4  kind::mxf4nvf4  K=64 per instruction, four E4M3 scales (16-element blocks)
+#include "api_internal.h"
+#include "common.cuh"
+#include "tma_host.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+namespace mpsa {
+
+constexpr int GEMM_BM = 128, GEMM_BN = 256, GEMM_STAGES = 4;
+constexpr int GEMM_SLAB = 128;                       // bytes of K per stage and row
+constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_SLAB;    // 16 KB
+constexpr int GEMM_B_BYTES = GEMM_BN * GEMM_SLAB;    // 32 KB
+constexpr int GEMM_SFA_BYTES = 4 * 512;              // up to 4 scale tiles per stage
+constexpr int GEMM_SFB_BYTES = 2 * 4 * 512;
+constexpr int GEMM_STAGE_BYTES = GEMM_A_BYTES + GEMM_B_BYTES + GEMM_SFA_BYTES + GEMM_SFB_BYTES;
+constexpr int GEMM_SMEM = GEMM_STAGES * GEMM_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t GEMM_TMEM_COLS = 512;
+constexpr uint32_t GEMM_SF_COL0 = 256;               // scale sets live behind the accumulator
+constexpr uint32_t GEMM_SF_SET_STRIDE = 64;
+
+struct GemmParams {
+  int M, N, K;            // elements
+  int mode;               // 0 mxfp8, 1 mxfp4, 2 nvfp4
+  int a_fmt, b_fmt;       // element format field of the instruction descriptor
+  const uint8_t* sfa;     // [ceil(M/128), nchunks, 512]
+  const uint8_t* sfb;     // [ceil(N/128), nchunks, 512]
+  int nchunks;            // scale tiles along K
+  void* c; long long ldc; int out_dtype;   // 0 f32, 1 f16, 2 bf16, 3 fp8 e5m2
+  float alpha;
+  int* status;
+};
+
+__device__ __forceinline__ void store_row32(void* c, long long off, int out_dtype, const float (&v)[32], int nvalid) {
+  if (out_dtype == 0) {
+    float* o = reinterpret_cast<float*>(c) + off;
+    if (nvalid == 32 && ((uintptr_t)o % 16 == 0)) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) reinterpret_cast<float4*>(o)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+      for (int i = 0; i < nvalid; ++i) o[i] = v[i];
+    }
+  } else if (out_dtype == 1 || out_dtype == 2) {
+    uint16_t* o = reinterpret_cast<uint16_t*>(c) + off;
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (out_dtype == 1) {
+        __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    if (nvalid == 32 && ((uintptr_t)o % 16 == 0)) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) reinterpret_cast<uint4*>(o)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+    } else {
+      for (int i = 0; i < nvalid; ++i) o[i] = (uint16_t)(w[i >> 1] >> ((i & 1) * 16));
+    }
+  } else {
+    uint8_t* o = reinterpret_cast<uint8_t*>(c) + off;
+    for (int i = 0; i < nvalid; ++i) o[i] = (uint8_t)__nv_cvt_float_to_fp8(v[i], __NV_SATFINITE, __NV_E5M2);
+  }
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024 - (raw & 1023)) & 1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GEMM_STAGES * GEMM_STAGE_BYTES);
+  uint64_t* full = bars;                       // [STAGES]
+  uint64_t* empty = bars + GEMM_STAGES;        // [STAGES]
+  uint64_t* accum_full = bars + 2 * GEMM_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * GEMM_STAGES + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * GEMM_BM, n0 = blockIdx.y * GEMM_BN;
+  // per-mode geometry
+  const int epb = p.mode == 0 ? 1 : 2;                   // elements per byte
+  const int k_stage = GEMM_SLAB * epb;                   // elements of K per stage
+  const int k_mma = p.mode == 0 ? 32 : 64;               // elements of K per instruction
+  const int chunk_elems = p.mode == 2 ? 64 : 128;        // K elements covered by one scale tile
+  const int nc_stage = k_stage / chunk_elems;            // scale tiles per stage and row tile
+  const int KT = (p.K + k_stage - 1) / k_stage;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(accum_full, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, GEMM_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      const int mt = blockIdx.x, nt0 = blockIdx.y * 2;
+      const int n_row_tiles = (p.N + 127) / 128;
+      int issued = 0;
+      bool ok = true;
+      for (int kt = 0; kt < KT && ok; ++kt) {
+        const int s = kt % GEMM_STAGES;
+        if (kt >= GEMM_STAGES) ok = mbar_wait(&empty[s], ((kt / GEMM_STAGES) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
+        if (!ok) break;
+        uint8_t* st = smem + s * GEMM_STAGE_BYTES;
+        const int c0 = kt * nc_stage;
+        const int ncv = min(nc_stage, p.nchunks - c0);          // valid scale tiles in this stage
+        const int nbt = min(2, n_row_tiles - nt0);              // valid B row tiles
+        const uint32_t bytes = GEMM_A_BYTES + GEMM_B_BYTES + (uint32_t)ncv * 512u * (1 + nbt);
+        mbar_arrive_expect_tx(&full[s], bytes);
+        tma_load_2d(st, &tmap_a, &full[s], kt * GEMM_SLAB, m0);
+        tma_load_2d(st + GEMM_A_BYTES, &tmap_b, &full[s], kt * GEMM_SLAB, n0);
+        bulk_load(st + GEMM_A_BYTES + GEMM_B_BYTES, p.sfa + ((long long)mt * p.nchunks + c0) * 512, ncv * 512, &full[s]);
+        for (int t = 0; t < nbt; ++t)
+          bulk_load(st + GEMM_A_BYTES + GEMM_B_BYTES + GEMM_SFA_BYTES + t * nc_stage * 512,
+                    p.sfb + ((long long)(nt0 + t) * p.nchunks + c0) * 512, ncv * 512, &full[s]);
+        issued = kt + 1;
+      }
+      if (!ok) {
+        // unwind: let the copies already in flight land before the CTA's shared memory goes away
+        for (int kt = max(0, issued - GEMM_STAGES); kt < issued; ++kt)
+          mbar_wait(&full[kt % GEMM_STAGES], (kt / GEMM_STAGES) & 1, p.status, KS_TIMEOUT_TMA);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      uint32_t idesc;
+      if (p.mode == 0) idesc = idesc_block_scaled(p.a_fmt, p.b_fmt, GEMM_BM, GEMM_BN, 1);
+      else if (p.mode == 1) idesc = idesc_block_scaled(1, 1, GEMM_BM, GEMM_BN, 1);
+      else idesc = idesc_block_scaled(1, 1, GEMM_BM, GEMM_BN, 0);
+      bool ok = true;
+      for (int kt = 0; kt < KT && ok; ++kt) {
+        const int s = kt % GEMM_STAGES;
+        ok = mbar_wait(&full[s], (kt / GEMM_STAGES) & 1, p.status, KS_TIMEOUT_TMA);
+        if (!ok) break;
+        tc_fence_after();
+        uint8_t* st = smem + s * GEMM_STAGE_BYTES;
+        const uint32_t a_addr = smem_u32(st), b_addr = smem_u32(st + GEMM_A_BYTES);
+        const uint32_t sfa_s = smem_u32(st + GEMM_A_BYTES + GEMM_B_BYTES);
+        const uint32_t sfb_s = sfa_s + GEMM_SFA_BYTES;
+        const uint32_t sf_set = tmem + GEMM_SF_COL0 + (kt & 1) * GEMM_SF_SET_STRIDE;
+        const uint32_t sfa_t = sf_set, sfb_t = sf_set + 16;
+        const int c0 = kt * nc_stage;
+        const int ncv = min(nc_stage, p.nchunks - c0);
+        for (int c = 0; c < ncv; ++c) {
+          tc_cp_32x128b_warpx4(sfa_t + 4 * c, sdesc_sf_tile(sfa_s + c * 512));
+          tc_cp_32x128b_warpx4(sfb_t + 8 * c, sdesc_sf_tile(sfb_s + c * 512));
+          tc_cp_32x128b_warpx4(sfb_t + 8 * c + 4, sdesc_sf_tile(sfb_s + (nc_stage + c) * 512));
+        }
+        const int k_left = p.K - kt * k_stage;
+        const int nmma = min(k_stage, k_left + k_mma - 1) / k_mma;   // instructions with any valid K
+        const uint64_t adesc = sdesc_kmajor_sw128(a_addr), bdesc = sdesc_kmajor_sw128(b_addr);
+        for (int j = 0; j < nmma; ++j) {
+          const uint64_t ad = adesc + (uint64_t)(j * 2);   // +32 bytes of K per instruction (>>4)
+          const uint64_t bd = bdesc + (uint64_t)(j * 2);
+          const uint32_t acc = (kt > 0 || j > 0) ? 1u : 0u;
+          if (p.mode == 0) {
+            mma_mxf8f6f4(tmem, ad, bd, idesc_with_sf_id(idesc, j, j), sfa_t, sfb_t, acc);
+          } else if (p.mode == 1) {
+            const int c = j >> 1, id = (j & 1) * 2;
+            mma_mxf4(tmem, ad, bd, idesc_with_sf_id(idesc, id, id), sfa_t + 4 * c, sfb_t + 8 * c, acc);
+          } else {
+            mma_nvf4(tmem, ad, bd, idesc, sfa_t + 4 * j, sfb_t + 8 * j, acc);
+          }
+        }
+        tc_commit(&empty[s]);
+      }
+      if (ok) tc_commit(accum_full);
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;                       // TMEM lane quarter this warp may touch
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(accum_full, 0, p.status, KS_TIMEOUT_MMA));
+    tc_fence_after();
+    if (ok) {
+      const int row = m0 + q * 32 + lane;
+      for (int ch = 0; ch < GEMM_BN / 32; ++ch) {
+        uint32_t r[32];
+        tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + ch * 32, r);
+        tmem_ld_wait();
+        const int col = n0 + ch * 32;
+        if (row < p.M && col < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          store_row32(p.c, (long long)row * p.ldc + col, p.out_dtype, v, min(32, p.N - col));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, GEMM_TMEM_COLS);
+}
+
+}  // namespace mpsa
+
+using namespace mpsa;
+
+extern "C" int mpsa_gemm_block_scaled(const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                      void* c, int M, int N, int K, long long lda_bytes, long long ldb_bytes,
+                                      long long ldc, int mode, int a_fmt, int b_fmt, int out_dtype, float alpha,
+                                      int* status, void* stream) {
+  if (!a || !b || !a_scale || !b_scale || !c || !status)
+    return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: null pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: non-positive shape");
+  if (mode < 0 || mode > 2) return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: mode must be 0 (mxfp8), 1 (mxfp4) or 2 (nvfp4)");
+  if (out_dtype < 0 || out_dtype > 3) return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: out_dtype must be 0..3");
+  const int chunk = mode == 2 ? 64 : 128;
+  if (K % chunk != 0) return set_error(MPSA_ERR_UNSUPPORTED, "gemm_block_scaled: K must be a multiple of %d for this mode", chunk);
+  if (mode == 0 && !((a_fmt == 0 || a_fmt == 1) && (b_fmt == 0 || b_fmt == 1)))
+    return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: mxfp8 element formats are 0 (E4M3) or 1 (E5M2)");
+  const int epb = mode == 0 ? 1 : 2;
+  const long long kbytes = K / epb;
+  if (((uintptr_t)a % 16) || ((uintptr_t)b % 16) || (lda_bytes % 16) || (ldb_bytes % 16) || lda_bytes < kbytes ||
+      ldb_bytes < kbytes || ((uintptr_t)a_scale % 16) || ((uintptr_t)b_scale % 16))
+    return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: operands need 16-byte aligned bases and row pitches >= K bytes");
+  if (ldc < N) return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: ldc < N");
+  CUtensorMap ta, tb;
+  if (make_tmap_2d_bytes(&ta, a, kbytes, M, lda_bytes, GEMM_SLAB, GEMM_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      make_tmap_2d_bytes(&tb, b, kbytes, N, ldb_bytes, GEMM_SLAB, GEMM_BN, CU_TENSOR_MAP_SWIZZLE_128B))
+    return set_error(MPSA_ERR_LAUNCH, "gemm_block_scaled: cuTensorMapEncodeTiled failed");
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.mode = mode; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
+  p.sfa = (const uint8_t*)a_scale; p.sfb = (const uint8_t*)b_scale; p.nchunks = K / chunk;
+  p.c = c; p.ldc = ldc; p.out_dtype = out_dtype; p.alpha = alpha; p.status = status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_block_scaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
+      return set_error(MPSA_ERR_LAUNCH, "gemm_block_scaled: cannot reserve %d bytes of shared memory", GEMM_SMEM);
+    attr_set = true;
+  }
+  dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + GEMM_BN - 1) / GEMM_BN);
+  if (grid.y > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "gemm_block_scaled: N too large");
+  gemm_block_scaled_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ta, tb, p);
+  return check_launch("gemm_block_scaled");
+}

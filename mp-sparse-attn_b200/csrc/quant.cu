@@ -1,0 +1,311 @@
+// MX block quantizers (bf16/fp16/fp32 -> MXFP8 / MXFP4 with E8M0 scales per 32 elements, and the
+// per-32 int8 variant) for sm_100a.
+//
+// One CTA handles a tile of 128 rows x 128 columns of one (batch, head).  Each thread owns runs of
+// 16 consecutive elements (128-bit loads), two neighbouring lanes own one 32-element block and
+// combine their amax with a single warp shuffle.  One pass over the input can emit, at once,
+//   * MXFP8 codes (E5M2 as in the reference, or E4M3), one byte per element,
+//   * MXFP4 codes packed two per byte (low nibble first) and/or one per byte (the reference's
+//     output format, ours/quant_mxint8.py:454),
+//   * the scales row-major [.., L, D/32] (reference format) and/or as 512-byte 128x4 tiles
+//     [.., ceil(L/128), ceil(D/128), 32, 4, 4] - the layout tcgen05.cp moves into TMEM unchanged
+//     (ours/mxfp_attn_kernel.py:56-57 builds the same layout with a separate permute+copy).
+// The kernel is HBM-bound: algorithmic bytes per element are 2 (bf16 in) + 1 (fp8) + 1/32, or
+// 2 + 1/2 + 1/32 for packed fp4.
+#include "api_internal.h"
+#include "quant_math.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace mpsa {
+
+struct QuantParams {
+  const void* x;
+  int in_dtype;               // 0 bf16, 1 fp16, 2 fp32
+  int B, H, L, D;
+  long long xs_b, xs_h, xs_l;  // input strides in elements (inner stride 1)
+  float s;                     // fp32 scalar multiplied into x before quantisation
+  int fp8_fmt;                 // FMT_FP8_E5M2 or FMT_FP8_E4M3
+  // reference-format outputs (strided like the input tensor's logical shape)
+  uint8_t* fp8_codes;  long long o8_b, o8_h, o8_l;
+  uint8_t* fp4_codes_unpacked;  long long o4_b, o4_h, o4_l;
+  uint8_t* fp8_scales_rm;      // [B,H,L,D/32]
+  uint8_t* fp4_scales_rm;
+  // kernel-format outputs (dense [B,H,L,*])
+  uint8_t* fp4_codes_packed;   // [B,H,L,D/2]
+  uint8_t* fp8_scales_tiled;   // [B,H,ceil(L/128),ceil(D/128),512]
+  uint8_t* fp4_scales_tiled;
+};
+
+template <typename T>
+__device__ __forceinline__ void load16(const T* p, float (&v)[16]);
+
+template <>
+__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[16]) {
+  uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+  uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void load16<__half>(const __half* p, float (&v)[16]) {
+  uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+  uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    __half2 h = *reinterpret_cast<__half2*>(&w[i]);
+    float2 f = __half22float2(h);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+template <>
+__device__ __forceinline__ void load16<float>(const float* p, float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float4 a = __ldg(reinterpret_cast<const float4*>(p) + i);
+    v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = a.z; v[4 * i + 3] = a.w;
+  }
+}
+
+constexpr int kQuantThreads = 256;
+constexpr int kRunsPerThread = 4;   // 256 threads * 4 runs * 16 elements = 128 x 128 tile
+
+template <typename T>
+__global__ void __launch_bounds__(kQuantThreads) quant_mx_kernel(const QuantParams p) {
+  __shared__ __align__(16) uint8_t sf8[512];
+  __shared__ __align__(16) uint8_t sf4[512];
+  const int tile_l = blockIdx.x, tile_d = blockIdx.y, bh = blockIdx.z;
+  const int b = bh / p.H, h = bh % p.H;
+  const int row0 = tile_l * 128, col0 = tile_d * 128;
+  const int tid = threadIdx.x;
+  const bool want8 = p.fp8_codes || p.fp8_scales_rm || p.fp8_scales_tiled;
+  const bool want4 = p.fp4_codes_unpacked || p.fp4_codes_packed || p.fp4_scales_rm || p.fp4_scales_tiled;
+
+  // padding of the scale tile: rows beyond L and k-blocks beyond D carry E8M0 1.0
+  reinterpret_cast<uint16_t*>(sf8)[tid] = 0x7f7f;
+  reinterpret_cast<uint16_t*>(sf4)[tid] = 0x7f7f;
+  __syncthreads();
+
+  const T* xb = reinterpret_cast<const T*>(p.x) + (long long)b * p.xs_b + (long long)h * p.xs_h;
+  float v[kRunsPerThread][16];
+  bool live[kRunsPerThread];
+#pragma unroll
+  for (int i = 0; i < kRunsPerThread; ++i) {
+    const int g = tid + i * kQuantThreads;      // run index inside the tile
+    const int r = row0 + (g >> 3), c = col0 + (g & 7) * 16;
+    live[i] = (r < p.L) && (c < p.D);
+    if (live[i]) {
+      load16<T>(xb + (long long)r * p.xs_l + c, v[i]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[i][j] = 0.0f;
+    }
+  }
+  const int nblk = p.D >> 5;
+#pragma unroll
+  for (int i = 0; i < kRunsPerThread; ++i) {
+    const int g = tid + i * kQuantThreads;
+    const int rl = g >> 3;                  // row inside the tile
+    const int r = row0 + rl, c = col0 + (g & 7) * 16;
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      v[i][j] = __fmul_rn(v[i][j], p.s);
+      amax = fmaxf(amax, fabsf(v[i][j]));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    if (!live[i]) continue;
+    const int kb = c >> 5;                  // 32-element block index along D
+    const int sf_off = (rl & 31) * 16 + (rl >> 5) * 4 + (kb & 3);
+    const bool writer = (tid & 1) == 0;
+    const long long row_lin = ((long long)b * p.H + h) * p.L + r;
+    if (want8) {
+      BlockScale bs = mx_block_scale(amax, p.fp8_fmt == FMT_FP8_E4M3 ? 8 : 7);
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+        if (!bs.zero) {
+          c0 = fp8_code(v[i][4 * j + 0] * bs.inv_scale, p.fp8_fmt);
+          c1 = fp8_code(v[i][4 * j + 1] * bs.inv_scale, p.fp8_fmt);
+          c2 = fp8_code(v[i][4 * j + 2] * bs.inv_scale, p.fp8_fmt);
+          c3 = fp8_code(v[i][4 * j + 3] * bs.inv_scale, p.fp8_fmt);
+        }
+        w[j] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+      }
+      if (p.fp8_codes) {
+        uint8_t* o = p.fp8_codes + (long long)b * p.o8_b + (long long)h * p.o8_h + (long long)r * p.o8_l + c;
+        *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      if (writer) {
+        sf8[sf_off] = bs.code;
+        if (p.fp8_scales_rm) p.fp8_scales_rm[row_lin * nblk + kb] = bs.code;
+      }
+    }
+    if (want4) {
+      BlockScale bs = mx_block_scale(amax, 3);
+      uint32_t code[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float y = v[i][j] * bs.inv_scale;
+        y = fminf(fmaxf(y, -6.0f), 6.0f);
+        code[j] = bs.zero ? 8u : fp4_code_ref(y);
+      }
+      if (p.fp4_codes_unpacked) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          w[j] = code[4 * j] | (code[4 * j + 1] << 8) | (code[4 * j + 2] << 16) | (code[4 * j + 3] << 24);
+        uint8_t* o = p.fp4_codes_unpacked + (long long)b * p.o4_b + (long long)h * p.o4_h +
+                     (long long)r * p.o4_l + c;
+        *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      if (p.fp4_codes_packed) {
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          lo |= code[j] << (4 * j);
+          hi |= code[8 + j] << (4 * j);
+        }
+        uint8_t* o = p.fp4_codes_packed + row_lin * (p.D >> 1) + (c >> 1);
+        *reinterpret_cast<uint2*>(o) = make_uint2(lo, hi);
+      }
+      if (writer) {
+        sf4[sf_off] = bs.code;
+        if (p.fp4_scales_rm) p.fp4_scales_rm[row_lin * nblk + kb] = bs.code;
+      }
+    }
+  }
+  __syncthreads();
+  // one coalesced 512-byte store per scale tile
+  const long long ntl = (p.L + 127) >> 7, ntd = (p.D + 127) >> 7;
+  const long long tile_lin = (((long long)b * p.H + h) * ntl + tile_l) * ntd + tile_d;
+  if (tid < 32) {
+    if (p.fp8_scales_tiled && want8)
+      reinterpret_cast<uint4*>(p.fp8_scales_tiled + tile_lin * 512)[tid] = reinterpret_cast<uint4*>(sf8)[tid];
+  } else if (tid < 64) {
+    if (p.fp4_scales_tiled && want4)
+      reinterpret_cast<uint4*>(p.fp4_scales_tiled + tile_lin * 512)[tid - 32] =
+          reinterpret_cast<uint4*>(sf4)[tid - 32];
+  }
+}
+
+// ---- per-32 int8 quantizer (ours/quant_mxint8.py:21-58) ------------------------------------
+struct QuantI8Params {
+  const void* x; int in_dtype; int B, H, L, D;
+  long long xs_b, xs_h, xs_l; float s;
+  int8_t* codes; long long o_b, o_h, o_l;
+  float* scales;   // [B,H,L,D/32]
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kQuantThreads) quant_i8_kernel(const QuantI8Params p) {
+  const int tile_l = blockIdx.x, tile_d = blockIdx.y, bh = blockIdx.z;
+  const int b = bh / p.H, h = bh % p.H;
+  const int tid = threadIdx.x;
+  const T* xb = reinterpret_cast<const T*>(p.x) + (long long)b * p.xs_b + (long long)h * p.xs_h;
+#pragma unroll
+  for (int i = 0; i < kRunsPerThread; ++i) {
+    const int g = tid + i * kQuantThreads;
+    const int r = tile_l * 128 + (g >> 3), c = tile_d * 128 + (g & 7) * 16;
+    const bool live = (r < p.L) && (c < p.D);
+    float v[16];
+    if (live) load16<T>(xb + (long long)r * p.xs_l + c, v);
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      v[j] = live ? __fmul_rn(v[j], p.s) : 0.0f;
+      amax = fmaxf(amax, fabsf(v[j]));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    if (!live) continue;
+    const float scale = __fadd_rn(__fdiv_rn(amax, 127.0f), 0.0000001f);
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t q0 = (uint8_t)int8_code_ref(v[4 * j + 0], scale), q1 = (uint8_t)int8_code_ref(v[4 * j + 1], scale);
+      uint32_t q2 = (uint8_t)int8_code_ref(v[4 * j + 2], scale), q3 = (uint8_t)int8_code_ref(v[4 * j + 3], scale);
+      w[j] = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
+    }
+    int8_t* o = p.codes + (long long)b * p.o_b + (long long)h * p.o_h + (long long)r * p.o_l + c;
+    *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+    if ((tid & 1) == 0) {
+      // stored scale goes through an E5M2 round trip (ours/quant_mxint8.py:57)
+      __nv_fp8_storage_t s8 = __nv_cvt_float_to_fp8(scale, __NV_SATFINITE, __NV_E5M2);
+      __half_raw hr = __nv_cvt_fp8_to_halfraw(s8, __NV_E5M2);
+      const long long row_lin = ((long long)b * p.H + h) * p.L + r;
+      p.scales[row_lin * (p.D >> 5) + (c >> 5)] = __half2float(__half(hr));
+    }
+  }
+}
+
+}  // namespace mpsa
+
+using namespace mpsa;
+
+extern "C" int mpsa_quant_mx(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b,
+                             long long xs_h, long long xs_l, float s, int fp8_fmt, void* fp8_codes,
+                             long long o8_b, long long o8_h, long long o8_l, void* fp4_codes_unpacked,
+                             long long o4_b, long long o4_h, long long o4_l, void* fp8_scales_rm,
+                             void* fp4_scales_rm, void* fp4_codes_packed, void* fp8_scales_tiled,
+                             void* fp4_scales_tiled, void* stream) {
+  if (!x || B <= 0 || H <= 0 || L <= 0 || D <= 0) return set_error(MPSA_ERR_BAD_ARG, "quant_mx: null input or non-positive shape");
+  if (D % 32 != 0) return set_error(MPSA_ERR_UNSUPPORTED, "quant_mx: head_dim must be a multiple of 32");
+  if (in_dtype < 0 || in_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "quant_mx: in_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
+  if (fp8_fmt != FMT_FP8_E5M2 && fp8_fmt != FMT_FP8_E4M3) return set_error(MPSA_ERR_BAD_ARG, "quant_mx: fp8_fmt must be 1 (E5M2) or 2 (E4M3)");
+  const int esz = in_dtype == 2 ? 4 : 2;
+  if (((uintptr_t)x % 16) || ((xs_b * esz) % 16) || ((xs_h * esz) % 16) || ((xs_l * esz) % 16))
+    return set_error(MPSA_ERR_BAD_ARG, "quant_mx: input base and strides must be 16-byte aligned");
+  if ((fp8_codes && (((uintptr_t)fp8_codes | o8_b | o8_h | o8_l) % 16)) ||
+      (fp4_codes_unpacked && (((uintptr_t)fp4_codes_unpacked | o4_b | o4_h | o4_l) % 16)) ||
+      (fp4_codes_packed && ((uintptr_t)fp4_codes_packed % 16)) ||
+      (fp8_scales_tiled && ((uintptr_t)fp8_scales_tiled % 16)) ||
+      (fp4_scales_tiled && ((uintptr_t)fp4_scales_tiled % 16)))
+    return set_error(MPSA_ERR_BAD_ARG, "quant_mx: output pointers and strides must be 16-byte aligned");
+  QuantParams p;
+  p.x = x; p.in_dtype = in_dtype; p.B = B; p.H = H; p.L = L; p.D = D;
+  p.xs_b = xs_b; p.xs_h = xs_h; p.xs_l = xs_l; p.s = s; p.fp8_fmt = fp8_fmt;
+  p.fp8_codes = (uint8_t*)fp8_codes; p.o8_b = o8_b; p.o8_h = o8_h; p.o8_l = o8_l;
+  p.fp4_codes_unpacked = (uint8_t*)fp4_codes_unpacked; p.o4_b = o4_b; p.o4_h = o4_h; p.o4_l = o4_l;
+  p.fp8_scales_rm = (uint8_t*)fp8_scales_rm; p.fp4_scales_rm = (uint8_t*)fp4_scales_rm;
+  p.fp4_codes_packed = (uint8_t*)fp4_codes_packed;
+  p.fp8_scales_tiled = (uint8_t*)fp8_scales_tiled; p.fp4_scales_tiled = (uint8_t*)fp4_scales_tiled;
+  dim3 grid((L + 127) / 128, (D + 127) / 128, B * H);
+  if (grid.y > 65535 || grid.z > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "quant_mx: B*H and D/128 must be below 65536");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (in_dtype == 0) quant_mx_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, st>>>(p);
+  else if (in_dtype == 1) quant_mx_kernel<__half><<<grid, kQuantThreads, 0, st>>>(p);
+  else quant_mx_kernel<float><<<grid, kQuantThreads, 0, st>>>(p);
+  return check_launch("quant_mx");
+}
+
+extern "C" int mpsa_quant_int8(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b,
+                               long long xs_h, long long xs_l, float s, void* codes, long long o_b,
+                               long long o_h, long long o_l, void* scales, void* stream) {
+  if (!x || !codes || !scales || B <= 0 || H <= 0 || L <= 0 || D <= 0)
+    return set_error(MPSA_ERR_BAD_ARG, "quant_int8: null pointer or non-positive shape");
+  if (D % 32 != 0) return set_error(MPSA_ERR_UNSUPPORTED, "quant_int8: head_dim must be a multiple of 32");
+  if (in_dtype < 0 || in_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "quant_int8: bad in_dtype");
+  const int esz = in_dtype == 2 ? 4 : 2;
+  if (((uintptr_t)x % 16) || ((xs_b * esz) % 16) || ((xs_h * esz) % 16) || ((xs_l * esz) % 16) ||
+      (((uintptr_t)codes | o_b | o_h | o_l) % 16))
+    return set_error(MPSA_ERR_BAD_ARG, "quant_int8: pointers and strides must be 16-byte aligned");
+  QuantI8Params p;
+  p.x = x; p.in_dtype = in_dtype; p.B = B; p.H = H; p.L = L; p.D = D;
+  p.xs_b = xs_b; p.xs_h = xs_h; p.xs_l = xs_l; p.s = s;
+  p.codes = (int8_t*)codes; p.o_b = o_b; p.o_h = o_h; p.o_l = o_l; p.scales = (float*)scales;
+  dim3 grid((L + 127) / 128, (D + 127) / 128, B * H);
+  if (grid.y > 65535 || grid.z > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "quant_int8: B*H and D/128 must be below 65536");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (in_dtype == 0) quant_i8_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, st>>>(p);
+  else if (in_dtype == 1) quant_i8_kernel<__half><<<grid, kQuantThreads, 0, st>>>(p);
+  else quant_i8_kernel<float><<<grid, kQuantThreads, 0, st>>>(p);
+  return check_launch("quant_int8");
+}

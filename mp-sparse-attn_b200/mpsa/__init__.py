@@ -1,0 +1,11 @@
+"""B200-native kernels for diagonal-tiled mixed-precision (MXFP) attention.
+
+`mpsa.ops` holds the tensor-level operations (torch tensors in, torch tensors out, CUDA work
+done by libmpsa.so through its C-ABI); the `ours` package beside this one mirrors the
+reference project's module and function names on top of them.
+"""
+from . import _lib  # noqa: F401
+from .ops import (  # noqa: F401
+    TILE_SKIP, TILE_FP8, TILE_FP4, QuantizedOperand, quantize_mx, quantize_int8, prepare_vt,
+    precision_map_band, attention_forward, attention_forward_quantized, diagonal_tiled_attention, gemm_block_scaled, check_status,
+)

@@ -1,0 +1,300 @@
+"""Tensor-level operations on top of the C-ABI.  torch supplies device memory and streams; all
+arithmetic runs in the hand-written sm_100a kernels of libmpsa.so."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+TILE_SKIP, TILE_FP8, TILE_FP4 = 0, 1, 2
+LOG2E = 1.44269504  # ours/quant_mxint8.py:494
+
+_IN_DTYPE = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+_OUT_DTYPE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.float8_e5m2: 3}
+_FP8_QUANT = {"e5m2": 1, "e4m3": 2}
+_FP8_DESC = {"e5m2": 1, "e4m3": 0}
+_status = {}
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("mpsa operations need CUDA tensors; there is no CPU path")
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word the kernels write when one of their bounded waits expires."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+    return _status[key]
+
+
+def check_status(device=None):
+    """Synchronise and raise if a kernel recorded an expired wait (1 TMA, 2 MMA, 3 pipeline)."""
+    dev = torch.cuda.current_device() if device is None else device
+    w = status_word(dev)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise _lib.MpsaError(f"a kernel gave up waiting (status {code}: "
+                             f"{ {1: 'TMA bytes', 2: 'tensor-core commit', 3: 'pipeline hand-off'}.get(code, '?')})")
+
+
+def q_side_scale(head_dim: int, sm_scale: Optional[float] = None) -> float:
+    """sm_scale * log2(e), the factor the reference folds into Q (ours/quant_mxint8.py:479-494)."""
+    if sm_scale is None:
+        sm_scale = head_dim ** -0.5
+    return sm_scale * LOG2E
+
+
+@dataclass
+class QuantizedOperand:
+    """One side (Q or K) quantised for the tensor cores; any field may be None if not requested."""
+    fp8: Optional[torch.Tensor] = None          # uint8 [B,H,L,D]
+    fp8_sf: Optional[torch.Tensor] = None       # uint8 [B,H,ceil(L/128),ceil(D/128),512]
+    fp4: Optional[torch.Tensor] = None          # uint8 [B,H,L,D/2] packed
+    fp4_sf: Optional[torch.Tensor] = None
+    fp8_scales: Optional[torch.Tensor] = None   # uint8 [B,H,L,D/32] row-major (reference format)
+    fp4_scales: Optional[torch.Tensor] = None
+    fp4_unpacked: Optional[torch.Tensor] = None  # uint8 [B,H,L,D] one code per byte (reference format)
+    fp8_elem: str = "e5m2"
+
+
+def _bhld(x: torch.Tensor, tensor_layout: str):
+    """Logical (B,H,L,D) view parameters of a HND or NHD tensor: sizes and element strides."""
+    if x.dim() != 4:
+        raise ValueError("expected a 4-D tensor")
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    if tensor_layout == "HND":
+        B, H, L, D = x.shape
+        sb, sh, sl = x.stride(0), x.stride(1), x.stride(2)
+    elif tensor_layout == "NHD":
+        B, L, H, D = x.shape
+        sb, sh, sl = x.stride(0), x.stride(2), x.stride(1)
+    else:
+        raise ValueError(f"Unknown tensor layout: {tensor_layout}")
+    return x, (B, H, L, D), (sb, sh, sl)
+
+
+def quantize_mx(x: torch.Tensor, scale: float = 1.0, *, want_fp8=True, want_fp4=True, reference_format=False,
+                kernel_format=True, fp8_elem="e5m2", tensor_layout="HND") -> QuantizedOperand:
+    """Quantise one operand along its last axis in 32-element MX blocks (one kernel launch).
+
+    reference_format: emit what ours/quant_mxint8.py returns (fp4 one code per byte, row-major
+    scales, shaped like the input).  kernel_format: emit packed fp4 and 128x4 scale tiles."""
+    _require_cuda(x)
+    if x.dtype not in _IN_DTYPE:
+        raise ValueError(f"unsupported input dtype {x.dtype}")
+    x, (B, H, L, D), (sb, sh, sl) = _bhld(x, tensor_layout)
+    dev = x.device
+    out = QuantizedOperand(fp8_elem=fp8_elem)
+    u8 = dict(dtype=torch.uint8, device=dev)
+    nl, nd = -(-L // 128), -(-D // 128)
+    o8 = (0, 0, 0)
+    o4 = (0, 0, 0)
+
+    def _strides(t):
+        return (t.stride(0), t.stride(1), t.stride(2)) if tensor_layout == "HND" else \
+            (t.stride(0), t.stride(2), t.stride(1))
+
+    if want_fp8:
+        out.fp8 = torch.empty(x.shape, **u8)
+        o8 = _strides(out.fp8)
+        if reference_format:
+            out.fp8_scales = torch.empty((B, H, L, D // 32), **u8)
+        if kernel_format:
+            out.fp8_sf = torch.empty((B, H, nl, nd, 512), **u8)
+    if want_fp4:
+        if reference_format:
+            out.fp4_unpacked = torch.empty(x.shape, **u8)
+            o4 = _strides(out.fp4_unpacked)
+            out.fp4_scales = torch.empty((B, H, L, D // 32), **u8)
+        if kernel_format:
+            out.fp4 = torch.empty((B, H, L, D // 2), **u8)
+            out.fp4_sf = torch.empty((B, H, nl, nd, 512), **u8)
+    with torch.cuda.device(dev):
+        rc = _lib.load().mpsa_quant_mx(
+            x.data_ptr(), _IN_DTYPE[x.dtype], B, H, L, D, sb, sh, sl, float(scale), _FP8_QUANT[fp8_elem],
+            _ptr(out.fp8), *o8, _ptr(out.fp4_unpacked), *o4, _ptr(out.fp8_scales), _ptr(out.fp4_scales),
+            _ptr(out.fp4), _ptr(out.fp8_sf), _ptr(out.fp4_sf), _stream())
+    _lib.check(rc)
+    return out
+
+
+def quantize_int8(x: torch.Tensor, scale: float = 1.0, tensor_layout="HND"):
+    """Per-32 int8 codes and fp32 scales of one operand (ours/quant_mxint8.py:21-58)."""
+    _require_cuda(x)
+    x, (B, H, L, D), (sb, sh, sl) = _bhld(x, tensor_layout)
+    codes = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    oc = (codes.stride(0), codes.stride(1), codes.stride(2)) if tensor_layout == "HND" else \
+        (codes.stride(0), codes.stride(2), codes.stride(1))
+    scales = torch.empty((B, H, L, D // 32), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().mpsa_quant_int8(x.data_ptr(), _IN_DTYPE[x.dtype], B, H, L, D, sb, sh, sl, float(scale),
+                                         codes.data_ptr(), *oc, scales.data_ptr(), _stream())
+    _lib.check(rc)
+    return codes, scales
+
+
+def prepare_vt(v: torch.Tensor) -> torch.Tensor:
+    """V [B,H,Skv,D] -> fp16 V^T [B,H,D,Skv_pad] (Skv_pad = Skv rounded up to 128, zero filled)."""
+    _require_cuda(v)
+    if v.stride(-1) != 1:
+        v = v.contiguous()
+    B, H, Skv, D = v.shape
+    pad = -(-Skv // 128) * 128
+    vt = torch.empty((B, H, D, pad), dtype=torch.float16, device=v.device)
+    with torch.cuda.device(v.device):
+        rc = _lib.load().mpsa_prepare_vt(v.data_ptr(), _IN_DTYPE[v.dtype], vt.data_ptr(), B, H, Skv, D, pad,
+                                         v.stride(0), v.stride(1), v.stride(2), _stream())
+    _lib.check(rc)
+    return vt
+
+
+def precision_map_band(S: int, Skv: int, causal: bool, band: int = 1, tile: int = 128, device="cuda") -> torch.Tensor:
+    """uint8 [ceil(S/tile), ceil(Skv/tile)]: FP8 within `band` tiles of the diagonal, FP4 elsewhere,
+    SKIP above the causal diagonal."""
+    nq, nk = -(-S // tile), -(-Skv // tile)
+    m = torch.empty((nq, nk), dtype=torch.uint8, device=device)
+    with torch.cuda.device(m.device):
+        rc = _lib.load().mpsa_route_band(m.data_ptr(), nq, nk, tile, int(causal), band, S, Skv, _stream())
+    _lib.check(rc)
+    return m
+
+
+def _pad_depth_128(x: torch.Tensor) -> torch.Tensor:
+    D = x.shape[-1]
+    if D == 128:
+        return x
+    return torch.nn.functional.pad(x, (0, 128 - D))
+
+
+def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, band: int = 1,
+                      prec_map: Optional[torch.Tensor] = None, uniform: Optional[str] = None,
+                      sm_scale: Optional[float] = None, fp8_elem: str = "e5m2",
+                      out_dtype: torch.dtype = torch.bfloat16, check: bool = False) -> torch.Tensor:
+    """Quantise Q/K (both MXFP8 and MXFP4 in one pass each), transpose V, build the precision map and
+    run the fused forward.  q [B,Hq,S,D], k/v [B,Hkv,Skv,D]; D in {64, 128}."""
+    _require_cuda(q, k, v)
+    B, Hq, S, D = q.shape
+    _, Hkv, Skv, _ = k.shape
+    if D not in (64, 128):
+        raise ValueError("headdim should be in [64, 128].")
+    sq = q_side_scale(D, sm_scale)
+    qq = quantize_mx(_pad_depth_128(q), sq, fp8_elem=fp8_elem)
+    kq = quantize_mx(_pad_depth_128(k), 1.0, fp8_elem=fp8_elem)
+    vt = prepare_vt(v)
+    return attention_forward_quantized(qq, kq, vt, B, Hq, Hkv, S, Skv, D, causal=causal, band=band,
+                                       prec_map=prec_map, uniform=uniform, out_dtype=out_dtype, check=check)
+
+
+def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt: torch.Tensor, B: int, Hq: int,
+                                Hkv: int, S: int, Skv: int, D: int, *, causal: bool, band: int = 1,
+                                prec_map: Optional[torch.Tensor] = None, uniform: Optional[str] = None,
+                                out_dtype: torch.dtype = torch.bfloat16, check: bool = False) -> torch.Tensor:
+    """The fused forward on operands that are already quantised (depth padded to 128) and a V^T from
+    prepare_vt.  Both formats of Q and K must be present unless `uniform` restricts the map to one."""
+    dev = vt.device
+    nq, nk = -(-S // 128), -(-Skv // 128)
+    if prec_map is None:
+        prec_map = precision_map_band(S, Skv, causal, band, 128, dev)
+        if uniform is not None:
+            code = TILE_FP8 if uniform == "fp8" else TILE_FP4
+            prec_map = torch.where(prec_map == TILE_SKIP, prec_map, torch.full_like(prec_map, code))
+    if prec_map.dtype != torch.uint8 or tuple(prec_map.shape[-2:]) != (nq, nk):
+        raise ValueError(f"precision map must be uint8 [..., {nq}, {nk}]")
+    prec_map = prec_map.contiguous()
+    if prec_map.dim() == 2:
+        msb = msh = 0
+    elif prec_map.dim() == 4:
+        if tuple(prec_map.shape[:2]) != (B, Hq):
+            raise ValueError("4-D precision map must be [B, Hq, nq, nk]")
+        msb, msh = prec_map.stride(0), prec_map.stride(1)
+    else:
+        raise ValueError("precision map must be 2-D or 4-D")
+    if out_dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"Unsupported dtype: {out_dtype}")
+
+    # A format the map never selects may be absent; the kernel still maps both, so stand in a
+    # zero buffer of the right size (never a smaller one: the TMA map spans rows x row-bytes).
+    def _codes(t, rows, row_bytes):
+        return t if t is not None else torch.zeros((rows, row_bytes), dtype=torch.uint8, device=dev)
+    q8, q4 = _codes(qq.fp8, B * Hq * S, 128), _codes(qq.fp4, B * Hq * S, 64)
+    k8, k4 = _codes(kq.fp8, B * Hkv * Skv, 128), _codes(kq.fp4, B * Hkv * Skv, 64)
+    q8s = qq.fp8_sf if qq.fp8_sf is not None else qq.fp4_sf
+    q4s = qq.fp4_sf if qq.fp4_sf is not None else qq.fp8_sf
+    k8s = kq.fp8_sf if kq.fp8_sf is not None else kq.fp4_sf
+    k4s = kq.fp4_sf if kq.fp4_sf is not None else kq.fp8_sf
+    for t, rows, rb in ((q8, B * Hq * S, 128), (q4, B * Hq * S, 64), (k8, B * Hkv * Skv, 128), (k4, B * Hkv * Skv, 64)):
+        if t.numel() != rows * rb or not t.is_contiguous():
+            raise ValueError("quantised operand has the wrong size (depth must be padded to 128)")
+    for t, n in ((q8s, B * Hq * nq), (q4s, B * Hq * nq), (k8s, B * Hkv * nk), (k4s, B * Hkv * nk)):
+        if t.numel() != n * 512 or not t.is_contiguous():
+            raise ValueError("scale tiles have the wrong size")
+    if vt.shape[-1] % 128 or vt.shape[-1] < Skv or tuple(vt.shape[:3]) != (B, Hkv, D) or vt.dtype != torch.float16:
+        raise ValueError("vt must be fp16 [B, Hkv, D, Skv rounded up to 128]")
+    if (qq.fp8 is None or kq.fp8 is None) and uniform != "fp4":
+        raise ValueError("MXFP8 operands missing but the precision map may select FP8 tiles")
+    if (qq.fp4 is None or kq.fp4 is None) and uniform != "fp8":
+        raise ValueError("MXFP4 operands missing but the precision map may select FP4 tiles")
+    out = torch.empty((B, Hq, S, D), dtype=out_dtype, device=dev)
+    st = status_word(dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().mpsa_attn_fwd(
+            q8.data_ptr(), q8s.data_ptr(), q4.data_ptr(), q4s.data_ptr(),
+            k8.data_ptr(), k8s.data_ptr(), k4.data_ptr(), k4s.data_ptr(),
+            vt.data_ptr(), prec_map.data_ptr(), msb, msh, out.data_ptr(), _OUT_DTYPE[out_dtype],
+            B, Hq, Hkv, S, Skv, D, vt.shape[-1], int(causal), _FP8_DESC[qq.fp8_elem], st.data_ptr(), _stream())
+    _lib.check(rc)
+    if check:
+        check_status(dev)
+    return out
+
+
+def diagonal_tiled_attention(q, k, v, causal=True):
+    """README-level entry of the reference project: diagonal tiles in MXFP8, the rest in MXFP4."""
+    return attention_forward(q, k, v, causal=causal, out_dtype=q.dtype if q.dtype != torch.float32 else torch.float32)
+
+
+_GEMM_MODE = {"mxfp8": 0, "mxfp4": 1, "nvfp4": 2}
+
+
+def gemm_block_scaled(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor,
+                      out_dtype: torch.dtype, M: int, N: int, K: int, mode: str, *, a_elem="e5m2", b_elem="e5m2",
+                      alpha: float = 1.0, check: bool = False) -> torch.Tensor:
+    """C[M,N] = alpha * (A.sa)(B.sb)^T.  a [M,K/epb] / b [N,K/epb] bytes (uint8 or float8), scales as 128x4
+    tiles [rows/128, K/vec/4, 32,4,4] (uint8 E8M0, or E4M3 bytes for nvfp4)."""
+    _require_cuda(a, b, a_scale, b_scale)
+    if mode not in _GEMM_MODE:
+        raise ValueError(f"Invalid block scale type: {mode}")
+    if out_dtype not in _OUT_DTYPE:
+        raise ValueError(f"Unsupported dtype: {out_dtype}")
+    if a.stride(-1) != 1:
+        a = a.contiguous()
+    if b.stride(-1) != 1:
+        b = b.contiguous()
+    a_scale, b_scale = a_scale.contiguous(), b_scale.contiguous()
+    c = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    st = status_word(a.device)
+    with torch.cuda.device(a.device):
+        rc = _lib.load().mpsa_gemm_block_scaled(
+            a.data_ptr(), a_scale.data_ptr(), b.data_ptr(), b_scale.data_ptr(), c.data_ptr(), M, N, K,
+            a.stride(0) * a.element_size(), b.stride(0) * b.element_size(), c.stride(0), _GEMM_MODE[mode],
+            _FP8_DESC[a_elem], _FP8_DESC[b_elem], _OUT_DTYPE[out_dtype], float(alpha), st.data_ptr(), _stream())
+    _lib.check(rc)
+    if check:
+        check_status(a.device)
+    return c

@@ -1,0 +1,62 @@
+"""Fused MXFP attention with the entry points of ours/mxfp_attn_kernel.py of the reference:
+mxfp_attn_kernel (:19-74) and block_scaled_batched_attn (:362-423)."""
+import torch
+
+from mpsa import ops as _ops
+
+
+@torch.compiler.disable
+def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
+                     is_causal=False, scale=None, smooth_k=False, attention_sink=False, tensor_layout="HND",
+                     output_dtype=torch.float16, return_sparsity=False, block_scale_type="mxfp4", skip_thresh=None):
+    """q [B,Hq,S,D], k/v [B,Hkv,Skv,D] (HND) or [B,S,H,D] (NHD) -> o in q's layout.
+
+    block_scale_type: "mxfp4" / "mxfp8" quantise every tile of Q.K^T to that format (the two modes
+    of the reference); "diag" keeps the diagonal tiles in MXFP8 and the rest in MXFP4.
+    attn_mask, dropout_p, attention_sink, return_sparsity and skip_thresh are accepted and ignored,
+    as in the reference wrapper; is_causal, scale and output_dtype are honoured (the reference
+    ignores them)."""
+    torch.cuda.set_device(v.device)
+    if tensor_layout == "NHD":
+        q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    elif tensor_layout != "HND":
+        raise ValueError(f"Unknown tensor layout: {tensor_layout}")
+    if q.dtype == torch.float32:
+        q, k = q.to(torch.float16), k.to(torch.float16)      # ours/mxfp_attn_kernel.py:28-29
+    if smooth_k:
+        k = k - k.mean(dim=-2, keepdim=True)                 # :33-34
+    assert q.shape[-1] in [64, 128], "headdim should be in [64, 128]."
+    if block_scale_type == "mxfp4":
+        uniform = "fp4"
+    elif block_scale_type == "diag":
+        uniform = None
+    else:
+        uniform = "fp8"
+    o = _ops.attention_forward(q, k, v, causal=bool(is_causal), uniform=uniform, sm_scale=scale,
+                               out_dtype=output_dtype)
+    return o.transpose(1, 2) if tensor_layout == "NHD" else o
+
+
+def block_scaled_batched_attn(a_desc, a_scale, b_desc, b_scale, v_ori, dtype_dst, B, H, M, N, K, configs, STAGE=1,
+                              skip_thresh=None):
+    """Attention from already-quantised operands in the reference's formats: a/b fp8 [B,H,L,K]
+    (float8_e5m2) or packed fp4 [B,H,L,K/2], scales as 128x4 tiles [B,H,L/128,K/32/4,32,4,4]
+    (K must be 128), v [B,H,N,K].  STAGE 1 = full attention; STAGE 3 = causal."""
+    if dtype_dst not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"Unsupported dtype: {dtype_dst}")
+    if K != 128:
+        raise ValueError("pre-quantised operands need head_dim 128")
+    fp4 = configs["ELEM_PER_BYTE_A"] == 2
+    elem = "e4m3" if a_desc.dtype == torch.float8_e4m3fn else "e5m2"
+
+    def operand(codes, scales):
+        c = codes.view(torch.uint8).contiguous()
+        s = scales.view(torch.uint8).contiguous().reshape(B, H, -1, 1, 512)
+        if fp4:
+            return _ops.QuantizedOperand(fp4=c, fp4_sf=s, fp8_elem=elem)
+        return _ops.QuantizedOperand(fp8=c, fp8_sf=s, fp8_elem=elem)
+
+    Hkv = v_ori.shape[1]
+    return _ops.attention_forward_quantized(operand(a_desc, a_scale), operand(b_desc, b_scale),
+                                            _ops.prepare_vt(v_ori), B, H, Hkv, M, N, K, causal=(STAGE == 3),
+                                            uniform="fp4" if fp4 else "fp8", out_dtype=dtype_dst)

@@ -303,10 +303,12 @@ def gemm_block_scaled(a_codes, a_scales, b_codes, b_scales, fmt_a: str, fmt_b: s
 # --------------------------------------------------------------------------------------
 # precision map (no counterpart in the reference; PARITY UNPINNED)
 # --------------------------------------------------------------------------------------
-def precision_map_band(n_q_tiles: int, n_k_tiles: int, causal: bool, band: int = 1) -> torch.Tensor:
+def precision_map_band(n_q_tiles: int, n_k_tiles: int, causal: bool, band: int = 1,
+                       off_tiles: int = 0) -> torch.Tensor:
     """uint8 [n_q_tiles, n_k_tiles]: FP8 iff |i-j| < band, else FP4; causal => j>i SKIP.
-    The causal tile range follows the two-stage loop of ours/online_routing.py:68-77."""
-    i = torch.arange(n_q_tiles)[:, None]
+    ``off_tiles`` = (Skv - S) / tile shifts the diagonal when the queries are the last S of Skv
+    positions.  The causal tile range follows the two-stage loop of ours/online_routing.py:68-77."""
+    i = torch.arange(n_q_tiles)[:, None] + off_tiles
     j = torch.arange(n_k_tiles)[None, :]
     m = torch.where((i - j).abs() < band, TILE_FP8, TILE_FP4).to(torch.uint8)
     if causal:
@@ -373,7 +375,7 @@ def attention_mxfp(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
     K8, K4 = dequant(k8c, k8s, f8), dequant(k4c, k4s, "fp4")
     nq, nk = -(-S // tile), -(-Skv // tile)
     if prec_map is None:
-        prec_map = precision_map_band(nq, nk, causal, band)
+        prec_map = precision_map_band(nq, nk, causal, band, (Skv - S) // tile)
         if uniform is not None:
             code = TILE_FP8 if uniform == "fp8" else TILE_FP4
             prec_map = torch.where(prec_map == TILE_SKIP, prec_map,

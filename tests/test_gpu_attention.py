@@ -1,0 +1,126 @@
+"""Fused attention forward against the CPU oracle on the same seeded inputs.
+
+Tolerances (from the task statement): cosine similarity >= 0.9999 and relative L2 <= 1e-2 against
+the oracle's MXFP emulation with P in fp16 (the reference's P.V precision); the error against
+plain fp32 attention is only reported."""
+import pytest
+import torch
+
+from oracle import mx_oracle as O
+
+pytestmark = pytest.mark.gpu
+COS_MIN, REL_L2_MAX = 0.9999, 1e-2
+
+
+def _run(q, k, v, causal, **kw):
+    import mpsa
+    out = mpsa.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal=causal, out_dtype=torch.float32, check=True, **kw)
+    return out.cpu()
+
+
+def _check(out, ref, what):
+    m = O.parity_metrics(out, ref)
+    assert m["cos"] >= COS_MIN and m["rel_l2"] <= REL_L2_MAX, (what, m)
+    return m
+
+
+@pytest.mark.parametrize("uniform", ["fp8", "fp4", None])
+@pytest.mark.parametrize("causal", [False, True])
+def test_one_and_two_tiles(uniform, causal):
+    for S in (128, 256):
+        q, k, v = O.make_qkv(0, 1, 2, 2, S, 128)
+        ref = O.attention_mxfp(q, k, v, causal=causal, uniform=uniform)
+        _check(_run(q, k, v, causal, uniform=uniform), ref, (S, uniform, causal))
+
+
+def test_map_is_identical_to_oracle():
+    import mpsa
+    for (S, Skv, causal, band) in [(1024, 1024, True, 1), (1024, 1024, False, 1), (640, 640, True, 2), (300, 300, True, 1)]:
+        got = mpsa.precision_map_band(S, Skv, causal, band).cpu()
+        exp = O.precision_map_band(-(-S // 128), -(-Skv // 128), causal, band)
+        assert torch.equal(got, exp)
+    got = mpsa.precision_map_band(1024, 1024, True, 1, tile=64).cpu()
+    assert torch.equal(got, O.precision_map_band(16, 16, True, 1))
+
+
+def test_plumbing_config_d64():
+    """B=1, H=8, S=1024, D=64 causal, seed 0 (128x128 tiles)."""
+    q, k, v = O.make_qkv(0, 1, 8, 8, 1024, 64)
+    ref = O.attention_mxfp(q, k, v, causal=True)
+    out = _run(q, k, v, True)
+    _check(out, ref, "cfg1")
+    print("vs fp32 attention:", O.parity_metrics(out, O.attention_fp32(q, k, v, True)))
+
+
+def test_gqa_outliers_causal():
+    """Llama-3-8B-like head layout at a small sequence: Hq=8, Hkv=2, D=128, outlier K channels."""
+    q, k, v = O.make_qkv(2, 1, 8, 2, 1024, 128, outliers=5)
+    ref = O.attention_mxfp(q, k, v, causal=True)
+    _check(_run(q, k, v, True), ref, "gqa")
+
+
+def test_ragged_lengths_and_custom_map():
+    q, k, v = O.make_qkv(3, 2, 2, 1, 333, 128)
+    for causal in (False, True):
+        ref = O.attention_mxfp(q, k, v, causal=causal)
+        _check(_run(q, k, v, causal), ref, ("ragged", causal))
+    # arbitrary per-(batch, head) map: checkerboard of FP8 / FP4 tiles, non causal
+    B, H, S = 2, 2, 512
+    q, k, v = O.make_qkv(4, B, H, H, S, 128)
+    g = torch.Generator().manual_seed(1)
+    pm = torch.randint(1, 3, (B, H, 4, 4), generator=g, dtype=torch.uint8)
+    ref = O.attention_mxfp(q, k, v, causal=False, prec_map=pm)
+    _check(_run(q, k, v, False, prec_map=pm.cuda()), ref, "custom map")
+    # skipped tiles in a non-causal map, and a row tile with nothing to attend to -> zeros
+    pm[:, :, 1, :] = 0
+    pm[:, :, 2, 1] = 0
+    ref = O.attention_mxfp(q, k, v, causal=False, prec_map=pm)
+    out = _run(q, k, v, False, prec_map=pm.cuda())
+    assert float(out[:, :, 128:256].abs().max()) == 0.0
+    keep = torch.ones(S, dtype=torch.bool)
+    keep[128:256] = False
+    _check(out[:, :, keep], ref[:, :, keep], "skips")
+
+
+def test_reference_entry_points():
+    from ours.mxfp_attn_kernel import mxfp_attn_kernel
+    from ours.mxfp_attn import mxfp_attn
+    q, k, v = O.make_qkv(5, 1, 4, 4, 512, 128, dtype=torch.float16)
+    for bst, uni in (("mxfp4", "fp4"), ("mxfp8", "fp8")):
+        ref = O.attention_mxfp(q, k, v, causal=False, uniform=uni)
+        o = mxfp_attn_kernel(q.cuda(), k.cuda(), v.cuda(), is_causal=False, block_scale_type=bst, skip_thresh=-1e9)
+        assert o.dtype == torch.float16 and o.shape == q.shape
+        m = O.parity_metrics(o.float().cpu(), ref)
+        assert m["cos"] >= COS_MIN and m["rel_l2"] <= REL_L2_MAX, m
+    o = mxfp_attn(q.cuda(), k.cuda(), v.cuda(), is_causal=True, smooth_k=False, block_scale_type="diag",
+                  output_dtype=torch.bfloat16)
+    ref = O.attention_mxfp(q, k, v, causal=True)
+    m = O.parity_metrics(o.float().cpu(), ref)
+    assert o.dtype == torch.bfloat16 and m["cos"] >= 0.9999 and m["rel_l2"] <= 1.5e-2, m
+    # NHD layout
+    o2 = mxfp_attn_kernel(q.transpose(1, 2).contiguous().cuda(), k.transpose(1, 2).contiguous().cuda(),
+                          v.transpose(1, 2).contiguous().cuda(), is_causal=False, tensor_layout="NHD",
+                          block_scale_type="mxfp8")
+    ref = O.attention_mxfp(q, k, v, causal=False, uniform="fp8")
+    m = O.parity_metrics(o2.transpose(1, 2).float().cpu(), ref)
+    assert m["cos"] >= COS_MIN and m["rel_l2"] <= REL_L2_MAX, m
+    with pytest.raises(AssertionError):
+        mxfp_attn_kernel(torch.zeros(1, 1, 128, 96, device="cuda", dtype=torch.float16),
+                         torch.zeros(1, 1, 128, 96, device="cuda", dtype=torch.float16),
+                         torch.zeros(1, 1, 128, 96, device="cuda", dtype=torch.float16))
+
+
+def test_long_sequence_slice_and_properties():
+    """S = 8192 with the Llama-like layout: a slice of query rows of one head against the oracle,
+    and row-stochastic behaviour (V = ones -> O = ones) over the whole output."""
+    import mpsa
+    q, k, v = O.make_qkv(2, 1, 8, 2, 8192, 128, outliers=5)
+    out = mpsa.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal=True, out_dtype=torch.float32, check=True)
+    h = 5
+    rows = slice(8192 - 256, 8192)
+    ref = O.attention_mxfp(q[:, h:h + 1, rows], k[:, h // 4:h // 4 + 1], v[:, h // 4:h // 4 + 1], causal=True,
+                           prec_map=O.precision_map_band(64, 64, True)[62:64])
+    _check(out[:, h:h + 1, rows].cpu(), ref, "slice")
+    ones = torch.ones_like(v)
+    o1 = mpsa.attention_forward(q.cuda(), k.cuda(), ones.cuda(), causal=True, out_dtype=torch.float32, check=True)
+    assert float((o1 - 1).abs().max()) < 2e-3

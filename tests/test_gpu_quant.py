@@ -1,0 +1,110 @@
+"""CUDA quantizers (through the C-ABI) against the golden vectors and the CPU oracle: bit-exact
+codes and scale codes, both the reference output format and the kernel format."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import mx_oracle as O
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def _gold():
+    return np.load(os.path.join(G, "quant_kat.npz"))
+
+
+@pytest.mark.parametrize("tag", ["kat", "d128", "d64"])
+def test_reference_signatures_match_golden(tag):
+    from ours.quant_mxint8 import quant_mxfp4, quant_mxfp8e5, quant_fpxint8
+    z = _gold()
+    if tag == "kat":
+        q = k = torch.from_numpy(z["kat_x"]).view(torch.bfloat16)
+    else:
+        q = torch.from_numpy(z[f"{tag}_q"]).view(torch.bfloat16)
+        k = torch.from_numpy(z[f"{tag}_k"]).view(torch.bfloat16)
+    qd, kd = q.cuda(), k.cuda()
+    a, sa, b, sb = quant_mxfp4(qd, kd)
+    assert a.dtype == torch.uint8 and a.shape == q.shape and sa.shape == q.shape[:-1] + (q.shape[-1] // 32,)
+    assert np.array_equal(a.cpu().numpy(), z[f"{tag}_fp4_q"]) and np.array_equal(sa.cpu().numpy(), z[f"{tag}_fp4_qs"])
+    assert np.array_equal(b.cpu().numpy(), z[f"{tag}_fp4_k"]) and np.array_equal(sb.cpu().numpy(), z[f"{tag}_fp4_ks"])
+    a, sa, b, sb = quant_mxfp8e5(qd, kd)
+    assert a.dtype == torch.float8_e5m2
+    assert np.array_equal(sa.cpu().numpy(), z[f"{tag}_fp8_qs"]) and np.array_equal(sb.cpu().numpy(), z[f"{tag}_fp8_ks"])
+    oq, _, ok, _ = O.quant_mxfp8e5(q, k)
+    assert torch.equal(a.view(torch.uint8).cpu(), oq) and torch.equal(b.view(torch.uint8).cpu(), ok)
+    a, sa, b, sb = quant_fpxint8(qd, kd)
+    assert np.array_equal(a.cpu().numpy(), z[f"{tag}_i8_q"]) and np.array_equal(b.cpu().numpy(), z[f"{tag}_i8_k"])
+    oa, osa, ob, osb = O.quant_fpxint8(q, k)
+    assert torch.equal(sa.cpu(), osa) and torch.equal(sb.cpu(), osb)
+
+
+@pytest.mark.parametrize("shape,dtype,outliers", [
+    ((1, 2, 256, 128), torch.bfloat16, 5),
+    ((2, 3, 200, 128), torch.float16, 0),      # ragged: L not a multiple of 128
+    ((1, 1, 77, 64), torch.bfloat16, 3),       # D = 64, short
+    ((1, 2, 130, 256), torch.float32, 0),      # D = 256 (two scale-tile columns)
+])
+def test_kernel_format_matches_oracle(shape, dtype, outliers):
+    import mpsa
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(shape, generator=g)
+    if outliers:
+        x[..., torch.randperm(shape[-1], generator=g)[:outliers]] *= 20
+    x = x.to(dtype)
+    x[0, 0, 3, :32] = 0          # an all-zero block
+    s = O.q_side_scale(shape[-1])
+    r = mpsa.quantize_mx(x.cuda(), s, reference_format=True, kernel_format=True)
+    c4, s4 = O.quant_mxfp4_side(x, s)
+    c8, s8 = O.quant_mxfp8_side(x, s)
+    assert torch.equal(r.fp4_unpacked.cpu(), c4) and torch.equal(r.fp4_scales.cpu(), s4)
+    assert torch.equal(r.fp8.cpu(), c8) and torch.equal(r.fp8_scales.cpu(), s8)
+    assert torch.equal(r.fp4.cpu(), O.pack_e2m1(c4))
+    assert torch.equal(r.fp4_sf.cpu().reshape(O.swizzle_scales(s4).shape), O.swizzle_scales(s4))
+    assert torch.equal(r.fp8_sf.cpu().reshape(O.swizzle_scales(s8).shape), O.swizzle_scales(s8))
+    # E4M3 variant (no reference counterpart: checked against the oracle's restatement only)
+    r = mpsa.quantize_mx(x.cuda(), s, want_fp4=False, reference_format=True, kernel_format=False, fp8_elem="e4m3")
+    c8, s8 = O.quant_mxfp8_side(x, s, "e4m3")
+    assert torch.equal(r.fp8.cpu(), c8) and torch.equal(r.fp8_scales.cpu(), s8)
+
+
+def test_nhd_layout_and_strided_input():
+    from ours.quant_mxint8 import quant_mxfp4
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(2, 192, 4, 128, generator=g).to(torch.bfloat16)   # [B, L, H, D]
+    k = torch.randn(2, 192, 2, 128, generator=g).to(torch.bfloat16)
+    a, sa, b, sb = quant_mxfp4(q.cuda(), k.cuda(), tensor_layout="NHD")
+    assert a.shape == q.shape and sa.shape == (2, 4, 192, 4)
+    oa, osa, ob, osb = O.quant_mxfp4(q.transpose(1, 2), k.transpose(1, 2))
+    assert torch.equal(a.cpu().transpose(1, 2), oa) and torch.equal(sa.cpu(), osa)
+    assert torch.equal(b.cpu().transpose(1, 2), ob) and torch.equal(sb.cpu(), osb)
+    with pytest.raises(ValueError):
+        quant_mxfp4(q.cuda(), k.cuda(), tensor_layout="XYZ")
+
+
+def test_full_size_properties():
+    """Headline-size Q operand (32 heads x 32768 x 128): properties that need no oracle pass."""
+    import mpsa
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(1, 32, 32768, 128, generator=g, device="cuda").to(torch.bfloat16)
+    r = mpsa.quantize_mx(x, 1.0, reference_format=True, kernel_format=True)
+    # scale code == exponent of the block amax - emax + 127 (bf16 input: no rounding edge)
+    amax = x.float().abs().reshape(1, 32, 32768, 4, 32).amax(-1)
+    e = torch.floor(torch.log2(amax)).to(torch.int32)
+    assert torch.equal(r.fp4_scales.to(torch.int32), e - 3 + 127)
+    assert torch.equal(r.fp8_scales.to(torch.int32), e - 7 + 127)
+    # every block's largest element saturates to +-6 and no code is a NaN pattern
+    mag = (r.fp4_unpacked & 7).reshape(1, 32, 32768, 4, 32).amax(-1)
+    assert int(mag.min()) == 7
+    # packed nibbles reproduce the unpacked codes
+    lo, hi = r.fp4 & 0xF, r.fp4 >> 4
+    assert torch.equal(torch.stack((lo, hi), -1).flatten(-2), r.fp4_unpacked)
+    # dequantised fp8 is within half an E5M2 ulp (2^-3 relative) of the input
+    deq = r.fp8.view(torch.float8_e5m2).float() * torch.exp2(r.fp8_scales.float() - 127).repeat_interleave(32, -1)
+    err = (deq - x.float()).abs()
+    assert float((err / amax.repeat_interleave(32, -1)).max()) <= 2.0 ** -3
+    # a 2048-row slice against the oracle, bit exact
+    c4, s4 = O.quant_mxfp4_side(x[0, 7, 4096:6144].cpu(), 1.0)
+    assert torch.equal(r.fp4_unpacked[0, 7, 4096:6144].cpu(), c4) and torch.equal(r.fp4_scales[0, 7, 4096:6144].cpu(), s4)
