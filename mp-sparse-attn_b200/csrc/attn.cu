@@ -17,8 +17,13 @@
 //               2^8, which leaves the result O = sum(P.V) / sum(P) unchanged.
 //   O += P.V    tcgen05.mma kind::f16 with P read from TMEM and V^T (fp16, [D, keys]) from shared
 //               memory, fp32 accumulation in TMEM (:340 accumulates each tile in fp16 first).
-// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 4-7 softmax/correction/epilogue.  S is
-// double-buffered in TMEM so that Q.K^T of tile t+1 overlaps the softmax of tile t.
+// Roles: warp 0 TMA producer, warp 1 MMA issuer (warps 2-3 idle), warps 4.. softmax/correction/epilogue.  S is
+// double-buffered in TMEM so that Q.K^T of tile t+1 overlaps the softmax of tile t.  NWG softmax
+// warpgroups take the key tiles in turn (warpgroup w owns tiles t = w mod NWG), so that the
+// exponentials of one tile (MUFU) overlap the max / pack / TMEM traffic of the next; the running
+// row maximum is handed from the owner of tile t to the owner of tile t+1 through shared memory.
+// Inside a warpgroup the 128 keys of a tile can further be split over NSPLIT threads per query row,
+// which exchange partial row maxima.  Every thread keeps a partial row sum; the epilogue adds them.
 // TMEM columns: S0/P0 [0,128) S1/P1 [128,256) O [256,384) Q scales [384,392) K scales [392,400).
 #include "api_internal.h"
 #include "common.cuh"
@@ -26,6 +31,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cstdlib>
 
 namespace mpsa {
 
@@ -39,14 +45,32 @@ constexpr int ATT_OFF_Q4 = ATT_OFF_Q8 + ATT_Q8_BYTES;
 constexpr int ATT_OFF_K = ATT_OFF_Q4 + ATT_Q4_BYTES;
 constexpr int ATT_OFF_V = ATT_OFF_K + ATT_KSTAGES * ATT_K_BYTES;
 constexpr int ATT_OFF_SF = ATT_OFF_V + ATT_VSTAGES * ATT_V_BYTES;   // Q8, Q4, K[stages] scale tiles
-constexpr int ATT_OFF_BAR = ATT_OFF_SF + (2 + ATT_KSTAGES) * 512;
-constexpr int ATT_SMEM = ATT_OFF_BAR + 256 + 1024;
-constexpr int ATT_THREADS = 256;
+constexpr int ATT_MAX_SPLIT = 4, ATT_MAX_WG = 2;
+constexpr int ATT_OFF_XMAX = ATT_OFF_SF + (2 + ATT_KSTAGES) * 512;   // float [WG][2][SPLIT][128] partial row maxima
+constexpr int ATT_OFF_XSUM = ATT_OFF_XMAX + ATT_MAX_WG * 2 * ATT_MAX_SPLIT * 128 * 4;   // float [WG*SPLIT][128] partial sums
+constexpr int ATT_OFF_MROW = ATT_OFF_XSUM + ATT_MAX_WG * ATT_MAX_SPLIT * 128 * 4;       // float [3][128] running row max: per tile parity, and an unsynchronised hint
+constexpr int ATT_OFF_BAR = ATT_OFF_MROW + 3 * 128 * 4;
+constexpr int ATT_OFF_MAP = ATT_OFF_BAR + 512;                        // this CTA's row of the precision map
+constexpr int ATT_MAP_SMEM = 4096;                                    // rows longer than this stay in global memory
+constexpr int ATT_SMEM = ATT_OFF_MAP + ATT_MAP_SMEM + 1024;
 constexpr uint32_t ATT_TMEM_COLS = 512;
 constexpr uint32_t ATT_COL_S = 0, ATT_COL_O = 256, ATT_COL_SFQ8 = 384, ATT_COL_SFQ4 = 388, ATT_COL_SFK = 392;
 constexpr float ATT_RESCALE_LOG2 = 8.0f;
 
 constexpr int TILE_SKIP = 0, TILE_FP8 = 1, TILE_FP4 = 2;
+
+// Optional timeline recording (development builds only, -DMPSA_TRACE): clock64 stamps of one CTA.
+#ifdef MPSA_TRACE
+__device__ long long* g_trace = nullptr;             // [3 roles][64 tiles][8 events]
+#define TRACE_INIT() long long* trace_ptr = (blockIdx.x == 8 && blockIdx.y == 0 && blockIdx.z == 0) ? g_trace : nullptr
+#define TRACE(role, tile, ev)                                                                         \
+  do {                                                                                                \
+    if (trace_ptr && (tile) < 64) trace_ptr[((role) * 64 + (tile)) * 8 + (ev)] = clock64();           \
+  } while (0)
+#else
+#define TRACE_INIT() do {} while (0)
+#define TRACE(role, tile, ev) do {} while (0)
+#endif
 
 struct AttnParams {
   int B, Hq, Hkv, S, Skv, D;        // D = value head dim (64 or 128); Q/K depth is padded to 128
@@ -82,6 +106,14 @@ __device__ __forceinline__ void tmem_st32p(uint32_t taddr, const uint32_t* r) {
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st16p(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -93,7 +125,8 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   return r;
 }
 
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+template <int NWG, int NSPLIT>
+__global__ void __launch_bounds__(128 + 128 * NWG * NSPLIT, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant__ CUtensorMap tm_q4,
                 const __grid_constant__ CUtensorMap tm_k8, const __grid_constant__ CUtensorMap tm_k4,
                 const __grid_constant__ CUtensorMap tm_vt, const AttnParams p) {
@@ -109,21 +142,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   uint64_t* s_full = v_empty + ATT_VSTAGES;        // 2
   uint64_t* p_ready = s_full + 2;                  // 2
   uint64_t* pv_done = p_ready + 2;                 // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  uint64_t* x_bar = pv_done + 2;                   // [WG][2][4] partial-max exchange inside a warpgroup
+  uint64_t* m_bar = x_bar + ATT_MAX_WG * 8;        // [2][4] running-max hand-over, per tile parity and row quarter
+  uint64_t* l_bar = m_bar + 8;                     // [4] partial-sum exchange in the epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(l_bar + 4);
+  float* xmax = reinterpret_cast<float*>(smem + ATT_OFF_XMAX);
+  float* xsum = reinterpret_cast<float*>(smem + ATT_OFF_XSUM);
+  float* mrow = reinterpret_cast<float*>(smem + ATT_OFF_MROW);
 
+  TRACE_INIT();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.S + ATT_BM - 1) / ATT_BM, nk = (p.Skv + ATT_BN - 1) / ATT_BN;
   const int qi = nq - 1 - (int)blockIdx.x;          // heavy (late) causal rows first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
-  const uint8_t* map_row = p.map + (long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk;
+  const uint8_t* map_glob = p.map + (long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk;
+  // every role walks this row once per tile; keep it in shared memory when it fits
+  const uint8_t* map_row = (nk <= ATT_MAP_SMEM) ? (smem + ATT_OFF_MAP) : map_glob;
+  if (nk <= ATT_MAP_SMEM)
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) smem[ATT_OFF_MAP + i] = map_glob[i];
+  if (threadIdx.x < 128) reinterpret_cast<float*>(smem + ATT_OFF_MROW)[2 * 128 + threadIdx.x] = -INFINITY;   // reference hint
   const int off = p.Skv - p.S;                      // queries are aligned to the end of the keys
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < ATT_KSTAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
     for (int s = 0; s < ATT_VSTAGES; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 128); mbar_init(&pv_done[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 128 * NSPLIT); mbar_init(&pv_done[s], 1); }
+    for (int s = 0; s < ATT_MAX_WG * 8; ++s) mbar_init(&x_bar[s], NSPLIT);
+    for (int s = 0; s < 8; ++s) mbar_init(&m_bar[s], NSPLIT);
+    for (int s = 0; s < 4; ++s) mbar_init(&l_bar[s], NSPLIT * NWG);
     fence_mbar_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, ATT_TMEM_COLS);
@@ -202,155 +250,302 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
+    // Issue order: QK(0) QK(1) | PV(0) QK(2) | PV(1) QK(3) | ...  Everything that does not depend
+    // on the softmax of tile t (V and K arrival, descriptors) is settled before the wait for P(t),
+    // so that P.V(t) and Q.K^T(t+2) go out back to back once P(t) is there.
     if (lane == 0) {
-      const uint32_t idesc8 = idesc_block_scaled(p.fp8_fmt, p.fp8_fmt, ATT_BM, ATT_BN, 1);
-      const uint32_t idesc4 = idesc_block_scaled(1, 1, ATT_BM, ATT_BN, 1);
+      uint32_t id8[4], id4[2];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) id8[j] = idesc_with_sf_id(idesc_block_scaled(p.fp8_fmt, p.fp8_fmt, ATT_BM, ATT_BN, 1), j, j);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) id4[j] = idesc_with_sf_id(idesc_block_scaled(1, 1, ATT_BM, ATT_BN, 1), 2 * j, 2 * j);
       const uint32_t idesc_pv = idesc_f16(0, 0, ATT_BM, p.D);
       const uint64_t q8d = sdesc_kmajor_sw128(smem_u32(sQ8));
       const uint64_t q4d = sdesc_kmajor_sw64(smem_u32(sQ4));
+      const uint64_t k8d0 = sdesc_kmajor_sw128(smem_u32(sK));       // + stage * (ATT_K_BYTES >> 4)
+      const uint64_t k4d0 = sdesc_kmajor_sw64(smem_u32(sK));
+      const uint64_t vd0 = sdesc_kmajor_sw128(smem_u32(sV));        // + stage * (ATT_V_BYTES >> 4)
+      const uint64_t sfk0 = sdesc_sf_tile(smem_u32(sSF + 2 * 512)); // + stage * (512 >> 4)
+      const uint32_t v_half16 = (uint32_t)v_half_bytes >> 4;
+      constexpr int PW = 128 / NSPLIT;                              // keys per softmax column split
       bool ok = mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
       if (ok) {
         tc_fence_after();
         tc_cp_32x128b_warpx4(tmem + ATT_COL_SFQ8, sdesc_sf_tile(smem_u32(sSF)));
         tc_cp_32x128b_warpx4(tmem + ATT_COL_SFQ4, sdesc_sf_tile(smem_u32(sSF + 512)));
       }
-      int jq = 0;                                  // next key tile for Q.K^T
+      int jq = 0;                                  // scan position in the map row
       int tq = 0, tp = 0;                          // tiles issued: Q.K^T and P.V
-      auto issue_qk = [&]() {
+      int jn = -1;                                 // key-tile index of the next Q.K^T to issue (-1: none)
+      auto find_next = [&]() {
         while (jq < nk && map_row[jq] == TILE_SKIP) ++jq;
-        if (jq >= nk) return false;
+        jn = (jq < nk) ? jq++ : -1;
+      };
+      auto wait_k = [&]() {                        // K tile of Q.K^T number tq has landed
+        ok = mbar_wait(&k_full[tq % ATT_KSTAGES], (tq / ATT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
+      };
+      auto issue_qk = [&]() {                      // needs jn >= 0 and wait_k() done
         const int s = tq % ATT_KSTAGES;
-        ok = mbar_wait(&k_full[s], (tq / ATT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
-        if (!ok) return false;
+        const bool f8 = map_row[jn] == TILE_FP8;
+        TRACE(1, tq, 0);
         tc_fence_after();
-        const bool f8 = map_row[jq] == TILE_FP8;
         const uint32_t sfk = tmem + ATT_COL_SFK + (tq & 1) * 4;
-        tc_cp_32x128b_warpx4(sfk, sdesc_sf_tile(smem_u32(sSF + (2 + s) * 512)));
+        tc_cp_32x128b_warpx4(sfk, sfk0 + (uint64_t)(s * (512 >> 4)));
         const uint32_t d = tmem + ATT_COL_S + (tq & 1) * 128;
-        const uint32_t kaddr = smem_u32(sK + s * ATT_K_BYTES);
         if (f8) {
-          const uint64_t kd = sdesc_kmajor_sw128(kaddr);
+          const uint64_t kd = k8d0 + (uint64_t)(s * (ATT_K_BYTES >> 4));
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            mma_mxf8f6f4(d, q8d + 2 * j, kd + 2 * j, idesc_with_sf_id(idesc8, j, j), tmem + ATT_COL_SFQ8, sfk, j > 0);
+          for (int j = 0; j < 4; ++j) mma_mxf8f6f4(d, q8d + 2 * j, kd + 2 * j, id8[j], tmem + ATT_COL_SFQ8, sfk, j > 0);
         } else {
-          const uint64_t kd = sdesc_kmajor_sw64(kaddr);
+          const uint64_t kd = k4d0 + (uint64_t)(s * (ATT_K_BYTES >> 4));
 #pragma unroll
-          for (int j = 0; j < 2; ++j)
-            mma_mxf4(d, q4d + 2 * j, kd + 2 * j, idesc_with_sf_id(idesc4, 2 * j, 2 * j), tmem + ATT_COL_SFQ4, sfk, j > 0);
+          for (int j = 0; j < 2; ++j) mma_mxf4(d, q4d + 2 * j, kd + 2 * j, id4[j], tmem + ATT_COL_SFQ4, sfk, j > 0);
         }
         tc_commit(&k_empty[s]);
         tc_commit(&s_full[tq & 1]);
-        ++tq; ++jq;
-        return true;
+        TRACE(1, tq, 1);
+        ++tq;
       };
-      bool more = ok && issue_qk();
+      if (ok) {
+        find_next();
+        if (jn >= 0) { wait_k(); if (ok) issue_qk(); }
+        if (ok && tq == 1) {
+          find_next();
+          if (jn >= 0) { wait_k(); if (ok) issue_qk(); }
+        }
+        if (ok) find_next();
+      }
       while (ok && tp < tq) {
-        if (more) more = issue_qk();
-        if (!ok) break;
-        // P.V of tile tp
         const int bsel = tp & 1, s = tp % ATT_VSTAGES;
+        ok = mbar_wait(&v_full[s], (tp / ATT_VSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
+        if (ok && jn >= 0) wait_k();
+        if (!ok) break;
+        TRACE(1, tp, 2);
         ok = mbar_wait(&p_ready[bsel], (tp >> 1) & 1, p.status, KS_TIMEOUT_PIPE);
         if (!ok) break;
-        ok = mbar_wait(&v_full[s], (tp / ATT_VSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
-        if (!ok) break;
+        TRACE(1, tp, 3);
         tc_fence_after();
-        const uint32_t ptm = tmem + ATT_COL_S + bsel * 128;     // P: 64 columns of packed fp16
-        const uint32_t vaddr = smem_u32(sV + s * ATT_V_BYTES);
+        const uint32_t ptm = tmem + ATT_COL_S + bsel * 128;     // P: packed fp16, see the softmax role
+        const uint64_t vd = vd0 + (uint64_t)(s * (ATT_V_BYTES >> 4));
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t vd = sdesc_kmajor_sw128(vaddr + (ks >> 2) * v_half_bytes) + 2 * (ks & 3);
-          mma_f16_ts(tmem + ATT_COL_O, ptm + ks * 8, vd, idesc_pv, (tp > 0 || ks > 0) ? 1u : 0u);
+          const uint32_t pcol = ((ks * 16) / PW) * PW + ((ks * 16) % PW) / 2;
+          mma_f16_ts(tmem + ATT_COL_O, ptm + pcol, vd + (uint64_t)((ks >> 2) * v_half16 + 2 * (ks & 3)), idesc_pv,
+                     (tp > 0 || ks > 0) ? 1u : 0u);
         }
         tc_commit(&v_empty[s]);
         tc_commit(&pv_done[bsel]);
+        TRACE(1, tp, 4);
         ++tp;
+        if (jn >= 0) {
+          issue_qk();
+          find_next();
+        }
       }
     }
   } else if (warp >= 4) {
     // ------------------------------ softmax / correction / epilogue -----------
-    const int q = warp & 3;
+    // Per tile and thread: ONE pass over the S slice computes P = exp2(S - m) with the row reference
+    // m known so far, the slice maximum and the partial row sum; P stays in registers.  Afterwards
+    // the row maximum is assembled (partial maxima of the column splits), the reference decided by
+    // the previous tile's owner is taken over, and only if the reference has to move (the maximum
+    // grew by more than 2^8, or another warpgroup moved it meanwhile; always on the first tile) the
+    // tile is redone from S, which is still intact in TMEM.  P is written over S only then.
+    constexpr int W = 128 / NSPLIT;                 // keys of a tile owned by this thread
+    constexpr int NCH = W / 32;                     // 32-column chunks of the slice
+    const int sw = warp - 4;                        // warps 0-3 are the service warpgroup
+    const int q = warp & 3;                         // TMEM lane quarter this warp may access
+    const int g = (sw >> 2) % NSPLIT;               // column split owned by this warp
+    const int wg = (sw >> 2) / NSPLIT;              // warpgroup: owns tiles t with t % NWG == wg
+    const int part = wg * NSPLIT + g;               // index among the threads that share a row
     const int r_in = q * 32 + lane;                 // row inside the tile == TMEM lane
     const int m_glob = qi * ATT_BM + r_in;
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-    float m_used = -INFINITY, l_run = 0.0f;
+    const bool tracer = (q == 0 && g == 0 && lane == 0);
+    [[maybe_unused]] const int trole = (wg == 0) ? 2 : 0;
+    float* mhint = mrow + 2 * 128;
+    float m_seen = -INFINITY;                       // row reference this thread's partial sum refers to
+    float l_run = 0.0f;                             // partial row sum over this thread's tiles / columns
     bool ok = true;
-    int t = 0;
+    int t = 0;                                      // index among the non-skipped tiles
     for (int j = 0; j < nk && ok; ++j) {
       if (map_row[j] == TILE_SKIP) continue;
-      const int bsel = t & 1;
+      if (t % NWG != wg) { ++t; continue; }
+      const int bsel = t & 1, lt = t / NWG;         // S buffer; count of tiles this warpgroup has done
+      if (tracer) TRACE(trole, t, 0);
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[bsel], (t >> 1) & 1, p.status, KS_TIMEOUT_MMA));
       if (!ok) break;
+      if (tracer) TRACE(trole, t, 1);
       tc_fence_after();
-      const uint32_t s_addr = tmem + lane_base + ATT_COL_S + bsel * 128;
-      uint32_t sr[128];
+      const uint32_t slice_addr = tmem + lane_base + ATT_COL_S + bsel * 128 + g * W;
+      const int n0 = j * ATT_BN + g * W;            // first key of this thread's slice
+      const bool need_mask = (p.causal && (j * ATT_BN + ATT_BN - 1 > qi * ATT_BM + off)) || (j * ATT_BN + ATT_BN > p.Skv);
+      const int lim = p.causal ? min(p.Skv - 1, m_glob + off) : (p.Skv - 1);   // last visible key
+      // all chunk loads go out up front when the slice and its packed P fit in the register budget
+      constexpr int REG_BUDGET = ((16384 / 32) / (1 + NWG * NSPLIT)) >= 255 ? 255 : (((16384 / 32) / (1 + NWG * NSPLIT)) & ~7);
+      constexpr bool ALL_UP = (W + W / 2 + 40 <= REG_BUDGET);
+      uint32_t sr[ALL_UP ? W : 32];
+      uint32_t pk[W / 2];
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      float lsum0 = 0.0f, lsum1 = 0.0f;
+      // reference to start with: this thread's own on one warpgroup, else the latest published hint
+      const float m0 = (t == 0) ? -INFINITY : ((NWG > 1) ? mhint[r_in] : m_seen);
+      const float mref0 = (m0 == -INFINITY) ? 0.0f : m0;
+      // ---- the pass ----
+      if (ALL_UP) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32p(s_addr + c * 32, sr + c * 32);
-      tmem_ld_wait();
-      const int n0 = j * ATT_BN;
-      const bool need_mask = (p.causal && (n0 + ATT_BN - 1 > qi * ATT_BM + off)) || (n0 + ATT_BN > p.Skv);
-      float mx = -INFINITY;
-      if (need_mask) {
-        const int lim = p.causal ? min(p.Skv - 1, m_glob + off) : (p.Skv - 1);   // last visible key
-#pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          float v = (n0 + c <= lim) ? __uint_as_float(sr[c]) : -INFINITY;
-          sr[c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
+        for (int c = 0; c < NCH; ++c) tmem_ld32p(slice_addr + c * 32, sr + c * 32);
       } else {
-#pragma unroll
-        for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+        tmem_ld32p(slice_addr, sr);
       }
-      // running max with deferred rescale of the accumulator
-      const float m_new = fmaxf(m_used, mx);
-      const bool grow = (t > 0) && (m_new > m_used + ATT_RESCALE_LOG2);
-      if (t == 0) {
-        m_used = m_new;
-      } else if (__any_sync(0xffffffffu, grow)) {
-        // the accumulator must be quiescent: P.V of the previous tile finished
-        ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1, p.status, KS_TIMEOUT_MMA));
-        if (!ok) break;
-        tc_fence_after();
-        const float alpha = grow ? ex2(m_used - m_new) : 1.0f;
-        if (grow) { m_used = m_new; l_run *= alpha; }
-        for (int c = 0; c < p.D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32p(tmem + lane_base + ATT_COL_O + c * 32, o);
-          tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32p(tmem + lane_base + ATT_COL_O + c * 32, o);
+      for (int c = 0; c < NCH; ++c) {
+        uint32_t* sc = ALL_UP ? (sr + c * 32) : sr;
+        if (!ALL_UP || c == 0) tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (n0 + c * 32 + i > lim) sc[i] = 0xff800000u;      // -inf
         }
-        tmem_st_wait();
-      }
-      const float mref = (m_used == -INFINITY) ? 0.0f : m_used;   // row with no visible key so far
-      float lsum = 0.0f;
-      uint32_t pk[64];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const float p0 = ex2(__uint_as_float(sr[2 * c]) - mref);
-        const float p1 = ex2(__uint_as_float(sr[2 * c + 1]) - mref);
-        lsum += p0 + p1;
-        pk[c] = pack_f16x2(p0, p1);
+        for (int i = 0; i < 32; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sc[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(sc[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sc[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(sc[i + 3]));
+        }
+        if (t > 0) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = ex2(__uint_as_float(sc[2 * i]) - mref0);
+            const float p1 = ex2(__uint_as_float(sc[2 * i + 1]) - mref0);
+            lsum0 += p0;
+            lsum1 += p1;
+            pk[c * 16 + i] = pack_f16x2(p0, p1);
+          }
+        }
+        if (!ALL_UP && c + 1 < NCH) tmem_ld32p(slice_addr + (c + 1) * 32, sr);
       }
-      l_run += lsum;
-      tmem_st32p(s_addr, pk);
-      tmem_st32p(s_addr + 32, pk + 32);
+      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      if (tracer) TRACE(trole, t, 2);
+      if (NSPLIT > 1) {
+        // full-row maximum = max over the NSPLIT partial maxima of this row
+        float* xm = xmax + ((wg * 2 + (lt & 1)) * ATT_MAX_SPLIT) * 128;
+        xm[g * 128 + r_in] = mx;
+        __syncwarp();
+        uint64_t* xb = &x_bar[(wg * 2 + (lt & 1)) * 4 + q];
+        if (lane == 0) mbar_arrive(xb);
+        ok = __all_sync(0xffffffffu, mbar_wait(xb, (lt >> 1) & 1, p.status, KS_TIMEOUT_PIPE));
+        if (!ok) break;
+#pragma unroll
+        for (int gg = 0; gg < NSPLIT; ++gg) mx = fmaxf(mx, xm[gg * 128 + r_in]);
+      }
+      // ---- reference decided by the owner of the previous tile ----
+      float m1 = m_seen;
+      if (NWG > 1 && t > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&m_bar[((t - 1) & 1) * 4 + q], ((t - 1) >> 1) & 1, p.status, KS_TIMEOUT_PIPE));
+        if (!ok) break;
+        m1 = mrow[((t - 1) & 1) * 128 + r_in];
+      }
+      if (tracer) TRACE(trole, t, 3);
+      // the reference moves only when the maximum grew by more than 2^8 (every thread of a row takes
+      // the same decision: it sees the same maximum and the same previous reference)
+      const bool grow = (t == 0) || (mx > m1 + ATT_RESCALE_LOG2);
+      const float m_used = grow ? fmaxf(m1, mx) : m1;
+      if (m_seen != m_used) {                       // bring this thread's partial sum to the reference
+        l_run = (m_seen == -INFINITY) ? 0.0f : l_run * ex2(m_seen - m_used);
+        m_seen = m_used;
+      }
+      if (NWG > 1) {                                // publish the decision; the next tile's owner waits for it
+        if (g == 0) { mrow[(t & 1) * 128 + r_in] = m_used; mhint[r_in] = m_used; }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&m_bar[(t & 1) * 4 + q]);
+      }
+      const bool redo = (t == 0) || (m_used != m0);  // P of the pass used another reference (or none)
+      if (__any_sync(0xffffffffu, redo)) {
+        if (t > 0 && __any_sync(0xffffffffu, grow)) {
+          // rescale the accumulator; it must be quiescent: P.V of the previous tile finished
+          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1, p.status, KS_TIMEOUT_MMA));
+          if (!ok) break;
+          tc_fence_after();
+          const float alpha = grow ? ex2(m1 - m_used) : 1.0f;
+          for (int c = g; c < p.D / 32; c += NSPLIT) {          // this split's share of the O columns
+            uint32_t o[32];
+            tmem_ld32p(tmem + lane_base + ATT_COL_O + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32p(tmem + lane_base + ATT_COL_O + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+        // redo the pass from S with the final reference
+        const float mref = (m_used == -INFINITY) ? 0.0f : m_used;   // row with no visible key so far
+        lsum0 = 0.0f;
+        lsum1 = 0.0f;
+        tmem_ld32p(slice_addr, sr);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          tmem_ld_wait();
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (n0 + c * 32 + i > lim) sr[i] = 0xff800000u;
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = ex2(__uint_as_float(sr[2 * i]) - mref);
+            const float p1 = ex2(__uint_as_float(sr[2 * i + 1]) - mref);
+            lsum0 += p0;
+            lsum1 += p1;
+            pk[c * 16 + i] = pack_f16x2(p0, p1);
+          }
+          if (c + 1 < NCH) tmem_ld32p(slice_addr + (c + 1) * 32, sr);
+        }
+      }
+      l_run += lsum0 + lsum1;
+      if (tracer) TRACE(trole, t, 4);
+      // P (two fp16 per column) overwrites S inside this thread's own slice: key k of the tile sits
+      // in column (k / W) * W + (k % W) / 2
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) tmem_st16p(slice_addr + c * 16, pk + c * 16);
+      if (tracer) TRACE(trole, t, 5);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_ready[bsel]);
+      if (tracer) TRACE(trole, t, 6);
       ++t;
     }
-    // epilogue: O / l
+    // ---- epilogue: bring every partial sum to the final reference, add them, O / l ----
+    float l_tot = l_run;
+    if (NWG * NSPLIT > 1 && ok) {
+      if (NWG > 1 && t > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&m_bar[((t - 1) & 1) * 4 + q], ((t - 1) >> 1) & 1, p.status, KS_TIMEOUT_PIPE));
+        if (ok) {
+          const float m_fin = mrow[((t - 1) & 1) * 128 + r_in];
+          if (m_fin != m_seen) l_run = (m_seen == -INFINITY) ? 0.0f : l_run * ex2(m_seen - m_fin);
+        }
+      }
+      if (ok) {
+        xsum[part * 128 + r_in] = l_run;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&l_bar[q]);
+        ok = __all_sync(0xffffffffu, mbar_wait(&l_bar[q], 0, p.status, KS_TIMEOUT_PIPE));
+      }
+      if (ok) {
+        l_tot = 0.0f;
+#pragma unroll
+        for (int gg = 0; gg < NWG * NSPLIT; ++gg) l_tot += xsum[gg * 128 + r_in];
+      }
+    }
     if (ok && t > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1, p.status, KS_TIMEOUT_MMA));
       tc_fence_after();
     }
     if (ok) {
-      const float inv_l = (t > 0 && l_run > 0.0f) ? 1.0f / l_run : 0.0f;
+      const float inv_l = (t > 0 && l_tot > 0.0f) ? 1.0f / l_tot : 0.0f;
       const long long o_off = ((long long)(b * p.Hq + h) * p.S + m_glob) * p.D;
-      for (int c = 0; c < p.D / 32; ++c) {
+      for (int c = part; c < p.D / 32; c += NWG * NSPLIT) {
         uint32_t o[32];
         if (t > 0) {
           tmem_ld32p(tmem + lane_base + ATT_COL_O + c * 32, o);
@@ -432,6 +627,12 @@ __global__ void route_band_kernel(uint8_t* map, int nq, int nk, int T, int causa
 
 using namespace mpsa;
 
+#ifdef MPSA_TRACE
+extern "C" int mpsa_debug_set_trace(void* buf) {
+  return cudaMemcpyToSymbol(g_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -3;
+}
+#endif
+
 extern "C" int mpsa_route_band(void* map, int nq, int nk, int tile, int causal, int band, int S, int Skv, void* stream) {
   if (!map || nq <= 0 || nk <= 0 || tile <= 0 || band < 0) return set_error(MPSA_ERR_BAD_ARG, "route_band: bad argument");
   if (nq > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "route_band: more than 65535 query tiles");
@@ -486,15 +687,34 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   p.k8_sf = (const uint8_t*)k8_sf; p.k4_sf = (const uint8_t*)k4_sf;
   p.map = (const uint8_t*)map; p.map_sb = map_sb; p.map_sh = map_sh;
   p.out = out; p.out_dtype = out_dtype; p.status = status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess)
-      return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
-    attr_set = true;
+  // Softmax organisation: warpgroups taking tiles in turn (1 or 2) x threads per query row inside a
+  // warpgroup (1, 2 or 4).  MPSA_ATTN_WG / MPSA_ATTN_SPLIT override the default.
+  static int cfg = 0;
+  if (cfg == 0) {
+    const char* e1 = getenv("MPSA_ATTN_WG");
+    const char* e2 = getenv("MPSA_ATTN_SPLIT");
+    int nwg = e1 ? atoi(e1) : 2, ns = e2 ? atoi(e2) : 1;
+    if (nwg != 1 && nwg != 2) nwg = 2;
+    if (ns != 1 && ns != 2 && ns != 4) ns = 1;
+    if (nwg == 2 && ns == 4) ns = 2;
+    cudaError_t e = cudaSuccess;
+#define MPSA_SET_SMEM(A, B) \
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    MPSA_SET_SMEM(1, 1) MPSA_SET_SMEM(1, 2) MPSA_SET_SMEM(1, 4) MPSA_SET_SMEM(2, 1) MPSA_SET_SMEM(2, 2)
+#undef MPSA_SET_SMEM
+    if (e != cudaSuccess) return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
+    cfg = nwg * 10 + ns;
   }
   const int nq = (S + ATT_BM - 1) / ATT_BM;
   if (Hq > 65535 || B > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: Hq and B must be below 65536");
   dim3 grid(nq, Hq, B);
-  attn_fwd_kernel<<<grid, ATT_THREADS, ATT_SMEM, (cudaStream_t)stream>>>(tq8, tq4, tk8, tk4, tvt, p);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (cfg) {
+    case 11: attn_fwd_kernel<1, 1><<<grid, 256, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, p); break;
+    case 12: attn_fwd_kernel<1, 2><<<grid, 384, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, p); break;
+    case 14: attn_fwd_kernel<1, 4><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, p); break;
+    case 21: attn_fwd_kernel<2, 1><<<grid, 384, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, p); break;
+    default: attn_fwd_kernel<2, 2><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, p); break;
+  }
   return check_launch("attn_fwd");
 }

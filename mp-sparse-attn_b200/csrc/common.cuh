@@ -7,6 +7,10 @@
 #include <cuda_runtime.h>
 #include <cuda.h>
 
+#ifndef MPSA_WAIT_MODE
+#define MPSA_WAIT_MODE 0
+#endif
+
 namespace mpsa {
 
 // ---- status word written by kernels -----------------------------------------------------
@@ -19,12 +23,6 @@ enum KernelStatus : int {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
 }
 
 // ---- mbarrier ---------------------------------------------------------------------------
@@ -41,11 +39,17 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
+// One probe of the barrier phase (the hardware may hold the thread for a short, implementation
+// defined time before answering).
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
+#if MPSA_WAIT_MODE == 1
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 0x989680;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
@@ -53,21 +57,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wait limit for any single barrier phase.  Kernels here finish a phase in microseconds; two
-// seconds means something upstream never arrived.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// Wait limit for any single barrier phase, in SM clock cycles (about two seconds at 2 GHz).
+// Kernels here finish a phase in microseconds; hitting the limit means something upstream never
+// arrived.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 
 // Bounded wait.  Returns false when the limit expired (and records `code` in *status) or when
 // another role already recorded a failure, so that every role unwinds promptly.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = globaltimer_ns();
+#if MPSA_WAIT_MODE == 0
+  // Reading the global nanosecond timer is slow; doing it once after the first unsuccessful probe
+  // doubles as a back-off that keeps a waiting warp out of its scheduler's way.
+  {
+    unsigned long long g0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g0));
+    (void)g0;
+  }
+#endif
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+#if MPSA_WAIT_MODE == 2
+    __nanosleep(40);
+#endif
     if ((++spins & 0x3ff) == 0) {
       if (*(volatile int*)status != KS_OK) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (clock64() - t0 > kWaitLimitCycles) {
         atomicCAS(status, KS_OK, code);
         return false;
       }

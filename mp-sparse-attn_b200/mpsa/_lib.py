@@ -8,7 +8,7 @@ import os
 import sys
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libmpsa.so")
+_LIB_PATH = os.environ.get("MPSA_LIB") or os.path.join(_HERE, "libmpsa.so")   # MPSA_LIB: use another build
 _lib = None
 
 c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
