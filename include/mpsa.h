@@ -59,6 +59,26 @@ int mpsa_quant_int8(const void* x, int in_dtype, int B, int H, int L, int D, lon
 int mpsa_prepare_vt(const void* v, int in_dtype, void* vt, int B, int H, int Skv, int D, int Skv_pad,
                     long long vs_b, long long vs_h, long long vs_l, void* stream);
 
+/* NVFP4 quantizer of a 2-D operand [rows, cols] (row pitch ld elements) along its columns: 16-element
+ * blocks, E4M3 block scales, one fp32 tensor scale: ts = amax/(6*448), block scale = e4m3(amax_blk/(6*ts)),
+ * element = e2m1_rne(x/(scale*ts)).  The reference has the GEMM mode only (ours/block_scaled_matmul.py:321-324),
+ * no quantizer.  codes [rows, cols/2] (pitch ldc_bytes), scales [ceil(rows/128), cols/64, 512] (128x4 tiles of
+ * E4M3 bytes), tensor_scale: one float.  `scratch` holds one partial amax per 128x512 input tile:
+ * mpsa_quant_nvfp4_scratch_floats(rows, cols) floats; it needs no initialisation. */
+int mpsa_quant_nvfp4_scratch_floats(int rows, int cols);
+int mpsa_quant_nvfp4(const void* x, int in_dtype, int rows, int cols, long long ld, float s, void* scratch,
+                     long long scratch_floats, void* codes, long long ldc_bytes, void* scales, void* tensor_scale,
+                     void* stream);
+
+/* V operand of a quantised P.V: 32-key MX blocks along the SEQUENCE axis, transposed.  V [B,H,Skv,D]
+ * (strided) -> vt8 [B,H,D,Skv_pad] MXFP8 codes and/or vt4 [B,H,D,Skv_pad/2] MXFP4 codes (two per byte),
+ * scale tiles v8_sf / v4_sf [B,H,Skv_pad/128,512] (rows = head-dim index, columns = the four 32-key
+ * blocks of a 128-key tile).  Round-to-nearest-even elements (OCP MX rule).  No counterpart in the
+ * reference, which keeps V in fp16 (ours/mxfp_attn_kernel.py:29-31).  fp8_fmt: 1 E5M2, 2 E4M3. */
+int mpsa_quant_v_seq(const void* v, int in_dtype, int B, int H, int Skv, int D, int Skv_pad, long long vs_b,
+                     long long vs_h, long long vs_l, int fp8_fmt, void* vt8, void* v8_sf, void* vt4, void* v4_sf,
+                     void* stream);
+
 /* Band-rule precision map uint8 [nq, nk] over tile x tile cells: FP8 iff the cell is within
  * `band` tiles of the (end-aligned) diagonal, else FP4; causal cells entirely above the diagonal
  * are SKIP.  The reference has no per-tile precision selection; the causal tile range follows
@@ -69,7 +89,8 @@ int mpsa_route_band(void* map, int nq, int nk, int tile, int causal, int band, i
  * and its kernel (:103-359).
  *   q8/q4, k8/k4   codes from mpsa_quant_mx with D padded to 128: fp8 [B,H,L,128], fp4 packed [B,H,L,64]
  *   *_sf           tiled scales [B,H,ceil(L/128),512]
- *   vt             from mpsa_prepare_vt
+ *   pv_mode 0      P and V in fp16 (the reference's P.V precision): vt from mpsa_prepare_vt
+ *   pv_mode 1      P re-quantised to the tile's format, V from mpsa_quant_v_seq (vt8, v8_sf, vt4, v4_sf)
  *   map            uint8 [.., ceil(S/128), ceil(Skv/128)] with batch / head strides map_sb / map_sh (0 = shared)
  *   out            [B,Hq,S,D] contiguous
  *   fp8_fmt        descriptor format of the fp8 codes: 0 E4M3, 1 E5M2
@@ -77,7 +98,8 @@ int mpsa_route_band(void* map, int nq, int nk, int tile, int causal, int band, i
  *                  non-zero code here (1 TMA, 2 MMA, 3 pipeline) and unwinds
  */
 int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
-                  const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* map,
+                  const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* vt8,
+                  const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
                   long long map_sb, long long map_sh, void* out, int out_dtype, int B, int Hq, int Hkv, int S,
                   int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int* status, void* stream);
 

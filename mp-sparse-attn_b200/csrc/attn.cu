@@ -15,8 +15,12 @@
 //               max / sum (ours/mxfp_attn_kernel.py:320-328), writes P as fp16 back into TMEM over S
 //               (:339).  The accumulator is rescaled only when the running max grows by more than
 //               2^8, which leaves the result O = sum(P.V) / sum(P) unchanged.
-//   O += P.V    tcgen05.mma kind::f16 with P read from TMEM and V^T (fp16, [D, keys]) from shared
-//               memory, fp32 accumulation in TMEM (:340 accumulates each tile in fp16 first).
+//   O += P.V    pv_mode 0 (the reference's precision): tcgen05.mma kind::f16 with P (fp16) read from
+//               TMEM and V^T (fp16, [D, keys]) from shared memory, fp32 accumulation in TMEM (:340
+//               accumulates each tile in fp16 first).  pv_mode 1: P is re-quantised to the tile's
+//               format (MXFP8 or MXFP4, one E8M0 scale per 32 keys, written by the softmax threads)
+//               and multiplied with V quantised along the sequence, as block-scaled MMAs with P in
+//               TMEM; the row reference is kept integral so that the codes do not depend on it.
 // Roles: warp 0 TMA producer, warp 1 MMA issuer (warps 2-3 idle), warps 4.. softmax/correction/epilogue.  S is
 // double-buffered in TMEM so that Q.K^T of tile t+1 overlaps the softmax of tile t.  NWG softmax
 // warpgroups take the key tiles in turn (warpgroup w owns tiles t = w mod NWG), so that the
@@ -24,7 +28,8 @@
 // row maximum is handed from the owner of tile t to the owner of tile t+1 through shared memory.
 // Inside a warpgroup the 128 keys of a tile can further be split over NSPLIT threads per query row,
 // which exchange partial row maxima.  Every thread keeps a partial row sum; the epilogue adds them.
-// TMEM columns: S0/P0 [0,128) S1/P1 [128,256) O [256,384) Q scales [384,392) K scales [392,400).
+// TMEM columns: S0/P0 [0,128) S1/P1 [128,256) O [256,384) Q scales [384,392) K scales [392,400)
+// P scales [400,408) V scales [408,416).
 #include "api_internal.h"
 #include "common.cuh"
 #include "tma_host.h"
@@ -46,7 +51,8 @@ constexpr int ATT_OFF_K = ATT_OFF_Q4 + ATT_Q4_BYTES;
 constexpr int ATT_OFF_V = ATT_OFF_K + ATT_KSTAGES * ATT_K_BYTES;
 constexpr int ATT_OFF_SF = ATT_OFF_V + ATT_VSTAGES * ATT_V_BYTES;   // Q8, Q4, K[stages] scale tiles
 constexpr int ATT_MAX_SPLIT = 4, ATT_MAX_WG = 2;
-constexpr int ATT_OFF_XMAX = ATT_OFF_SF + (2 + ATT_KSTAGES) * 512;   // float [WG][2][SPLIT][128] partial row maxima
+constexpr int ATT_OFF_PSF = ATT_OFF_SF + (2 + ATT_KSTAGES) * 512;    // P scale tiles [2], V scale tiles [VSTAGES]
+constexpr int ATT_OFF_XMAX = ATT_OFF_PSF + (2 + ATT_VSTAGES) * 512;   // float [WG][2][SPLIT][128] partial row maxima
 constexpr int ATT_OFF_XSUM = ATT_OFF_XMAX + ATT_MAX_WG * 2 * ATT_MAX_SPLIT * 128 * 4;   // float [WG*SPLIT][128] partial sums
 constexpr int ATT_OFF_MROW = ATT_OFF_XSUM + ATT_MAX_WG * ATT_MAX_SPLIT * 128 * 4;       // float [3][128] running row max: per tile parity, and an unsynchronised hint
 constexpr int ATT_OFF_BAR = ATT_OFF_MROW + 3 * 128 * 4;
@@ -55,6 +61,7 @@ constexpr int ATT_MAP_SMEM = 4096;                                    // rows lo
 constexpr int ATT_SMEM = ATT_OFF_MAP + ATT_MAP_SMEM + 1024;
 constexpr uint32_t ATT_TMEM_COLS = 512;
 constexpr uint32_t ATT_COL_S = 0, ATT_COL_O = 256, ATT_COL_SFQ8 = 384, ATT_COL_SFQ4 = 388, ATT_COL_SFK = 392;
+constexpr uint32_t ATT_COL_SFP = 400, ATT_COL_SFV = 408;
 constexpr float ATT_RESCALE_LOG2 = 8.0f;
 
 constexpr int TILE_SKIP = 0, TILE_FP8 = 1, TILE_FP4 = 2;
@@ -78,6 +85,8 @@ struct AttnParams {
   int fp8_fmt;                       // descriptor format field: 0 E4M3, 1 E5M2
   const uint8_t* q8_sf; const uint8_t* q4_sf;   // [B,Hq,nq,512]
   const uint8_t* k8_sf; const uint8_t* k4_sf;   // [B,Hkv,nk,512]
+  const uint8_t* v8_sf; const uint8_t* v4_sf;   // [B,Hkv,nk,512] (pv_mode 1)
+  int pv_mode;                       // 0: P and V in fp16; 1: P and V in the tile's MX format
   const uint8_t* map; long long map_sb, map_sh; // [.., nq, nk], strides may be 0 (broadcast)
   void* out; int out_dtype;          // [B,Hq,S,D] contiguous; 0 f32, 1 f16, 2 bf16
   int* status;
@@ -124,12 +133,127 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+__device__ __forceinline__ void tmem_st8p(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st4p(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3])
+               : "memory");
+}
+// Block-scaled MMAs with the A operand (P) in TMEM.
+__device__ __forceinline__ void mma_mxf8f6f4_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t sfa,
+                                                uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], [%1], %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_mxf4_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t sfa,
+                                            uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], [%1], %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+// 8 floats -> 8 E2M1 codes (round to nearest even, saturating), element 0 in the low nibble.
+__device__ __forceinline__ uint32_t pack_e2m1x8(float y0, float y1, float y2, float y3, float y4, float y5, float y6,
+                                                float y7) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(r)
+      : "f"(y0), "f"(y1), "f"(y2), "f"(y3), "f"(y4), "f"(y5), "f"(y6), "f"(y7));
+  return r;
+}
+// 4 floats -> 4 fp8 codes (E5M2 or E4M3, round to nearest even, saturating), element 0 in the low byte.
+template <bool E4M3>
+__device__ __forceinline__ uint32_t pack_fp8x4(float y0, float y1, float y2, float y3) {
+  uint32_t r;
+  if (E4M3) {
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+        "mov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r) : "f"(y0), "f"(y1), "f"(y2), "f"(y3));
+  } else {
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "cvt.rn.satfinite.e5m2x2.f32 lo, %2, %1;\n\t"
+        "cvt.rn.satfinite.e5m2x2.f32 hi, %4, %3;\n\t"
+        "mov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r) : "f"(y0), "f"(y1), "f"(y2), "f"(y3));
+  }
+  return r;
+}
 
-template <int NWG, int NSPLIT>
+// One 32-key block of one query row: P = exp2(S - m) in the precision the P.V product uses.
+//   PMODE 0: fp16 pairs (16 words).  PMODE 1/2: MXFP8 E5M2/E4M3 (8 words), PMODE 3: MXFP4 (4 words), with the
+//   block's E8M0 scale code returned: shared exponent floor(log2(amax P)) - emax = floor(bmax - m) - emax,
+//   folded into the exponent so that exp2 delivers P / scale directly (power-of-two scaling is exact).
+//   `lsum` accumulates the unrounded P (the reference sums P before rounding it, ours/mxfp_attn_kernel.py:325).
+template <int PMODE>
+__device__ __forceinline__ uint32_t softmax_block(const uint32_t* sc, float mref, float bmax, uint32_t* pk,
+                                                  float& lsum0, float& lsum1) {
+  if (PMODE == 0) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float p0 = ex2(__uint_as_float(sc[2 * i]) - mref);
+      const float p1 = ex2(__uint_as_float(sc[2 * i + 1]) - mref);
+      lsum0 += p0;
+      lsum1 += p1;
+      pk[i] = pack_f16x2(p0, p1);
+    }
+    return 0;
+  } else {
+    constexpr int EMAX = (PMODE == 3) ? 2 : ((PMODE == 2) ? 8 : 7);
+    if (bmax == -INFINITY) {                      // nothing visible in this block
+      constexpr int NW = (PMODE == 3) ? 4 : 8;
+#pragma unroll
+      for (int i = 0; i < NW; ++i) pk[i] = 0;
+      return 0;
+    }
+    int sh = (int)floorf(bmax - mref) - EMAX;
+    sh = max(sh, -126);
+    const float cb = mref + (float)sh;            // exact: mref is integral in this mode
+    float y[32];
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      y[i] = ex2(__uint_as_float(sc[i]) - cb);
+      y[i + 1] = ex2(__uint_as_float(sc[i + 1]) - cb);
+      a0 += y[i];
+      a1 += y[i + 1];
+    }
+    const float two_sh = __uint_as_float((uint32_t)(sh + 127) << 23);
+    lsum0 = fmaf(a0, two_sh, lsum0);
+    lsum1 = fmaf(a1, two_sh, lsum1);
+    if (PMODE == 3) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        pk[i] = pack_e2m1x8(y[8 * i], y[8 * i + 1], y[8 * i + 2], y[8 * i + 3], y[8 * i + 4], y[8 * i + 5], y[8 * i + 6], y[8 * i + 7]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) pk[i] = pack_fp8x4<PMODE == 2>(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]);
+    }
+    return (uint32_t)(sh + 127);
+  }
+}
+
+
+template <int NWG, int NSPLIT, int PVQ>
 __global__ void __launch_bounds__(128 + 128 * NWG * NSPLIT, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant__ CUtensorMap tm_q4,
                 const __grid_constant__ CUtensorMap tm_k8, const __grid_constant__ CUtensorMap tm_k4,
-                const __grid_constant__ CUtensorMap tm_vt, const AttnParams p) {
+                const __grid_constant__ CUtensorMap tm_vt, const __grid_constant__ CUtensorMap tm_vt8,
+                const __grid_constant__ CUtensorMap tm_vt4, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024 - (raw & 1023)) & 1023);
@@ -185,13 +309,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   uint8_t* sK = smem + ATT_OFF_K;
   uint8_t* sV = smem + ATT_OFF_V;
   uint8_t* sSF = smem + ATT_OFF_SF;                 // [0] Q8, [1] Q4, [2+s] K stage s
+  uint8_t* sPSF = smem + ATT_OFF_PSF;               // [0..1] P scale tiles per S buffer, [2+s] V stage s
   const int v_half_bytes = p.D * 128;               // one 64-key half of a V^T tile
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_q4); tma_prefetch_desc(&tm_k8);
-      tma_prefetch_desc(&tm_k4); tma_prefetch_desc(&tm_vt);
+      tma_prefetch_desc(&tm_k4); tma_prefetch_desc(&tm_vt); tma_prefetch_desc(&tm_vt8); tma_prefetch_desc(&tm_vt4);
       const int q_row = (b * p.Hq + h) * p.S + qi * ATT_BM;
       const long long qsf = ((long long)(b * p.Hq + h) * nq + qi) * 512;
       mbar_arrive_expect_tx(q_full, ATT_Q8_BYTES + ATT_Q4_BYTES + 1024);
@@ -225,9 +350,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         const int s = tv % ATT_VSTAGES;
         if (tv >= ATT_VSTAGES) ok = mbar_wait(&v_empty[s], ((tv / ATT_VSTAGES) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
         if (!ok) return false;
-        mbar_arrive_expect_tx(&v_full[s], 2 * v_half_bytes);
-        tma_load_2d(sV + s * ATT_V_BYTES, &tm_vt, &v_full[s], jv * ATT_BN, v_row);
-        tma_load_2d(sV + s * ATT_V_BYTES + v_half_bytes, &tm_vt, &v_full[s], jv * ATT_BN + 64, v_row);
+        if (PVQ == 0) {
+          mbar_arrive_expect_tx(&v_full[s], 2 * v_half_bytes);
+          tma_load_2d(sV + s * ATT_V_BYTES, &tm_vt, &v_full[s], jv * ATT_BN, v_row);
+          tma_load_2d(sV + s * ATT_V_BYTES + v_half_bytes, &tm_vt, &v_full[s], jv * ATT_BN + 64, v_row);
+        } else {
+          // V^T tile in the tile's format: D rows of 128 (MXFP8) or 64 (MXFP4) bytes, and its scale tile
+          const bool f8 = map_row[jv] == TILE_FP8;
+          mbar_arrive_expect_tx(&v_full[s], (f8 ? v_half_bytes : v_half_bytes / 2) + 512);
+          tma_load_2d(sV + s * ATT_V_BYTES, f8 ? &tm_vt8 : &tm_vt4, &v_full[s], f8 ? jv * ATT_BN : jv * (ATT_BN / 2), v_row);
+          bulk_load(sPSF + (2 + s) * 512, (f8 ? p.v8_sf : p.v4_sf) + ksf0 + (long long)jv * 512, 512, &v_full[s]);
+        }
         ++tv; ++jv;
         return true;
       };
@@ -267,6 +400,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       const uint64_t vd0 = sdesc_kmajor_sw128(smem_u32(sV));        // + stage * (ATT_V_BYTES >> 4)
       const uint64_t sfk0 = sdesc_sf_tile(smem_u32(sSF + 2 * 512)); // + stage * (512 >> 4)
       const uint32_t v_half16 = (uint32_t)v_half_bytes >> 4;
+      const uint64_t v4d0 = sdesc_kmajor_sw64(smem_u32(sV));        // MXFP4 V^T tile (64-byte rows)
+      const uint64_t sfp0 = sdesc_sf_tile(smem_u32(sPSF));          // P scale tiles [2], then V scale tiles per stage
+      uint32_t idp8[4], idp4[2];                                    // P.V block-scaled: M=128, N=D
+#pragma unroll
+      for (int j = 0; j < 4; ++j) idp8[j] = idesc_with_sf_id(idesc_block_scaled(p.fp8_fmt, p.fp8_fmt, ATT_BM, p.D, 1), j, j);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) idp4[j] = idesc_with_sf_id(idesc_block_scaled(1, 1, ATT_BM, p.D, 1), 2 * j, 2 * j);
+      uint32_t fmt_ring = 0;                                        // bit (t & 3): tile t is an FP8 tile
       constexpr int PW = 128 / NSPLIT;                              // keys per softmax column split
       bool ok = mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
       if (ok) {
@@ -287,6 +428,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       auto issue_qk = [&]() {                      // needs jn >= 0 and wait_k() done
         const int s = tq % ATT_KSTAGES;
         const bool f8 = map_row[jn] == TILE_FP8;
+        fmt_ring = (fmt_ring & ~(1u << (tq & 3))) | ((f8 ? 1u : 0u) << (tq & 3));
         TRACE(1, tq, 0);
         tc_fence_after();
         const uint32_t sfk = tmem + ATT_COL_SFK + (tq & 1) * 4;
@@ -325,13 +467,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         if (!ok) break;
         TRACE(1, tp, 3);
         tc_fence_after();
-        const uint32_t ptm = tmem + ATT_COL_S + bsel * 128;     // P: packed fp16, see the softmax role
-        const uint64_t vd = vd0 + (uint64_t)(s * (ATT_V_BYTES >> 4));
+        const uint32_t ptm = tmem + ATT_COL_S + bsel * 128;     // P, see the softmax role for its columns
+        const uint32_t acc0 = tp > 0 ? 1u : 0u;
+        if (PVQ == 0) {
+          const uint64_t vd = vd0 + (uint64_t)(s * (ATT_V_BYTES >> 4));
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t pcol = ((ks * 16) / PW) * PW + ((ks * 16) % PW) / 2;
-          mma_f16_ts(tmem + ATT_COL_O, ptm + pcol, vd + (uint64_t)((ks >> 2) * v_half16 + 2 * (ks & 3)), idesc_pv,
-                     (tp > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t pcol = ((ks * 16) / PW) * PW + ((ks * 16) % PW) / 2;
+            mma_f16_ts(tmem + ATT_COL_O, ptm + pcol, vd + (uint64_t)((ks >> 2) * v_half16 + 2 * (ks & 3)), idesc_pv,
+                       ks > 0 ? 1u : acc0);
+          }
+        } else {
+          const uint32_t sfp = tmem + ATT_COL_SFP + bsel * 4, sfv = tmem + ATT_COL_SFV + (tp & 1) * 4;
+          tc_cp_32x128b_warpx4(sfp, sfp0 + (uint64_t)(bsel * (512 >> 4)));
+          tc_cp_32x128b_warpx4(sfv, sfp0 + (uint64_t)((2 + s) * (512 >> 4)));
+          if ((fmt_ring >> (tp & 3)) & 1) {
+            const uint64_t vd = vd0 + (uint64_t)(s * (ATT_V_BYTES >> 4));
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {                     // 32 keys per instruction, 8 TMEM columns of P
+              const uint32_t pcol = ((ks * 32) / PW) * PW + ((ks * 32) % PW) / 4;
+              mma_mxf8f6f4_ts(tmem + ATT_COL_O, ptm + pcol, vd + 2 * ks, idp8[ks], sfp, sfv, ks > 0 ? 1u : acc0);
+            }
+          } else {
+            const uint64_t vd = v4d0 + (uint64_t)(s * (ATT_V_BYTES >> 4));
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {                     // 64 keys per instruction, 8 TMEM columns of P
+              const uint32_t pcol = ((ks * 64) / PW) * PW + ((ks * 64) % PW) / 8;
+              mma_mxf4_ts(tmem + ATT_COL_O, ptm + pcol, vd + 2 * ks, idp4[ks], sfp, sfv, ks > 0 ? 1u : acc0);
+            }
+          }
         }
         tc_commit(&v_empty[s]);
         tc_commit(&pv_done[bsel]);
@@ -386,8 +550,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       constexpr bool ALL_UP = (W + W / 2 + 40 <= REG_BUDGET);
       uint32_t sr[ALL_UP ? W : 32];
       uint32_t pk[W / 2];
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      float mx0 = -INFINITY;
       float lsum0 = 0.0f, lsum1 = 0.0f;
+      uint32_t psc = 0;                             // E8M0 codes of this thread's P blocks (pv_mode 1)
+      // precision of P for this tile: 0 fp16; 1 MXFP8 E5M2; 2 MXFP8 E4M3; 3 MXFP4
+      const int pmode = (PVQ == 0) ? 0 : ((map_row[j] == TILE_FP8) ? (p.fp8_fmt == 0 ? 2 : 1) : 3);
       // reference to start with: this thread's own on one warpgroup, else the latest published hint
       const float m0 = (t == 0) ? -INFINITY : ((NWG > 1) ? mhint[r_in] : m_seen);
       const float mref0 = (m0 == -INFINITY) ? 0.0f : m0;
@@ -407,26 +574,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
           for (int i = 0; i < 32; ++i)
             if (n0 + c * 32 + i > lim) sc[i] = 0xff800000u;      // -inf
         }
+        float b0 = -INFINITY, b1 = -INFINITY, b2 = -INFINITY, b3 = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(sc[i]));
-          mx1 = fmaxf(mx1, __uint_as_float(sc[i + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(sc[i + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(sc[i + 3]));
+          b0 = fmaxf(b0, __uint_as_float(sc[i]));
+          b1 = fmaxf(b1, __uint_as_float(sc[i + 1]));
+          b2 = fmaxf(b2, __uint_as_float(sc[i + 2]));
+          b3 = fmaxf(b3, __uint_as_float(sc[i + 3]));
         }
+        const float bm = fmaxf(fmaxf(b0, b1), fmaxf(b2, b3));       // maximum of this 32-key block
+        mx0 = fmaxf(mx0, bm);
         if (t > 0) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float p0 = ex2(__uint_as_float(sc[2 * i]) - mref0);
-            const float p1 = ex2(__uint_as_float(sc[2 * i + 1]) - mref0);
-            lsum0 += p0;
-            lsum1 += p1;
-            pk[c * 16 + i] = pack_f16x2(p0, p1);
-          }
+          uint32_t code = 0;
+          if (pmode == 0) code = softmax_block<0>(sc, mref0, bm, pk + c * 16, lsum0, lsum1);
+          else if (pmode == 3) code = softmax_block<3>(sc, mref0, bm, pk + c * 4, lsum0, lsum1);
+          else if (pmode == 1) code = softmax_block<1>(sc, mref0, bm, pk + c * 8, lsum0, lsum1);
+          else code = softmax_block<2>(sc, mref0, bm, pk + c * 8, lsum0, lsum1);
+          psc |= code << (8 * c);
         }
         if (!ALL_UP && c + 1 < NCH) tmem_ld32p(slice_addr + (c + 1) * 32, sr);
       }
-      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      float mx = mx0;
       if (tracer) TRACE(trole, t, 2);
       if (NSPLIT > 1) {
         // full-row maximum = max over the NSPLIT partial maxima of this row
@@ -451,7 +619,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       // the reference moves only when the maximum grew by more than 2^8 (every thread of a row takes
       // the same decision: it sees the same maximum and the same previous reference)
       const bool grow = (t == 0) || (mx > m1 + ATT_RESCALE_LOG2);
-      const float m_used = grow ? fmaxf(m1, mx) : m1;
+      // with quantised P the reference is kept integral: a power-of-two change of P then changes block
+      // scale codes only, never element codes
+      const float m_used = grow ? (PVQ ? ceilf(fmaxf(m1, mx)) : fmaxf(m1, mx)) : m1;
       if (m_seen != m_used) {                       // bring this thread's partial sum to the reference
         l_run = (m_seen == -INFINITY) ? 0.0f : l_run * ex2(m_seen - m_used);
         m_seen = m_used;
@@ -483,6 +653,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         const float mref = (m_used == -INFINITY) ? 0.0f : m_used;   // row with no visible key so far
         lsum0 = 0.0f;
         lsum1 = 0.0f;
+        psc = 0;
         tmem_ld32p(slice_addr, sr);
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
@@ -492,23 +663,47 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
             for (int i = 0; i < 32; ++i)
               if (n0 + c * 32 + i > lim) sr[i] = 0xff800000u;
           }
+          float b0 = -INFINITY, b1 = -INFINITY, b2 = -INFINITY, b3 = -INFINITY;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float p0 = ex2(__uint_as_float(sr[2 * i]) - mref);
-            const float p1 = ex2(__uint_as_float(sr[2 * i + 1]) - mref);
-            lsum0 += p0;
-            lsum1 += p1;
-            pk[c * 16 + i] = pack_f16x2(p0, p1);
+          for (int i = 0; i < 32; i += 4) {
+            b0 = fmaxf(b0, __uint_as_float(sr[i]));
+            b1 = fmaxf(b1, __uint_as_float(sr[i + 1]));
+            b2 = fmaxf(b2, __uint_as_float(sr[i + 2]));
+            b3 = fmaxf(b3, __uint_as_float(sr[i + 3]));
           }
+          const float bm = fmaxf(fmaxf(b0, b1), fmaxf(b2, b3));
+          uint32_t code = 0;
+          if (pmode == 0) code = softmax_block<0>(sr, mref, bm, pk + c * 16, lsum0, lsum1);
+          else if (pmode == 3) code = softmax_block<3>(sr, mref, bm, pk + c * 4, lsum0, lsum1);
+          else if (pmode == 1) code = softmax_block<1>(sr, mref, bm, pk + c * 8, lsum0, lsum1);
+          else code = softmax_block<2>(sr, mref, bm, pk + c * 8, lsum0, lsum1);
+          psc |= code << (8 * c);
           if (c + 1 < NCH) tmem_ld32p(slice_addr + (c + 1) * 32, sr);
         }
       }
       l_run += lsum0 + lsum1;
       if (tracer) TRACE(trole, t, 4);
-      // P (two fp16 per column) overwrites S inside this thread's own slice: key k of the tile sits
-      // in column (k / W) * W + (k % W) / 2
+      // P overwrites S inside this thread's own slice: key k of the tile sits in column
+      // (k / W) * W + (k % W) / e with e = 2 (fp16), 4 (MXFP8) or 8 (MXFP4) elements per 32-bit column
+      if (pmode == 0) {
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) tmem_st16p(slice_addr + c * 16, pk + c * 16);
+        for (int c = 0; c < NCH; ++c) tmem_st16p(slice_addr + c * 16, pk + c * 16);
+      } else {
+        if (pmode == 3) {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) tmem_st4p(slice_addr + c * 4, pk + c * 4);
+        } else {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) tmem_st8p(slice_addr + c * 8, pk + c * 8);
+        }
+        // this row's block scales go into the 128x4 scale tile of the S buffer, which the MMA warp
+        // copies to TMEM: row r, block k at byte (r % 32) * 16 + (r / 32) * 4 + k
+        uint8_t* dst = sPSF + bsel * 512 + lane * 16 + q * 4 + g * NCH;
+        if (NCH == 4) *reinterpret_cast<uint32_t*>(dst) = psc;
+        else if (NCH == 2) *reinterpret_cast<uint16_t*>(dst) = (uint16_t)psc;
+        else *dst = (uint8_t)psc;
+        fence_proxy_async_smem();                   // make the tile visible to tcgen05.cp
+      }
       if (tracer) TRACE(trole, t, 5);
       tmem_st_wait();
       tc_fence_before();
@@ -656,35 +851,51 @@ extern "C" int mpsa_prepare_vt(const void* v, int in_dtype, void* vt, int B, int
 }
 
 extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
-                             const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* map,
+                             const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* vt8,
+                             const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
                              long long map_sb, long long map_sh, void* out, int out_dtype, int B, int Hq, int Hkv,
                              int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int* status, void* stream) {
-  if (!q8 || !q8_sf || !q4 || !q4_sf || !k8 || !k8_sf || !k4 || !k4_sf || !vt || !map || !out || !status)
+  if (!q8 || !q8_sf || !q4 || !q4_sf || !k8 || !k8_sf || !k4 || !k4_sf || !map || !out || !status)
     return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: null pointer");
+  if (pv_mode != 0 && pv_mode != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: pv_mode must be 0 (fp16 P.V) or 1 (quantised P.V)");
+  if (pv_mode == 0 && !vt) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: pv_mode 0 needs vt");
+  if (pv_mode == 1 && (!vt8 || !v8_sf || !vt4 || !v4_sf)) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: pv_mode 1 needs vt8, v8_sf, vt4, v4_sf");
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || Skv <= 0) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: non-positive shape");
   if (Hq % Hkv) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: Hq must be a multiple of Hkv");
   if (D != 64 && D != 128) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: head_dim must be 64 or 128");
   if (out_dtype < 0 || out_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: out_dtype must be 0 (f32), 1 (f16) or 2 (bf16)");
   if (fp8_fmt != 0 && fp8_fmt != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: fp8_fmt must be 0 (E4M3) or 1 (E5M2)");
   if (causal && Skv < S) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: causal needs Skv >= S");
-  if (Skv_pad < Skv || Skv_pad % 8) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: Skv_pad must be >= Skv and a multiple of 8");
-  const void* ptrs[] = {q8, q8_sf, q4, q4_sf, k8, k8_sf, k4, k4_sf, vt, out};
+  if (Skv_pad < Skv || Skv_pad % 128) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: Skv_pad must be Skv rounded up to 128");
+  const void* ptrs[] = {q8, q8_sf, q4, q4_sf, k8, k8_sf, k4, k4_sf, vt, vt8, v8_sf, vt4, v4_sf, out};
   for (const void* ptr : ptrs)
     if ((uintptr_t)ptr % 16) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: every tensor base must be 16-byte aligned");
   if ((long long)B * Hq * S >= (1ll << 31) || (long long)B * Hkv * Skv >= (1ll << 31))
     return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: B*H*S must fit in 31 bits");
-  CUtensorMap tq8, tq4, tk8, tk4, tvt;
+  CUtensorMap tq8, tq4, tk8, tk4, tvt, tvt8, tvt4;
   const uint64_t qrows = (uint64_t)B * Hq * S, krows = (uint64_t)B * Hkv * Skv;
   if (make_tmap_2d_bytes(&tq8, q8, ATT_DQK, qrows, ATT_DQK, 128, ATT_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
       make_tmap_2d_bytes(&tq4, q4, ATT_DQK / 2, qrows, ATT_DQK / 2, 64, ATT_BM, CU_TENSOR_MAP_SWIZZLE_64B) ||
       make_tmap_2d_bytes(&tk8, k8, ATT_DQK, krows, ATT_DQK, 128, ATT_BN, CU_TENSOR_MAP_SWIZZLE_128B) ||
       make_tmap_2d_bytes(&tk4, k4, ATT_DQK / 2, krows, ATT_DQK / 2, 64, ATT_BN, CU_TENSOR_MAP_SWIZZLE_64B) ||
-      make_tmap_2d_b16(&tvt, vt, Skv_pad, (uint64_t)B * Hkv * D, (uint64_t)Skv_pad * 2, 64, D, CU_TENSOR_MAP_SWIZZLE_128B))
+      false)
     return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled failed");
+  const uint64_t vrows = (uint64_t)B * Hkv * D;
+  if (pv_mode == 0) {
+    if (make_tmap_2d_b16(&tvt, vt, Skv_pad, vrows, (uint64_t)Skv_pad * 2, 64, D, CU_TENSOR_MAP_SWIZZLE_128B))
+      return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled failed");
+    tvt8 = tvt; tvt4 = tvt;      // not dereferenced in this mode
+  } else {
+    if (make_tmap_2d_bytes(&tvt8, vt8, Skv_pad, vrows, Skv_pad, 128, D, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        make_tmap_2d_bytes(&tvt4, vt4, Skv_pad / 2, vrows, Skv_pad / 2, 64, D, CU_TENSOR_MAP_SWIZZLE_64B))
+      return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled failed");
+    tvt = tvt8;                  // not dereferenced in this mode
+  }
   AttnParams p;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S = S; p.Skv = Skv; p.D = D; p.causal = causal; p.fp8_fmt = fp8_fmt;
   p.q8_sf = (const uint8_t*)q8_sf; p.q4_sf = (const uint8_t*)q4_sf;
   p.k8_sf = (const uint8_t*)k8_sf; p.k4_sf = (const uint8_t*)k4_sf;
+  p.v8_sf = (const uint8_t*)v8_sf; p.v4_sf = (const uint8_t*)v4_sf; p.pv_mode = pv_mode;
   p.map = (const uint8_t*)map; p.map_sb = map_sb; p.map_sh = map_sh;
   p.out = out; p.out_dtype = out_dtype; p.status = status;
   // Softmax organisation: warpgroups taking tiles in turn (1 or 2) x threads per query row inside a
@@ -699,7 +910,8 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
     if (nwg == 2 && ns == 4) ns = 2;
     cudaError_t e = cudaSuccess;
 #define MPSA_SET_SMEM(A, B) \
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM); \
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
     MPSA_SET_SMEM(1, 1) MPSA_SET_SMEM(1, 2) MPSA_SET_SMEM(1, 4) MPSA_SET_SMEM(2, 1) MPSA_SET_SMEM(2, 2)
 #undef MPSA_SET_SMEM
     if (e != cudaSuccess) return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
@@ -709,12 +921,20 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   if (Hq > 65535 || B > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: Hq and B must be below 65536");
   dim3 grid(nq, Hq, B);
   cudaStream_t st = (cudaStream_t)stream;
+  if (pv_mode == 1 && cfg % 10 == 4)
+    return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: quantised P.V needs at most 2 softmax threads per query row");
+#define MPSA_LAUNCH(A, B, T)                                                                              \
+  do {                                                                                                    \
+    if (pv_mode == 0) attn_fwd_kernel<A, B, 0><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p); \
+    else attn_fwd_kernel<A, B, 1><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);         \
+  } while (0)
   switch (cfg) {
-    case 11: attn_fwd_kernel<1, 1><<<grid, 256, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, p); break;
-    case 12: attn_fwd_kernel<1, 2><<<grid, 384, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, p); break;
-    case 14: attn_fwd_kernel<1, 4><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, p); break;
-    case 21: attn_fwd_kernel<2, 1><<<grid, 384, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, p); break;
-    default: attn_fwd_kernel<2, 2><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, p); break;
+    case 11: MPSA_LAUNCH(1, 1, 256); break;
+    case 12: MPSA_LAUNCH(1, 2, 384); break;
+    case 14: MPSA_LAUNCH(1, 4, 640); break;
+    case 21: MPSA_LAUNCH(2, 1, 384); break;
+    default: MPSA_LAUNCH(2, 2, 640); break;
   }
+#undef MPSA_LAUNCH
   return check_launch("attn_fwd");
 }

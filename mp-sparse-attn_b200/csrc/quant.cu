@@ -246,6 +246,198 @@ __global__ void __launch_bounds__(kQuantThreads) quant_i8_kernel(const QuantI8Pa
   }
 }
 
+
+// ---- V operand of P.V: 32-key blocks along the SEQUENCE axis, transposed output -------------------
+// V [B,H,Skv,D] -> V^T codes [B,H,D,Skv_pad] (MXFP8) and/or [B,H,D,Skv_pad/2] (MXFP4 packed), scale tiles
+// [B,H,ceil(Skv/128),512] with rows = head-dim index and columns = the four 32-key blocks of a
+// 128-key tile.  Elements are rounded to nearest even (OCP MX rule: shared exponent
+// floor(log2(amax)) - emax, emax = 2 for E2M1; the fp8 rule is the same as in quant_mx_kernel).
+// The reference has no such quantizer: it keeps V in fp16 (ours/mxfp_attn_kernel.py:29-31).
+struct QuantVParams {
+  const void* v; int B, H, Skv, D, Skv_pad;
+  long long vs_b, vs_h, vs_l;
+  int fp8_fmt;
+  uint8_t* vt8; uint8_t* vt4; uint8_t* sf8; uint8_t* sf4;
+};
+
+__device__ __forceinline__ uint32_t cvt_e2m1x8(const float* y) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(r)
+      : "f"(y[0]), "f"(y[1]), "f"(y[2]), "f"(y[3]), "f"(y[4]), "f"(y[5]), "f"(y[6]), "f"(y[7]));
+  return r;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) quant_v_seq_kernel(const QuantVParams p) {
+  __shared__ float tile[64][129];                  // [key][d] half tile, padded against bank conflicts
+  __shared__ __align__(16) uint8_t s8[512];
+  __shared__ __align__(16) uint8_t s4[512];
+  const int kt = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int tid = threadIdx.x;
+  reinterpret_cast<uint16_t*>(s8)[tid] = 0x7f7f;
+  reinterpret_cast<uint16_t*>(s4)[tid] = 0x7f7f;
+  const T* src = reinterpret_cast<const T*>(p.v) + (long long)b * p.vs_b + (long long)h * p.vs_h;
+  for (int half = 0; half < 2; ++half) {
+    const int key0 = kt * 128 + half * 64;
+    __syncthreads();
+    for (int i = tid; i < 64 * p.D; i += 256) {
+      const int kl = i / p.D, d = i % p.D;
+      tile[kl][d] = (key0 + kl < p.Skv) ? (float)src[(long long)(key0 + kl) * p.vs_l + d] : 0.0f;
+    }
+    __syncthreads();
+    // one unit = (head-dim index d, 32-key block)
+    for (int u = tid; u < p.D * 2; u += 256) {
+      const int d = u % p.D, bl = u / p.D, blk = half * 2 + bl;
+      float v[32], amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        v[i] = tile[bl * 32 + i][d];
+        amax = fmaxf(amax, fabsf(v[i]));
+      }
+      const long long row = ((long long)bh * p.D + d);
+      const int sf_off = (d & 31) * 16 + (d >> 5) * 4 + blk;
+      if (p.vt8) {
+        BlockScale bs = mx_block_scale(amax, p.fp8_fmt == FMT_FP8_E4M3 ? 8 : 7);
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t c[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) c[e] = bs.zero ? 0u : fp8_code(v[4 * j + e] * bs.inv_scale, p.fp8_fmt);
+          w[j] = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+        }
+        uint4* o = reinterpret_cast<uint4*>(p.vt8 + row * p.Skv_pad + key0 + bl * 32);
+        o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        s8[sf_off] = bs.code;
+      }
+      if (p.vt4) {
+        BlockScale bs = mx_block_scale(amax, 2);
+        float y[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) y[i] = bs.zero ? 0.0f : v[i] * bs.inv_scale;
+        uint4 o4 = make_uint4(cvt_e2m1x8(y), cvt_e2m1x8(y + 8), cvt_e2m1x8(y + 16), cvt_e2m1x8(y + 24));
+        *reinterpret_cast<uint4*>(p.vt4 + row * (p.Skv_pad >> 1) + ((key0 + bl * 32) >> 1)) = o4;
+        s4[sf_off] = bs.code;
+      }
+    }
+  }
+  __syncthreads();
+  const long long nkt = p.Skv_pad >> 7;
+  const long long tile_lin = (long long)bh * nkt + kt;
+  if (tid < 32) {
+    if (p.sf8) reinterpret_cast<uint4*>(p.sf8 + tile_lin * 512)[tid] = reinterpret_cast<uint4*>(s8)[tid];
+  } else if (tid < 64) {
+    if (p.sf4) reinterpret_cast<uint4*>(p.sf4 + tile_lin * 512)[tid - 32] = reinterpret_cast<uint4*>(s4)[tid - 32];
+  }
+}
+
+
+// ---- NVFP4: 16-element blocks, E4M3 block scales, one fp32 tensor scale ------------------------------
+// The reference only has the GEMM mode string for this format (ours/block_scaled_matmul.py:321-324), no
+// quantizer.  Definition used here: ts = amax(tensor) / (6 * 448); block scale = e4m3_rne(amax(block) /
+// (6 * ts)); element = e2m1_rne(x / (scale * ts)).  Two launches: stage 1 leaves one partial amax per CTA
+// in a scratch array (no atomics, nothing to zero), stage 2 reduces the partials and quantises.
+struct QuantNvParams {
+  const void* x; int rows, cols; long long ld; float s;
+  float* scratch; int n_partials;
+  uint8_t* codes; long long ldc_bytes;      // [rows, cols/2]
+  uint8_t* scales;                          // [ceil(rows/128), cols/64, 512] E4M3 bytes
+  float* tensor_scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kQuantThreads) nvfp4_amax_kernel(const QuantNvParams p) {
+  __shared__ float red[kQuantThreads / 32];
+  const int tid = threadIdx.x;
+  const T* xb = reinterpret_cast<const T*>(p.x);
+  float amax = 0.0f;
+  // CTA tile: 128 rows x 512 columns, 16 elements per step and thread
+  for (int i = tid; i < 128 * 32; i += kQuantThreads) {
+    const int r = blockIdx.x * 128 + (i >> 5), c = blockIdx.y * 512 + (i & 31) * 16;
+    if (r < p.rows && c < p.cols) {
+      float v[16];
+      load16<T>(xb + (long long)r * p.ld + c, v);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(__fmul_rn(v[j], p.s)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((tid & 31) == 0) red[tid >> 5] = amax;
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < kQuantThreads / 32; ++w) amax = fmaxf(amax, red[w]);
+    p.scratch[blockIdx.y * gridDim.x + blockIdx.x] = amax;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kQuantThreads) nvfp4_quant_kernel(const QuantNvParams p) {
+  __shared__ __align__(16) uint8_t sf[2][512];
+  __shared__ float red[kQuantThreads / 32];
+  __shared__ float ts_s;
+  const int tid = threadIdx.x;
+  // tensor amax = max of the partials
+  float amax = 0.0f;
+  for (int i = tid; i < p.n_partials; i += kQuantThreads) amax = fmaxf(amax, p.scratch[i]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((tid & 31) == 0) red[tid >> 5] = amax;
+  reinterpret_cast<uint32_t*>(&sf[0][0])[tid] = 0;   // 1024 bytes: padding rows carry scale 0
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < kQuantThreads / 32; ++w) amax = fmaxf(amax, red[w]);
+    float ts = __fdiv_rn(amax, 2688.0f);              // 6 * 448
+    if (ts == 0.0f) ts = 1.0f;
+    ts_s = ts;
+    if (blockIdx.x == 0 && blockIdx.y == 0) *p.tensor_scale = ts;
+  }
+  __syncthreads();
+  const float ts = ts_s;
+  const float denom = __fmul_rn(6.0f, ts);
+  const T* xb = reinterpret_cast<const T*>(p.x);
+  const int row0 = blockIdx.x * 128, col0 = blockIdx.y * 128;
+#pragma unroll
+  for (int i = 0; i < kRunsPerThread; ++i) {
+    const int g = tid + i * kQuantThreads;          // 16-element block index inside the 128x128 tile
+    const int rl = g >> 3, r = row0 + rl, c = col0 + (g & 7) * 16;
+    if (r >= p.rows || c >= p.cols) continue;
+    float v[16], bmax = 0.0f;
+    load16<T>(xb + (long long)r * p.ld + c, v);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      v[j] = __fmul_rn(v[j], p.s);
+      bmax = fmaxf(bmax, fabsf(v[j]));
+    }
+    const float ratio = fminf(__fdiv_rn(bmax, denom), 448.0f);
+    const __nv_fp8_storage_t s8 = __nv_cvt_float_to_fp8(ratio, __NV_SATFINITE, __NV_E4M3);
+    const float sdec = __half2float(__half(__nv_cvt_fp8_to_halfraw(s8, __NV_E4M3)));
+    const float scf = __fmul_rn(sdec, ts);
+    float y[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) y[j] = (scf == 0.0f) ? 0.0f : __fdiv_rn(v[j], scf);
+    *reinterpret_cast<uint2*>(p.codes + (long long)r * p.ldc_bytes + (c >> 1)) = make_uint2(cvt_e2m1x8(y), cvt_e2m1x8(y + 8));
+    const int blk = (g & 7);                        // block inside the tile: chunk blk / 4, column blk % 4
+    sf[blk >> 2][(rl & 31) * 16 + (rl >> 5) * 4 + (blk & 3)] = (uint8_t)s8;
+  }
+  __syncthreads();
+  const long long nchunks = p.cols >> 6;
+  if (tid < 64) {
+    const int ch = tid >> 5;
+    const long long chunk = (long long)blockIdx.y * 2 + ch;
+    if (chunk < nchunks)
+      reinterpret_cast<uint4*>(p.scales + ((long long)blockIdx.x * nchunks + chunk) * 512)[tid & 31] =
+          reinterpret_cast<uint4*>(sf[ch])[tid & 31];
+  }
+}
+
 }  // namespace mpsa
 
 using namespace mpsa;
@@ -308,4 +500,64 @@ extern "C" int mpsa_quant_int8(const void* x, int in_dtype, int B, int H, int L,
   else if (in_dtype == 1) quant_i8_kernel<__half><<<grid, kQuantThreads, 0, st>>>(p);
   else quant_i8_kernel<float><<<grid, kQuantThreads, 0, st>>>(p);
   return check_launch("quant_int8");
+}
+
+extern "C" int mpsa_quant_v_seq(const void* v, int in_dtype, int B, int H, int Skv, int D, int Skv_pad, long long vs_b,
+                                long long vs_h, long long vs_l, int fp8_fmt, void* vt8, void* v8_sf, void* vt4,
+                                void* v4_sf, void* stream) {
+  if (!v || B <= 0 || H <= 0 || Skv <= 0) return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: null input or non-positive shape");
+  if (D != 64 && D != 128) return set_error(MPSA_ERR_UNSUPPORTED, "quant_v_seq: head_dim must be 64 or 128");
+  if (Skv_pad < Skv || Skv_pad % 128) return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: Skv_pad must be Skv rounded up to 128");
+  if (in_dtype < 0 || in_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: bad in_dtype");
+  if (fp8_fmt != FMT_FP8_E5M2 && fp8_fmt != FMT_FP8_E4M3) return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: fp8_fmt must be 1 (E5M2) or 2 (E4M3)");
+  if ((vt8 && !v8_sf) || (vt4 && !v4_sf) || (!vt8 && !vt4)) return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: codes and scales go together");
+  if (((uintptr_t)vt8 | (uintptr_t)vt4 | (uintptr_t)v8_sf | (uintptr_t)v4_sf) % 16)
+    return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: outputs must be 16-byte aligned");
+  if (B * H > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "quant_v_seq: B*H must be below 65536");
+  QuantVParams p;
+  p.v = v; p.B = B; p.H = H; p.Skv = Skv; p.D = D; p.Skv_pad = Skv_pad; p.vs_b = vs_b; p.vs_h = vs_h; p.vs_l = vs_l;
+  p.fp8_fmt = fp8_fmt; p.vt8 = (uint8_t*)vt8; p.vt4 = (uint8_t*)vt4; p.sf8 = (uint8_t*)v8_sf; p.sf4 = (uint8_t*)v4_sf;
+  dim3 grid(Skv_pad / 128, B * H);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (in_dtype == 0) quant_v_seq_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  else if (in_dtype == 1) quant_v_seq_kernel<__half><<<grid, 256, 0, st>>>(p);
+  else quant_v_seq_kernel<float><<<grid, 256, 0, st>>>(p);
+  return check_launch("quant_v_seq");
+}
+
+static int launch_nvfp4(const void* x, int in_dtype, int rows, int cols, long long ld, float s, float* scratch,
+                        long long scratch_floats, void* codes, long long ldc_bytes, void* scales, float* tensor_scale,
+                        cudaStream_t st, const char* who) {
+  if (!x || !codes || !scales || !tensor_scale || !scratch || rows <= 0 || cols <= 0)
+    return set_error(MPSA_ERR_BAD_ARG, "%s: null pointer or non-positive shape", who);
+  if (cols % 64) return set_error(MPSA_ERR_UNSUPPORTED, "%s: the quantised axis must be a multiple of 64", who);
+  if (in_dtype < 0 || in_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "%s: bad in_dtype", who);
+  const int esz = in_dtype == 2 ? 4 : 2;
+  if (((uintptr_t)x % 16) || ((ld * esz) % 16) || ((uintptr_t)codes % 8) || (ldc_bytes % 8) || ldc_bytes < cols / 2 ||
+      ((uintptr_t)scales % 16))
+    return set_error(MPSA_ERR_BAD_ARG, "%s: misaligned pointer or pitch", who);
+  dim3 g1((rows + 127) / 128, (cols + 511) / 512), g2((rows + 127) / 128, (cols + 127) / 128);
+  const long long n_partials = (long long)g1.x * g1.y;
+  if (n_partials > scratch_floats)
+    return set_error(MPSA_ERR_UNSUPPORTED, "%s: needs %lld floats of scratch, %lld available", who, n_partials, scratch_floats);
+  if (g1.y > 65535 || g2.y > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "%s: too many columns", who);
+  QuantNvParams p;
+  p.x = x; p.rows = rows; p.cols = cols; p.ld = ld; p.s = s; p.scratch = scratch; p.n_partials = (int)n_partials;
+  p.codes = (uint8_t*)codes; p.ldc_bytes = ldc_bytes; p.scales = (uint8_t*)scales; p.tensor_scale = tensor_scale;
+  if (in_dtype == 0) { nvfp4_amax_kernel<__nv_bfloat16><<<g1, kQuantThreads, 0, st>>>(p); nvfp4_quant_kernel<__nv_bfloat16><<<g2, kQuantThreads, 0, st>>>(p); }
+  else if (in_dtype == 1) { nvfp4_amax_kernel<__half><<<g1, kQuantThreads, 0, st>>>(p); nvfp4_quant_kernel<__half><<<g2, kQuantThreads, 0, st>>>(p); }
+  else { nvfp4_amax_kernel<float><<<g1, kQuantThreads, 0, st>>>(p); nvfp4_quant_kernel<float><<<g2, kQuantThreads, 0, st>>>(p); }
+  return check_launch(who);
+}
+
+extern "C" int mpsa_quant_nvfp4_scratch_floats(int rows, int cols) {
+  const long long n = (long long)((rows + 127) / 128) * ((cols + 511) / 512);
+  return n > 0x7fffffff ? -2 : (int)n;
+}
+
+extern "C" int mpsa_quant_nvfp4(const void* x, int in_dtype, int rows, int cols, long long ld, float s, void* scratch,
+                                long long scratch_floats, void* codes, long long ldc_bytes, void* scales,
+                                void* tensor_scale, void* stream) {
+  return launch_nvfp4(x, in_dtype, rows, cols, ld, s, (float*)scratch, scratch_floats, codes, ldc_bytes, scales,
+                      (float*)tensor_scale, (cudaStream_t)stream, "quant_nvfp4");
 }

@@ -149,6 +149,30 @@ def quantize_int8(x: torch.Tensor, scale: float = 1.0, tensor_layout="HND"):
     return codes, scales
 
 
+def quantize_nvfp4(x: torch.Tensor, scale: float = 1.0):
+    """NVFP4 quantisation of a 2-D operand [rows, K] along K: packed E2M1 codes [rows, K/2], E4M3 block
+    scales as 128x4 tiles [ceil(rows/128), K/64, 512] and the fp32 tensor scale (a 1-element tensor)."""
+    _require_cuda(x)
+    if x.dim() != 2:
+        raise ValueError("quantize_nvfp4 expects a 2-D tensor")
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    rows, cols = x.shape
+    lib = _lib.load()
+    n = lib.mpsa_quant_nvfp4_scratch_floats(rows, cols)
+    dev = x.device
+    scratch = torch.empty(max(n, 1), dtype=torch.float32, device=dev)
+    codes = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
+    scales = torch.empty((-(-rows // 128), cols // 64, 512), dtype=torch.uint8, device=dev)
+    ts = torch.empty(1, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.mpsa_quant_nvfp4(x.data_ptr(), _IN_DTYPE[x.dtype], rows, cols, x.stride(0), float(scale),
+                                  scratch.data_ptr(), scratch.numel(), codes.data_ptr(), codes.stride(0),
+                                  scales.data_ptr(), ts.data_ptr(), _stream())
+    _lib.check(rc)
+    return codes, scales, ts
+
+
 def prepare_vt(v: torch.Tensor) -> torch.Tensor:
     """V [B,H,Skv,D] -> fp16 V^T [B,H,D,Skv_pad] (Skv_pad = Skv rounded up to 128, zero filled)."""
     _require_cuda(v)
@@ -162,6 +186,34 @@ def prepare_vt(v: torch.Tensor) -> torch.Tensor:
                                          v.stride(0), v.stride(1), v.stride(2), _stream())
     _lib.check(rc)
     return vt
+
+
+@dataclass
+class QuantizedV:
+    """V quantised along the sequence for a quantised P.V (both formats, transposed)."""
+    vt8: torch.Tensor       # uint8 [B,H,D,Skv_pad]
+    v8_sf: torch.Tensor     # uint8 [B,H,Skv_pad/128,512]
+    vt4: torch.Tensor       # uint8 [B,H,D,Skv_pad/2]
+    v4_sf: torch.Tensor
+    fp8_elem: str = "e5m2"
+
+
+def quantize_v_seq(v: torch.Tensor, fp8_elem: str = "e5m2") -> QuantizedV:
+    """V [B,H,Skv,D] -> MXFP8 and MXFP4 V^T with 32-key blocks along the sequence (one launch)."""
+    _require_cuda(v)
+    if v.stride(-1) != 1:
+        v = v.contiguous()
+    B, H, Skv, D = v.shape
+    pad = -(-Skv // 128) * 128
+    u8 = dict(dtype=torch.uint8, device=v.device)
+    out = QuantizedV(torch.empty((B, H, D, pad), **u8), torch.empty((B, H, pad // 128, 512), **u8),
+                     torch.empty((B, H, D, pad // 2), **u8), torch.empty((B, H, pad // 128, 512), **u8), fp8_elem)
+    with torch.cuda.device(v.device):
+        rc = _lib.load().mpsa_quant_v_seq(v.data_ptr(), _IN_DTYPE[v.dtype], B, H, Skv, D, pad, v.stride(0), v.stride(1),
+                                          v.stride(2), _FP8_QUANT[fp8_elem], out.vt8.data_ptr(), out.v8_sf.data_ptr(),
+                                          out.vt4.data_ptr(), out.v4_sf.data_ptr(), _stream())
+    _lib.check(rc)
+    return out
 
 
 def precision_map_band(S: int, Skv: int, causal: bool, band: int = 1, tile: int = 128, device="cuda") -> torch.Tensor:
@@ -185,9 +237,12 @@ def _pad_depth_128(x: torch.Tensor) -> torch.Tensor:
 def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, band: int = 1,
                       prec_map: Optional[torch.Tensor] = None, uniform: Optional[str] = None,
                       sm_scale: Optional[float] = None, fp8_elem: str = "e5m2",
-                      out_dtype: torch.dtype = torch.bfloat16, check: bool = False) -> torch.Tensor:
-    """Quantise Q/K (both MXFP8 and MXFP4 in one pass each), transpose V, build the precision map and
-    run the fused forward.  q [B,Hq,S,D], k/v [B,Hkv,Skv,D]; D in {64, 128}."""
+                      out_dtype: torch.dtype = torch.bfloat16, pv_mode: str = "fp16", check: bool = False) -> torch.Tensor:
+    """Quantise Q/K (both MXFP8 and MXFP4 in one pass each), prepare V, build the precision map and
+    run the fused forward.  q [B,Hq,S,D], k/v [B,Hkv,Skv,D]; D in {64, 128}.
+
+    pv_mode "fp16": P and V in fp16, the P.V precision of the reference kernel.
+    pv_mode "requant": P is re-quantised to the tile's MX format and V is quantised along the sequence."""
     _require_cuda(q, k, v)
     B, Hq, S, D = q.shape
     _, Hkv, Skv, _ = k.shape
@@ -196,18 +251,25 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
     sq = q_side_scale(D, sm_scale)
     qq = quantize_mx(_pad_depth_128(q), sq, fp8_elem=fp8_elem)
     kq = quantize_mx(_pad_depth_128(k), 1.0, fp8_elem=fp8_elem)
-    vt = prepare_vt(v)
+    if pv_mode == "fp16":
+        vt = prepare_vt(v)
+    elif pv_mode == "requant":
+        vt = quantize_v_seq(v, fp8_elem)
+    else:
+        raise ValueError(f"unknown pv_mode {pv_mode!r}")
     return attention_forward_quantized(qq, kq, vt, B, Hq, Hkv, S, Skv, D, causal=causal, band=band,
                                        prec_map=prec_map, uniform=uniform, out_dtype=out_dtype, check=check)
 
 
-def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt: torch.Tensor, B: int, Hq: int,
+def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, B: int, Hq: int,
                                 Hkv: int, S: int, Skv: int, D: int, *, causal: bool, band: int = 1,
                                 prec_map: Optional[torch.Tensor] = None, uniform: Optional[str] = None,
                                 out_dtype: torch.dtype = torch.bfloat16, check: bool = False) -> torch.Tensor:
     """The fused forward on operands that are already quantised (depth padded to 128) and a V^T from
-    prepare_vt.  Both formats of Q and K must be present unless `uniform` restricts the map to one."""
-    dev = vt.device
+    prepare_vt (fp16 P.V) or a QuantizedV from quantize_v_seq (quantised P.V).  Both formats of Q and K
+    must be present unless `uniform` restricts the map to one."""
+    requant = isinstance(vt, QuantizedV)
+    dev = vt.vt8.device if requant else vt.device
     nq, nk = -(-S // 128), -(-Skv // 128)
     if prec_map is None:
         prec_map = precision_map_band(S, Skv, causal, band, 128, dev)
@@ -244,8 +306,18 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt: 
     for t, n in ((q8s, B * Hq * nq), (q4s, B * Hq * nq), (k8s, B * Hkv * nk), (k4s, B * Hkv * nk)):
         if t.numel() != n * 512 or not t.is_contiguous():
             raise ValueError("scale tiles have the wrong size")
-    if vt.shape[-1] % 128 or vt.shape[-1] < Skv or tuple(vt.shape[:3]) != (B, Hkv, D) or vt.dtype != torch.float16:
-        raise ValueError("vt must be fp16 [B, Hkv, D, Skv rounded up to 128]")
+    skv_pad = nk * 128
+    if requant:
+        if tuple(vt.vt8.shape) != (B, Hkv, D, skv_pad) or tuple(vt.vt4.shape) != (B, Hkv, D, skv_pad // 2) or \
+                vt.v8_sf.numel() != B * Hkv * nk * 512 or vt.v4_sf.numel() != B * Hkv * nk * 512:
+            raise ValueError("quantised V has the wrong shape")
+        if vt.fp8_elem != qq.fp8_elem:
+            raise ValueError("Q/K and V use different fp8 element formats")
+        vptrs = (None, vt.vt8.data_ptr(), vt.v8_sf.data_ptr(), vt.vt4.data_ptr(), vt.v4_sf.data_ptr(), 1)
+    else:
+        if tuple(vt.shape) != (B, Hkv, D, skv_pad) or vt.dtype != torch.float16 or not vt.is_contiguous():
+            raise ValueError("vt must be contiguous fp16 [B, Hkv, D, Skv rounded up to 128]")
+        vptrs = (vt.data_ptr(), None, None, None, None, 0)
     if (qq.fp8 is None or kq.fp8 is None) and uniform != "fp4":
         raise ValueError("MXFP8 operands missing but the precision map may select FP8 tiles")
     if (qq.fp4 is None or kq.fp4 is None) and uniform != "fp8":
@@ -256,17 +328,19 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt: 
         rc = _lib.load().mpsa_attn_fwd(
             q8.data_ptr(), q8s.data_ptr(), q4.data_ptr(), q4s.data_ptr(),
             k8.data_ptr(), k8s.data_ptr(), k4.data_ptr(), k4s.data_ptr(),
-            vt.data_ptr(), prec_map.data_ptr(), msb, msh, out.data_ptr(), _OUT_DTYPE[out_dtype],
-            B, Hq, Hkv, S, Skv, D, vt.shape[-1], int(causal), _FP8_DESC[qq.fp8_elem], st.data_ptr(), _stream())
+            *vptrs, prec_map.data_ptr(), msb, msh, out.data_ptr(), _OUT_DTYPE[out_dtype],
+            B, Hq, Hkv, S, Skv, D, skv_pad, int(causal), _FP8_DESC[qq.fp8_elem], st.data_ptr(), _stream())
     _lib.check(rc)
     if check:
         check_status(dev)
     return out
 
 
-def diagonal_tiled_attention(q, k, v, causal=True):
-    """README-level entry of the reference project: diagonal tiles in MXFP8, the rest in MXFP4."""
-    return attention_forward(q, k, v, causal=causal, out_dtype=q.dtype if q.dtype != torch.float32 else torch.float32)
+def diagonal_tiled_attention(q, k, v, causal=True, pv_mode="requant"):
+    """README-level entry of the reference project: diagonal tiles in MXFP8, the rest in MXFP4, P
+    re-quantised to the tile's format before P.V."""
+    return attention_forward(q, k, v, causal=causal, pv_mode=pv_mode,
+                             out_dtype=q.dtype if q.dtype != torch.float32 else torch.float32)
 
 
 _GEMM_MODE = {"mxfp8": 0, "mxfp4": 1, "nvfp4": 2}

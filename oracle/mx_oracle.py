@@ -329,6 +329,8 @@ def quant_v_seq(v: torch.Tensor, fmt: str):
     contraction axis of P.V).  Returns codes [.., D, S] (transposed, one per byte) and
     scales [.., D, S/32].  RNE element rule for fp4 (OCP MX), RNE cast for fp8."""
     vt = v.transpose(-1, -2).contiguous()
+    if vt.shape[-1] % 32:                          # a ragged tail is zero-padded to a whole block
+        vt = torch.nn.functional.pad(vt.float(), (0, 32 - vt.shape[-1] % 32))
     if fmt == "fp4":
         y, e8, amax = _mx_prepare(vt, 1.0, emax=2)
         codes = encode_e2m1_rne(torch.where(amax == 0, torch.zeros_like(y), y)).reshape(vt.shape)
@@ -355,9 +357,10 @@ def attention_mxfp(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
        ours/online_routing.py:113-115 is -inf here).
     3. m = rowmax, P = exp2(S - m), l = sum P from the unrounded fp32 P
        (ours/mxfp_attn_kernel.py:320-328).
-    4. pv_mode "fp16": P -> fp16, V -> fp16, O = P@V (:339-340).  pv_mode "requant": P is
-       block-quantised per 32 keys in the tile's format and V per 32 keys along the
-       sequence (no counterpart in the reference).
+    4. pv_mode "fp16": P -> fp16, V -> fp16, O = P@V (:339-340).  pv_mode "requant": P =
+       exp2(S - ceil(m)) is block-quantised per 32 keys in the tile's format (MXFP8 by the
+       rule of ours/quant_mxint8.py:164-221, MXFP4 by the OCP rule with round-to-nearest-even)
+       and V per 32 keys along the sequence (no counterpart in the reference).
     5. O = O / l (:355), cast to out_dtype.
     GQA: kv head = q head // (Hq/Hkv) (ours/online_routing.py:160).
     ``uniform`` = "fp8" | "fp4" forces one format for every non-skipped tile.
@@ -400,6 +403,11 @@ def attention_mxfp(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
             if return_scores:
                 scores[b, h] = sc
             m = sc.amax(dim=-1, keepdim=True)
+            if pv_mode == "requant":
+                # P is block-quantised with power-of-two scales, so an integral change of the
+                # reference changes scale codes only; the integral reference makes the element
+                # codes independent of how an implementation tracks the running maximum.
+                m = torch.ceil(m)
             p = torch.exp2(sc - m)
             l = p.sum(dim=-1, keepdim=True)
             if pv_mode == "fp16":
@@ -417,6 +425,9 @@ def _pv_requant(p: torch.Tensor, v: torch.Tensor, cell: torch.Tensor, tile: int,
     """P block-quantised per 32 keys (format of the tile) times V block-quantised per 32
     keys along the sequence.  PARITY UNPINNED."""
     S, Skv = p.shape
+    if Skv % 32:                                   # masked tail keys have P = 0: pad to a whole block
+        p = torch.nn.functional.pad(p, (0, 32 - Skv % 32))
+        cell = torch.nn.functional.pad(cell, (0, 32 - Skv % 32), value=int(cell[0, -1]))
     v8c, v8s = quant_v_seq(v, f8)
     v4c, v4s = quant_v_seq(v, "fp4")
     V8 = dequant(v8c, v8s, f8).T

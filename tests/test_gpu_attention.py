@@ -124,3 +124,53 @@ def test_long_sequence_slice_and_properties():
     ones = torch.ones_like(v)
     o1 = mpsa.attention_forward(q.cuda(), k.cuda(), ones.cuda(), causal=True, out_dtype=torch.float32, check=True)
     assert float((o1 - 1).abs().max()) < 2e-3
+
+
+# ---- quantised P.V (P re-quantised to the tile's format, V quantised along the sequence) -------------
+def test_v_quantizer_matches_oracle():
+    import mpsa
+    g = torch.Generator().manual_seed(8)
+    for (B, H, S, D) in [(1, 2, 256, 128), (2, 1, 200, 128), (1, 2, 128, 64)]:
+        v = (torch.randn(B, H, S, D, generator=g) * 1.7).to(torch.bfloat16)
+        v[0, 0, 32:64, 5] = 0                      # an all-zero block
+        r = mpsa.quantize_v_seq(v.cuda())
+        for fmt, codes, sf in (("fp8e5", r.vt8.cpu(), r.v8_sf.cpu()), ("fp4", r.vt4.cpu(), r.v4_sf.cpu())):
+            oc, osc = O.quant_v_seq(v, fmt)        # [B,H,D,S] codes, [B,H,D,S/32] scales
+            pad = r.vt8.shape[-1]
+            nblk = osc.shape[-1]                   # the oracle pads a ragged tail to a whole 32-key block
+            got = (O.unpack_e2m1(codes) if fmt == "fp4" else codes)[..., :nblk * 32]
+            assert torch.equal(got, oc)
+            # scale tiles: rows = d, columns = key blocks; one tile per 128 keys
+            tiles = sf.reshape(B, H, pad // 128, 32, 4, 4)
+            for kt in range(pad // 128):
+                for blk in range(4):
+                    kb = kt * 4 + blk
+                    if kb >= nblk:
+                        continue
+                    col = tiles[:, :, kt, :, :, blk]                  # [B,H,32,4]: d = i4*32 + i32
+                    flat = col.permute(0, 1, 3, 2).reshape(B, H, 128)[..., :D]
+                    assert torch.equal(flat, osc[..., kb]), (fmt, kt, blk)
+
+
+@pytest.mark.parametrize("uniform", ["fp8", "fp4", None])
+@pytest.mark.parametrize("causal", [False, True])
+def test_requant_pv_small(uniform, causal):
+    for S in (128, 384):
+        q, k, v = O.make_qkv(0, 1, 2, 2, S, 128)
+        ref = O.attention_mxfp(q, k, v, causal=causal, uniform=uniform, pv_mode="requant")
+        out = _run(q, k, v, causal, uniform=uniform, pv_mode="requant")
+        _check(out, ref, ("requant", S, uniform, causal))
+
+
+def test_requant_pv_gqa_outliers_and_ragged():
+    q, k, v = O.make_qkv(2, 1, 8, 2, 1024, 128, outliers=5)
+    ref = O.attention_mxfp(q, k, v, causal=True, pv_mode="requant")
+    out = _run(q, k, v, True, pv_mode="requant")
+    _check(out, ref, "requant gqa")
+    print("requant vs fp32 attention:", O.parity_metrics(out, O.attention_fp32(q, k, v, True)))
+    q, k, v = O.make_qkv(3, 2, 2, 1, 333, 128)
+    ref = O.attention_mxfp(q, k, v, causal=True, pv_mode="requant")
+    _check(_run(q, k, v, True, pv_mode="requant"), ref, "requant ragged")
+    q, k, v = O.make_qkv(0, 1, 4, 4, 512, 64)
+    ref = O.attention_mxfp(q, k, v, causal=True, pv_mode="requant")
+    _check(_run(q, k, v, True, pv_mode="requant"), ref, "requant d64")

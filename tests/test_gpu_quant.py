@@ -108,3 +108,27 @@ def test_full_size_properties():
     # a 2048-row slice against the oracle, bit exact
     c4, s4 = O.quant_mxfp4_side(x[0, 7, 4096:6144].cpu(), 1.0)
     assert torch.equal(r.fp4_unpacked[0, 7, 4096:6144].cpu(), c4) and torch.equal(r.fp4_scales[0, 7, 4096:6144].cpu(), s4)
+
+
+@pytest.mark.parametrize("rows,cols,dtype", [(256, 512, torch.bfloat16), (200, 320, torch.float16), (130, 1024, torch.float32)])
+def test_nvfp4_quantizer_matches_oracle(rows, cols, dtype):
+    """No reference counterpart (parity unpinned): checked against the oracle's restatement of the format."""
+    import mpsa
+    g = torch.Generator().manual_seed(21)
+    x = (torch.randn(rows, cols, generator=g) * 3).to(dtype)
+    x[5, 16:32] = 0
+    codes, scales, ts = mpsa.quantize_nvfp4(x.cuda())
+    oc, osc, ots = O.quant_nvfp4(x)
+    assert float(ts.cpu()) == float(ots)
+    assert torch.equal(codes.cpu(), O.pack_e2m1(oc))
+    assert torch.equal(scales.cpu().reshape(O.swizzle_scales(osc, pad_code=0).shape), O.swizzle_scales(osc, pad_code=0))
+    # and straight into the GEMM
+    y = (torch.randn(256, cols, generator=g)).to(dtype)
+    if cols % 64 == 0 and rows % 1 == 0:
+        cy, sy, tsy = mpsa.quantize_nvfp4(y.cuda())
+        out = mpsa.gemm_block_scaled(codes, scales, cy, sy, torch.float32, rows, 256, cols, "nvfp4",
+                                     alpha=float(ts.cpu()) * float(tsy.cpu()), check=True)
+        yc, ysc, yts = O.quant_nvfp4(y)
+        ref = O.gemm_block_scaled(oc, osc, yc, ysc, "nvfp4", "nvfp4", 16, ots, yts)
+        m = O.parity_metrics(out.cpu(), ref)
+        assert m["cos"] >= 0.9999 and m["rel_l2"] <= 1e-2, m
