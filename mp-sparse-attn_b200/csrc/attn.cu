@@ -900,23 +900,30 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   p.out = out; p.out_dtype = out_dtype; p.status = status;
   // Softmax organisation: warpgroups taking tiles in turn (1 or 2) x threads per query row inside a
   // warpgroup (1, 2 or 4).  MPSA_ATTN_WG / MPSA_ATTN_SPLIT override the default.
-  static int cfg = 0;
-  if (cfg == 0) {
+  // Defaults (measured on B200 at S=32768): fp16 P.V 2 warpgroups x 1, quantised P.V 2 x 2.
+  static int cfg_of[2] = {0, 0};
+  if (cfg_of[0] == 0) {
     const char* e1 = getenv("MPSA_ATTN_WG");
     const char* e2 = getenv("MPSA_ATTN_SPLIT");
-    int nwg = e1 ? atoi(e1) : 2, ns = e2 ? atoi(e2) : 1;
-    if (nwg != 1 && nwg != 2) nwg = 2;
-    if (ns != 1 && ns != 2 && ns != 4) ns = 1;
-    if (nwg == 2 && ns == 4) ns = 2;
+    for (int m = 0; m < 2; ++m) {
+      int nwg = e1 ? atoi(e1) : 2, ns = e2 ? atoi(e2) : (m == 0 ? 1 : 2);
+      if (nwg != 1 && nwg != 2) nwg = 2;
+      if (ns != 1 && ns != 2 && ns != 4) ns = 1;
+      if (nwg == 2 && ns == 4) ns = 2;
+      cfg_of[m] = nwg * 10 + ns;
+    }
     cudaError_t e = cudaSuccess;
 #define MPSA_SET_SMEM(A, B) \
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM); \
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
     MPSA_SET_SMEM(1, 1) MPSA_SET_SMEM(1, 2) MPSA_SET_SMEM(1, 4) MPSA_SET_SMEM(2, 1) MPSA_SET_SMEM(2, 2)
 #undef MPSA_SET_SMEM
-    if (e != cudaSuccess) return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
-    cfg = nwg * 10 + ns;
+    if (e != cudaSuccess) {
+      cfg_of[0] = 0;
+      return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
+    }
   }
+  const int cfg = cfg_of[pv_mode];
   const int nq = (S + ATT_BM - 1) / ATT_BM;
   if (Hq > 65535 || B > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: Hq and B must be below 65536");
   dim3 grid(nq, Hq, B);
