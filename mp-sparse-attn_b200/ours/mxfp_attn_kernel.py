@@ -12,7 +12,8 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
     """q [B,Hq,S,D], k/v [B,Hkv,Skv,D] (HND) or [B,S,H,D] (NHD) -> o in q's layout.
 
     block_scale_type: "mxfp4" / "mxfp8" quantise every tile of Q.K^T to that format (the two modes
-    of the reference); "diag" keeps the diagonal tiles in MXFP8 and the rest in MXFP4.
+    of the reference); "diag" keeps the diagonal tiles in MXFP8 and the rest in MXFP4; "diag_requant"
+    additionally re-quantises P to the tile's format before P.V (V quantised along the sequence).
     attn_mask, dropout_p, attention_sink, return_sparsity and skip_thresh are accepted and ignored,
     as in the reference wrapper; is_causal, scale and output_dtype are honoured (the reference
     ignores them)."""
@@ -28,12 +29,12 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
     assert q.shape[-1] in [64, 128], "headdim should be in [64, 128]."
     if block_scale_type == "mxfp4":
         uniform = "fp4"
-    elif block_scale_type == "diag":
+    elif block_scale_type in ("diag", "diag_requant"):
         uniform = None
     else:
         uniform = "fp8"
     o = _ops.attention_forward(q, k, v, causal=bool(is_causal), uniform=uniform, sm_scale=scale,
-                               out_dtype=output_dtype)
+                               out_dtype=output_dtype, pv_mode="requant" if block_scale_type == "diag_requant" else "fp16")
     return o.transpose(1, 2) if tensor_layout == "NHD" else o
 
 
