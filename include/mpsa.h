@@ -70,6 +70,20 @@ int mpsa_quant_nvfp4(const void* x, int in_dtype, int rows, int cols, long long 
                      long long scratch_floats, void* codes, long long ldc_bytes, void* scales, void* tensor_scale,
                      void* stream);
 
+/* The same quantizer for callers that cannot allocate device memory (a process whose memory was handed to
+ * its own pool at start-up, a plugin barred from the CUDA allocator on its request path, a bare C host):
+ * the partial maxima are kept in a 64 KB array built into the library's device image instead of a
+ * caller-provided scratch.  This entry has no counterpart in the reference.  It calls no allocator.
+ *   - Limit: ceil(rows/128) * ceil(cols/512) <= 16384 partials (about 1e9 elements); larger operands are
+ *     refused with MPSA_ERR_UNSUPPORTED and a message naming the limit.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array (each call overwrites the part it uses; nothing needs
+ *     clearing), so two calls that overlap in time on the GPU race: keep them on one stream or order them.
+ *   - Inputs and outputs are the caller's, as in mpsa_quant_nvfp4; results are identical to it. */
+int mpsa_quant_nvfp4_static(const void* x, int in_dtype, int rows, int cols, long long ld, float s, void* codes,
+                            long long ldc_bytes, void* scales, void* tensor_scale, void* stream);
+
 /* V operand of a quantised P.V: 32-key MX blocks along the SEQUENCE axis, transposed.  V [B,H,Skv,D]
  * (strided) -> vt8 [B,H,D,Skv_pad] MXFP8 codes and/or vt4 [B,H,D,Skv_pad/2] MXFP4 codes (two per byte),
  * scale tiles v8_sf / v4_sf [B,H,Skv_pad/128,512] (rows = head-dim index, columns = the four 32-key

@@ -17,6 +17,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <mutex>
 
 namespace mpsa {
 
@@ -560,4 +561,48 @@ extern "C" int mpsa_quant_nvfp4(const void* x, int in_dtype, int rows, int cols,
                                 void* tensor_scale, void* stream) {
   return launch_nvfp4(x, in_dtype, rows, cols, ld, s, (float*)scratch, scratch_floats, codes, ldc_bytes, scales,
                       (float*)tensor_scale, (cudaStream_t)stream, "quant_nvfp4");
+}
+
+// ---- NVFP4 quantizer for callers that must not allocate ------------------------------------------------
+// Some hosts of this library cannot obtain the scratch array the two-stage NVFP4 quantizer needs: a
+// serving process that gave its whole memory budget to its own pool at start-up, a plugin that is not
+// allowed to call the CUDA allocator on the request path, a C host with no allocator wrapper at all.
+// For them the partial maxima live in a fixed array inside this library's device image.  Every GPU that
+// loads the library carries these 64 KB until the process exits.
+constexpr int kStaticScratchFloats = 16384;            // one partial per 128x512 input tile
+static __device__ __align__(256) float g_nvfp4_scratch[kStaticScratchFloats];
+
+extern "C" int mpsa_quant_nvfp4_static(const void* x, int in_dtype, int rows, int cols, long long ld, float s,
+                                       void* codes, long long ldc_bytes, void* scales, void* tensor_scale,
+                                       void* stream) {
+  // In host code the array's name only stands for the symbol; its device address has to be asked for,
+  // once per device, with that device current.  The first call on a device does it.
+  constexpr int kMaxDevices = 64;
+  static float* scratch_of[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return set_error(MPSA_ERR_LAUNCH, "quant_nvfp4_static: cannot identify the current device");
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!scratch_of[dev]) {
+      float* ptr = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_nvfp4_scratch);
+      if (e != cudaSuccess || !ptr)
+        return set_error(MPSA_ERR_LAUNCH, "quant_nvfp4_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      scratch_of[dev] = ptr;
+    }
+    scratch = scratch_of[dev];
+  }
+  if (rows > 0 && cols > 0) {
+    const long long need = (long long)((rows + 127) / 128) * ((cols + 511) / 512);
+    if (need > kStaticScratchFloats)
+      return set_error(MPSA_ERR_UNSUPPORTED,
+                       "quant_nvfp4_static: a %d x %d operand needs %lld partial maxima, the built-in scratch holds %d "
+                       "(about 1e9 elements); use mpsa_quant_nvfp4 with caller-provided scratch",
+                       rows, cols, need, kStaticScratchFloats);
+  }
+  return launch_nvfp4(x, in_dtype, rows, cols, ld, s, scratch, kStaticScratchFloats, codes, ldc_bytes, scales,
+                      (float*)tensor_scale, (cudaStream_t)stream, "quant_nvfp4_static");
 }
