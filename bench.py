@@ -252,6 +252,63 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_ring(args):
+    """Long-context causal attention, B=1 Hq=32 Hkv=8 D=128 S=131072, sequence-sharded over the GPUs: every
+    rank quantises its slice once and the MXFP4 K/V blocks travel round an NCCL ring (strong scaling)."""
+    import torch.distributed as dist
+    import mpsa
+    from mpsa.ring import RingSchedule, ring_attention
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    S = 131072 if args.seq == 32768 else args.seq
+    sched = RingSchedule(world, rank, args.layout, True)
+    s_local = S // world
+    g = torch.Generator(device=dev).manual_seed(4 + rank)
+    q = torch.randn(1, HQ, s_local, D, generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn(1, HKV, s_local, D, generator=g, device=dev).to(torch.bfloat16)
+    v = torch.randn(1, HKV, s_local, D, generator=g, device=dev).to(torch.bfloat16)
+    K, W = args.steps, args.warmup
+
+    def sync_all():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        ring_attention(q, k, v, causal=True, layout=args.layout)
+    mpsa.check_status(dev)
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        ring_attention(q, k, v, causal=True, layout=args.layout)
+    e1.record()
+    sync_all()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    mpsa.check_status(dev)
+    if rank == 0:
+        flops = attn_flops(1, HQ, S, D)
+        print(json.dumps({
+            "metric": "effective attn TFLOPS, Llama-3-8B shape causal, sequence-parallel ring", "value": round(flops * K / (ms * 1e-3) / 1e12, 3),
+            "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 3),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "mxfp8/mxfp4 (fp32 accumulate)",
+            "data": "synthetic", "config": {"workload": f"cfg5 causal B=1 Hq=32 Hkv=8 D=128 S={S} sequence-sharded, "
+                                                        f"{args.layout} ownership, MXFP4 K/V ring over NCCL",
+                                            "work_units_per_rank": sched.work_units()}}))
+    dist.destroy_process_group()
+
+
 def cpu_baseline(steps=1, warmup=0, budget_s=25.0):
     """The oracle (CPU restatement of the reference's algorithm, PyTorch on all host cores) on the
     workload's head layout at S=8192: quantise, emulate both products, softmax, P.V.  The number of
@@ -303,13 +360,20 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seq", type=int, default=32768)
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "ring"],
+                    help="prefill: the headline single-GPU workload replicated per GPU; ring: S=131072 causal, "
+                         "sequence-sharded over the GPUs (strong scaling)")
+    ap.add_argument("--layout", default="zigzag", choices=["contiguous", "zigzag"])
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
-    run_ours(args)
+    if args.workload == "ring":
+        run_ring(args)
+    else:
+        run_ours(args)
 
 
 if __name__ == "__main__":

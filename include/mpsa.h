@@ -107,6 +107,7 @@ int mpsa_route_band(void* map, int nq, int nk, int tile, int causal, int band, i
  *   pv_mode 1      P re-quantised to the tile's format, V from mpsa_quant_v_seq (vt8, v8_sf, vt4, v4_sf)
  *   map            uint8 [.., ceil(S/128), ceil(Skv/128)] with batch / head strides map_sb / map_sh (0 = shared)
  *   out            [B,Hq,S,D] contiguous
+ *   lse            optional fp32 [B,Hq,S]: log2 of each row's softmax denominator (for merging partial results)
  *   fp8_fmt        descriptor format of the fp8 codes: 0 E4M3, 1 E5M2
  *   status         one int32, must be 0 on entry; a kernel whose bounded waits expire stores a
  *                  non-zero code here (1 TMA, 2 MMA, 3 pipeline) and unwinds
@@ -114,8 +115,16 @@ int mpsa_route_band(void* map, int nq, int nk, int tile, int causal, int band, i
 int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
                   const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* vt8,
                   const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
-                  long long map_sb, long long map_sh, void* out, int out_dtype, int B, int Hq, int Hkv, int S,
-                  int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int* status, void* stream);
+                  long long map_sb, long long map_sh, void* out, int out_dtype, void* lse, int B, int Hq, int Hkv,
+                  int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int* status, void* stream);
+
+/* Merges a partial attention result into an accumulator: acc fp32 [rows, D] and lse_acc fp32 [rows] are
+ * updated in place with part [rows, D] (part_dtype 0 f32, 1 f16, 2 bf16) and lse_part, where every lse is
+ * log2 of the softmax denominator of its (disjoint) key set as written by mpsa_attn_fwd; rows with
+ * lse = -inf carry no keys.  Used by the sequence-parallel ring, which has no counterpart in the
+ * reference (its kernel sees all keys in one launch, ours/mxfp_attn_kernel.py:245). */
+int mpsa_attn_merge(void* acc, void* lse_acc, const void* part, int part_dtype, const void* lse_part, long long rows,
+                    int D, void* stream);
 
 /* C[M,N] = alpha * (A . sa)(B . sb)^T.  Replaces block_scaled_matmul (ours/block_scaled_matmul.py:271-296)
  * and its kernel (:154-267).

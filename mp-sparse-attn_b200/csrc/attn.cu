@@ -89,6 +89,7 @@ struct AttnParams {
   int pv_mode;                       // 0: P and V in fp16; 1: P and V in the tile's MX format
   const uint8_t* map; long long map_sb, map_sh; // [.., nq, nk], strides may be 0 (broadcast)
   void* out; int out_dtype;          // [B,Hq,S,D] contiguous; 0 f32, 1 f16, 2 bf16
+  float* lse;                        // optional [B,Hq,S]: log2 of the softmax denominator (incl. the row reference)
   int* status;
 };
 
@@ -713,12 +714,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     }
     // ---- epilogue: bring every partial sum to the final reference, add them, O / l ----
     float l_tot = l_run;
+    float m_final = m_seen;                         // reference the partial sums end up referring to
     if (NWG * NSPLIT > 1 && ok) {
       if (NWG > 1 && t > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(&m_bar[((t - 1) & 1) * 4 + q], ((t - 1) >> 1) & 1, p.status, KS_TIMEOUT_PIPE));
         if (ok) {
           const float m_fin = mrow[((t - 1) & 1) * 128 + r_in];
           if (m_fin != m_seen) l_run = (m_seen == -INFINITY) ? 0.0f : l_run * ex2(m_seen - m_fin);
+          m_final = m_fin;
         }
       }
       if (ok) {
@@ -740,6 +743,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     if (ok) {
       const float inv_l = (t > 0 && l_tot > 0.0f) ? 1.0f / l_tot : 0.0f;
       const long long o_off = ((long long)(b * p.Hq + h) * p.S + m_glob) * p.D;
+      if (p.lse && part == 0 && m_glob < p.S)       // log2(sum_k exp2(S_k)): lets partial results be merged
+        p.lse[(long long)(b * p.Hq + h) * p.S + m_glob] = (t > 0 && l_tot > 0.0f) ? m_final + log2f(l_tot) : -INFINITY;
       for (int c = part; c < p.D / 32; c += NWG * NSPLIT) {
         uint32_t o[32];
         if (t > 0) {
@@ -779,6 +784,51 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, ATT_TMEM_COLS);
+}
+
+// ---- merging partial attention results -----------------------------------------------------------
+// Two softmax-normalised partial outputs over disjoint key sets, with their log2 denominators, combine to
+// the result over the union: w_i = 2^(lse_i - lse), lse = log2(2^lse_a + 2^lse_b).  acc (fp32) and
+// lse_acc are updated in place; one thread per 4 output elements.
+__global__ void __launch_bounds__(256) attn_merge_kernel(float* acc, float* lse_acc, const void* part, int part_dtype,
+                                                         const float* lse_part, long long rows, int D) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;     // index of a 4-element group
+  const long long per_row = D / 4;
+  if (i >= rows * per_row) return;
+  const long long r = i / per_row;
+  const float la = lse_acc[r], lb = lse_part[r];
+  const float lm = fmaxf(la, lb);
+  float wa = 0.0f, wb = 0.0f, lnew = -INFINITY;
+  if (lm != -INFINITY) {
+    const float ea = exp2f(la - lm), eb = exp2f(lb - lm);
+    const float inv = 1.0f / (ea + eb);
+    wa = ea * inv;
+    wb = eb * inv;
+    lnew = lm + log2f(ea + eb);
+  }
+  float4 a = reinterpret_cast<float4*>(acc)[i];
+  float4 bv;
+  if (part_dtype == 0) {
+    bv = reinterpret_cast<const float4*>(part)[i];
+  } else {
+    const uint2 raw = reinterpret_cast<const uint2*>(part)[i];
+    if (part_dtype == 1) {
+      const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+      const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+      bv = make_float4(f0.x, f0.y, f1.x, f1.y);
+    } else {
+      const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+      const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      bv = make_float4(f0.x, f0.y, f1.x, f1.y);
+    }
+  }
+  a.x = (wa == 0.0f ? 0.0f : a.x * wa) + (wb == 0.0f ? 0.0f : bv.x * wb);
+  a.y = (wa == 0.0f ? 0.0f : a.y * wa) + (wb == 0.0f ? 0.0f : bv.y * wb);
+  a.z = (wa == 0.0f ? 0.0f : a.z * wa) + (wb == 0.0f ? 0.0f : bv.z * wb);
+  a.w = (wa == 0.0f ? 0.0f : a.w * wa) + (wb == 0.0f ? 0.0f : bv.w * wb);
+  reinterpret_cast<float4*>(acc)[i] = a;
+  __syncwarp();
+  if (i % per_row == 0) lse_acc[r] = lnew;
 }
 
 // ---- V^T preparation: V [B,Hkv,Skv,D] (any 16-bit/32-bit float, strided) -> fp16 [B,Hkv,D,Skv_pad],
@@ -836,6 +886,22 @@ extern "C" int mpsa_route_band(void* map, int nq, int nk, int tile, int causal, 
   return check_launch("route_band");
 }
 
+extern "C" int mpsa_attn_merge(void* acc, void* lse_acc, const void* part, int part_dtype, const void* lse_part,
+                               long long rows, int D, void* stream) {
+  if (!acc || !lse_acc || !part || !lse_part || rows <= 0)
+    return set_error(MPSA_ERR_BAD_ARG, "attn_merge: null pointer or bad shape");
+  if (D != 32 && D != 64 && D != 128)      // a row's threads must sit in one warp (in-place update of lse_acc)
+    return set_error(MPSA_ERR_UNSUPPORTED, "attn_merge: head_dim must be 32, 64 or 128");
+  if (part_dtype < 0 || part_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "attn_merge: part_dtype must be 0 (f32), 1 (f16) or 2 (bf16)");
+  if (((uintptr_t)acc % 16) || ((uintptr_t)part % 16)) return set_error(MPSA_ERR_BAD_ARG, "attn_merge: 16-byte aligned buffers needed");
+  const long long groups = rows * (D / 4);
+  const long long blocks = (groups + 255) / 256;
+  if (blocks > 0x7fffffffll) return set_error(MPSA_ERR_UNSUPPORTED, "attn_merge: too many rows");
+  attn_merge_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((float*)acc, (float*)lse_acc, part, part_dtype,
+                                                                     (const float*)lse_part, rows, D);
+  return check_launch("attn_merge");
+}
+
 extern "C" int mpsa_prepare_vt(const void* v, int in_dtype, void* vt, int B, int H, int Skv, int D, int Skv_pad,
                                long long vs_b, long long vs_h, long long vs_l, void* stream) {
   if (!v || !vt || B <= 0 || H <= 0 || Skv <= 0 || D <= 0) return set_error(MPSA_ERR_BAD_ARG, "prepare_vt: bad argument");
@@ -853,8 +919,9 @@ extern "C" int mpsa_prepare_vt(const void* v, int in_dtype, void* vt, int B, int
 extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
                              const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* vt8,
                              const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
-                             long long map_sb, long long map_sh, void* out, int out_dtype, int B, int Hq, int Hkv,
-                             int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int* status, void* stream) {
+                             long long map_sb, long long map_sh, void* out, int out_dtype, void* lse, int B, int Hq,
+                             int Hkv, int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int* status,
+                             void* stream) {
   if (!q8 || !q8_sf || !q4 || !q4_sf || !k8 || !k8_sf || !k4 || !k4_sf || !map || !out || !status)
     return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: null pointer");
   if (pv_mode != 0 && pv_mode != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: pv_mode must be 0 (fp16 P.V) or 1 (quantised P.V)");
@@ -897,7 +964,7 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   p.k8_sf = (const uint8_t*)k8_sf; p.k4_sf = (const uint8_t*)k4_sf;
   p.v8_sf = (const uint8_t*)v8_sf; p.v4_sf = (const uint8_t*)v4_sf; p.pv_mode = pv_mode;
   p.map = (const uint8_t*)map; p.map_sb = map_sb; p.map_sh = map_sh;
-  p.out = out; p.out_dtype = out_dtype; p.status = status;
+  p.out = out; p.out_dtype = out_dtype; p.lse = (float*)lse; p.status = status;
   // Softmax organisation: warpgroups taking tiles in turn (1 or 2) x threads per query row inside a
   // warpgroup (1, 2 or 4).  MPSA_ATTN_WG / MPSA_ATTN_SPLIT override the default.
   // Defaults (measured on B200 at S=32768): fp16 P.V 2 warpgroups x 1, quantised P.V 2 x 2.

@@ -76,10 +76,42 @@ __device__ __forceinline__ void load16<float>(const float* p, float (&v)[16]) {
 }
 
 constexpr int kQuantThreads = 256;
-constexpr int kRunsPerThread = 4;   // 256 threads * 4 runs * 16 elements = 128 x 128 tile
+constexpr int kRunsPerThread = 4;   // 256 threads * 4 runs * 16 elements = 128 x 128 tile (int8 / NVFP4 kernels)
+constexpr int kMxThreads = 512;     // MX kernel: 512 threads * 2 runs * 16 elements
+constexpr int kMxRuns = 2;
+
+// 8 floats -> 8 E2M1 codes in one word (element 0 in the low nibble); the inputs are already on the
+// E2M1 grid (fp4_snap_ref), so the conversion is exact.
+__device__ __forceinline__ uint32_t cvt_e2m1x8_regs(float y0, float y1, float y2, float y3, float y4, float y5,
+                                                    float y6, float y7) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+      "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+      : "=r"(r)
+      : "f"(y0), "f"(y1), "f"(y2), "f"(y3), "f"(y4), "f"(y5), "f"(y6), "f"(y7));
+  return r;
+}
+// 4 floats -> 4 fp8 codes in one word (round to nearest even; satfinite clamps to +-57344 / +-448, which
+// is the clamp of ours/quant_mxint8.py:203).
+template <bool E4M3>
+__device__ __forceinline__ uint32_t cvt_fp8x4_regs(float y0, float y1, float y2, float y3) {
+  uint32_t r;
+  if (E4M3) {
+    asm("{\n\t.reg .b16 lo, hi;\n\tcvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\tcvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+        "mov.b32 %0, {lo, hi};\n\t}" : "=r"(r) : "f"(y0), "f"(y1), "f"(y2), "f"(y3));
+  } else {
+    asm("{\n\t.reg .b16 lo, hi;\n\tcvt.rn.satfinite.e5m2x2.f32 lo, %2, %1;\n\tcvt.rn.satfinite.e5m2x2.f32 hi, %4, %3;\n\t"
+        "mov.b32 %0, {lo, hi};\n\t}" : "=r"(r) : "f"(y0), "f"(y1), "f"(y2), "f"(y3));
+  }
+  return r;
+}
 
 template <typename T>
-__global__ void __launch_bounds__(kQuantThreads) quant_mx_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantParams p) {
   __shared__ __align__(16) uint8_t sf8[512];
   __shared__ __align__(16) uint8_t sf4[512];
   const int tile_l = blockIdx.x, tile_d = blockIdx.y, bh = blockIdx.z;
@@ -90,16 +122,18 @@ __global__ void __launch_bounds__(kQuantThreads) quant_mx_kernel(const QuantPara
   const bool want4 = p.fp4_codes_unpacked || p.fp4_codes_packed || p.fp4_scales_rm || p.fp4_scales_tiled;
 
   // padding of the scale tile: rows beyond L and k-blocks beyond D carry E8M0 1.0
-  reinterpret_cast<uint16_t*>(sf8)[tid] = 0x7f7f;
-  reinterpret_cast<uint16_t*>(sf4)[tid] = 0x7f7f;
+  if (tid < 256) {
+    reinterpret_cast<uint16_t*>(sf8)[tid] = 0x7f7f;
+    reinterpret_cast<uint16_t*>(sf4)[tid] = 0x7f7f;
+  }
   __syncthreads();
 
   const T* xb = reinterpret_cast<const T*>(p.x) + (long long)b * p.xs_b + (long long)h * p.xs_h;
-  float v[kRunsPerThread][16];
-  bool live[kRunsPerThread];
+  float v[kMxRuns][16];
+  bool live[kMxRuns];
 #pragma unroll
-  for (int i = 0; i < kRunsPerThread; ++i) {
-    const int g = tid + i * kQuantThreads;      // run index inside the tile
+  for (int i = 0; i < kMxRuns; ++i) {
+    const int g = tid + i * kMxThreads;         // run index inside the tile
     const int r = row0 + (g >> 3), c = col0 + (g & 7) * 16;
     live[i] = (r < p.L) && (c < p.D);
     if (live[i]) {
@@ -110,17 +144,19 @@ __global__ void __launch_bounds__(kQuantThreads) quant_mx_kernel(const QuantPara
     }
   }
   const int nblk = p.D >> 5;
+  const bool scaled = (p.s != 1.0f);
 #pragma unroll
-  for (int i = 0; i < kRunsPerThread; ++i) {
-    const int g = tid + i * kQuantThreads;
+  for (int i = 0; i < kMxRuns; ++i) {
+    const int g = tid + i * kMxThreads;
     const int rl = g >> 3;                  // row inside the tile
     const int r = row0 + rl, c = col0 + (g & 7) * 16;
     float amax = 0.0f;
+    if (scaled) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      v[i][j] = __fmul_rn(v[i][j], p.s);
-      amax = fmaxf(amax, fabsf(v[i][j]));
+      for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(v[i][j], p.s);
     }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     if (!live[i]) continue;
     const int kb = c >> 5;                  // 32-element block index along D
@@ -128,18 +164,20 @@ __global__ void __launch_bounds__(kQuantThreads) quant_mx_kernel(const QuantPara
     const bool writer = (tid & 1) == 0;
     const long long row_lin = ((long long)b * p.H + h) * p.L + r;
     if (want8) {
-      BlockScale bs = mx_block_scale(amax, p.fp8_fmt == FMT_FP8_E4M3 ? 8 : 7);
+      const BlockScale bs = mx_block_scale(amax, p.fp8_fmt == FMT_FP8_E4M3 ? 8 : 7);
       uint32_t w[4];
+      if (bs.zero) {
+        w[0] = w[1] = w[2] = w[3] = 0;        // the reference stores the NaN pattern of 0/0 here
+      } else if (p.fp8_fmt == FMT_FP8_E4M3) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t c0 = 0, c1 = 0, c2 = 0, c3 = 0;
-        if (!bs.zero) {
-          c0 = fp8_code(v[i][4 * j + 0] * bs.inv_scale, p.fp8_fmt);
-          c1 = fp8_code(v[i][4 * j + 1] * bs.inv_scale, p.fp8_fmt);
-          c2 = fp8_code(v[i][4 * j + 2] * bs.inv_scale, p.fp8_fmt);
-          c3 = fp8_code(v[i][4 * j + 3] * bs.inv_scale, p.fp8_fmt);
-        }
-        w[j] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+        for (int j = 0; j < 4; ++j)
+          w[j] = cvt_fp8x4_regs<true>(v[i][4 * j] * bs.inv_scale, v[i][4 * j + 1] * bs.inv_scale,
+                                      v[i][4 * j + 2] * bs.inv_scale, v[i][4 * j + 3] * bs.inv_scale);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          w[j] = cvt_fp8x4_regs<false>(v[i][4 * j] * bs.inv_scale, v[i][4 * j + 1] * bs.inv_scale,
+                                       v[i][4 * j + 2] * bs.inv_scale, v[i][4 * j + 3] * bs.inv_scale);
       }
       if (p.fp8_codes) {
         uint8_t* o = p.fp8_codes + (long long)b * p.o8_b + (long long)h * p.o8_h + (long long)r * p.o8_l + c;
@@ -151,30 +189,26 @@ __global__ void __launch_bounds__(kQuantThreads) quant_mx_kernel(const QuantPara
       }
     }
     if (want4) {
-      BlockScale bs = mx_block_scale(amax, 3);
-      uint32_t code[16];
+      const BlockScale bs = mx_block_scale(amax, 3);
+      uint32_t lo, hi;                         // 8 nibbles each, element 0 in the low nibble
+      if (bs.zero) {
+        lo = hi = 0x88888888u;                 // 0/0 in the reference: sign 1, exponent 0, mantissa 0
+      } else {
+        float y[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        float y = v[i][j] * bs.inv_scale;
-        y = fminf(fmaxf(y, -6.0f), 6.0f);
-        code[j] = bs.zero ? 8u : fp4_code_ref(y);
+        for (int j = 0; j < 16; ++j) y[j] = fp4_snap_ref(v[i][j] * bs.inv_scale);
+        lo = cvt_e2m1x8_regs(y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]);
+        hi = cvt_e2m1x8_regs(y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]);
       }
       if (p.fp4_codes_unpacked) {
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          w[j] = code[4 * j] | (code[4 * j + 1] << 8) | (code[4 * j + 2] << 16) | (code[4 * j + 3] << 24);
+        const uint32_t le = lo & 0x0f0f0f0fu, lod = (lo >> 4) & 0x0f0f0f0fu;
+        const uint32_t he = hi & 0x0f0f0f0fu, hod = (hi >> 4) & 0x0f0f0f0fu;
         uint8_t* o = p.fp4_codes_unpacked + (long long)b * p.o4_b + (long long)h * p.o4_h +
                      (long long)r * p.o4_l + c;
-        *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(o) = make_uint4(__byte_perm(le, lod, 0x5140), __byte_perm(le, lod, 0x7362),
+                                                  __byte_perm(he, hod, 0x5140), __byte_perm(he, hod, 0x7362));
       }
       if (p.fp4_codes_packed) {
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          lo |= code[j] << (4 * j);
-          hi |= code[8 + j] << (4 * j);
-        }
         uint8_t* o = p.fp4_codes_packed + row_lin * (p.D >> 1) + (c >> 1);
         *reinterpret_cast<uint2*>(o) = make_uint2(lo, hi);
       }
@@ -473,9 +507,9 @@ extern "C" int mpsa_quant_mx(const void* x, int in_dtype, int B, int H, int L, i
   dim3 grid((L + 127) / 128, (D + 127) / 128, B * H);
   if (grid.y > 65535 || grid.z > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "quant_mx: B*H and D/128 must be below 65536");
   cudaStream_t st = (cudaStream_t)stream;
-  if (in_dtype == 0) quant_mx_kernel<__nv_bfloat16><<<grid, kQuantThreads, 0, st>>>(p);
-  else if (in_dtype == 1) quant_mx_kernel<__half><<<grid, kQuantThreads, 0, st>>>(p);
-  else quant_mx_kernel<float><<<grid, kQuantThreads, 0, st>>>(p);
+  if (in_dtype == 0) quant_mx_kernel<__nv_bfloat16><<<grid, kMxThreads, 0, st>>>(p);
+  else if (in_dtype == 1) quant_mx_kernel<__half><<<grid, kMxThreads, 0, st>>>(p);
+  else quant_mx_kernel<float><<<grid, kMxThreads, 0, st>>>(p);
   return check_launch("quant_mx");
 }
 

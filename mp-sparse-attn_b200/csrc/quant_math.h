@@ -31,6 +31,14 @@ MPSA_HD float bits_to_float(uint32_t b) {
 #endif
 }
 
+MPSA_HD uint32_t float_to_bits_early(float f) {
+#if defined(__CUDA_ARCH__)
+  return __float_as_uint(f);
+#else
+  union { uint32_t u; float f; } c; c.f = f; return c.u;
+#endif
+}
+
 // Result of the shared-exponent step for one block.
 struct BlockScale {
   float inv_scale;   // 2^-shared_exp (exact); elements are multiplied by it
@@ -49,7 +57,11 @@ MPSA_HD BlockScale mx_block_scale(float amax, int emax) {
   // floor(log2f(amax)) with the accurate library log2f, as the reference's tl.log2 does.  This is
   // the exponent field of amax except for the one or two largest mantissa codes below a power of
   // two, where the correctly rounded logarithm already equals the next integer.
-  int e = (int)floorf(log2f(amax));
+  // The library call is only needed for those codes (and for subnormals); elsewhere the exponent
+  // field is the answer.
+  const uint32_t ab = float_to_bits_early(amax);
+  const uint32_t ef = ab >> 23, mant = ab & 0x007fffffu;
+  int e = (ef == 0 || ef == 255 || mant >= 0x007fff00u) ? (int)floorf(log2f(amax)) : (int)ef - 127;
   int sh = e - emax;
   if (sh < -126) sh = -126;
   if (sh > 126) sh = 126;
@@ -71,6 +83,29 @@ MPSA_HD uint32_t fp4_code_ref(float y) {
                (uint32_t)(a > 5.0f);
   uint32_t s = (y >= 0.0f) ? 0u : 8u;
   return s | m;
+}
+
+MPSA_HD uint32_t float_to_bits(float f) {
+#if defined(__CUDA_ARCH__)
+  return __float_as_uint(f);
+#else
+  union { uint32_t u; float f; } c; c.f = f; return c.u;
+#endif
+}
+
+// The reference's E2M1 rule as a snap to the grid: returns the (signed) E2M1-representable value whose
+// code fp4_code_ref(y) would produce, so that ANY exact float -> E2M1 converter (the hardware cvt on the
+// device, fp4_code_rne on the host) yields the reference's code.  |y| >= 1: keep the exponent, mantissa
+// becomes .5 iff it exceeded .25 (ours/quant_mxint8.py:326-328); |y| < 1: 0.5 iff |y| > 0.125 (:328 with
+// exp == 0); sign bit iff y < 0 (the reference tests y >= 0, so -0.0 counts as positive, :318).
+MPSA_HD float fp4_snap_ref(float y) {
+  y = y + 0.0f;                                   // -0.0 -> +0.0
+  const uint32_t u = float_to_bits(y);
+  const uint32_t s = u & 0x80000000u, au = u & 0x7fffffffu;
+  uint32_t r;
+  if (au >= 0x3f800000u) r = (au & 0x7f800000u) | (((au & 0x007fffffu) > 0x00200000u) ? 0x00400000u : 0u);
+  else r = (au > 0x3e000000u) ? 0x3f000000u : 0u;
+  return bits_to_float(s | r);
 }
 
 // E2M1 round-to-nearest-even, saturating (OCP MX rule; ours/mxfp.py:84-170).  Used where no

@@ -264,7 +264,7 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
 def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, B: int, Hq: int,
                                 Hkv: int, S: int, Skv: int, D: int, *, causal: bool, band: int = 1,
                                 prec_map: Optional[torch.Tensor] = None, uniform: Optional[str] = None,
-                                out_dtype: torch.dtype = torch.bfloat16, check: bool = False) -> torch.Tensor:
+                                out_dtype: torch.dtype = torch.bfloat16, check: bool = False, return_lse: bool = False):
     """The fused forward on operands that are already quantised (depth padded to 128) and a V^T from
     prepare_vt (fp16 P.V) or a QuantizedV from quantize_v_seq (quantised P.V).  Both formats of Q and K
     must be present unless `uniform` restricts the map to one."""
@@ -323,17 +323,36 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
     if (qq.fp4 is None or kq.fp4 is None) and uniform != "fp8":
         raise ValueError("MXFP4 operands missing but the precision map may select FP4 tiles")
     out = torch.empty((B, Hq, S, D), dtype=out_dtype, device=dev)
+    lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev) if return_lse else None
     st = status_word(dev)
     with torch.cuda.device(dev):
         rc = _lib.load().mpsa_attn_fwd(
             q8.data_ptr(), q8s.data_ptr(), q4.data_ptr(), q4s.data_ptr(),
             k8.data_ptr(), k8s.data_ptr(), k4.data_ptr(), k4s.data_ptr(),
-            *vptrs, prec_map.data_ptr(), msb, msh, out.data_ptr(), _OUT_DTYPE[out_dtype],
+            *vptrs, prec_map.data_ptr(), msb, msh, out.data_ptr(), _OUT_DTYPE[out_dtype], _ptr(lse),
             B, Hq, Hkv, S, Skv, D, skv_pad, int(causal), _FP8_DESC[qq.fp8_elem], st.data_ptr(), _stream())
     _lib.check(rc)
     if check:
         check_status(dev)
-    return out
+    return (out, lse) if return_lse else out
+
+
+def attention_merge(acc: torch.Tensor, lse_acc: torch.Tensor, part: torch.Tensor, lse_part: torch.Tensor) -> None:
+    """In-place merge of a partial attention result (part, lse_part) into (acc fp32, lse_acc): the result is
+    the softmax-weighted combination over the union of the two key sets."""
+    _require_cuda(acc, lse_acc, part, lse_part)
+    D = acc.shape[-1]
+    rows = acc.numel() // D
+    if acc.dtype != torch.float32 or lse_acc.dtype != torch.float32 or lse_part.dtype != torch.float32:
+        raise ValueError("accumulator and lse tensors must be fp32")
+    if part.shape != acc.shape or lse_acc.numel() != rows or lse_part.numel() != rows:
+        raise ValueError("shape mismatch between accumulator and partial result")
+    if not (acc.is_contiguous() and part.is_contiguous() and lse_acc.is_contiguous() and lse_part.is_contiguous()):
+        raise ValueError("attention_merge needs contiguous tensors")
+    with torch.cuda.device(acc.device):
+        rc = _lib.load().mpsa_attn_merge(acc.data_ptr(), lse_acc.data_ptr(), part.data_ptr(), _OUT_DTYPE[part.dtype],
+                                         lse_part.data_ptr(), rows, D, _stream())
+    _lib.check(rc)
 
 
 def diagonal_tiled_attention(q, k, v, causal=True, pv_mode="requant"):

@@ -29,7 +29,10 @@ extern "C" void host_quant_mx(const uint16_t* x, long long rows, int d, float s,
       fp8_scale[r * (d / 32) + kb] = b8.code;
       for (int i = 0; i < 32; ++i) {
         float y4 = fminf(fmaxf(v[i] * b4.inv_scale, -6.0f), 6.0f);
-        fp4[r * d + kb * 32 + i] = b4.zero ? 8 : (uint8_t)fp4_code_ref(y4);
+        const uint8_t direct = (uint8_t)fp4_code_ref(y4);
+        // the kernels snap to the grid and convert with the hardware; both routes must agree
+        const uint8_t snapped = (uint8_t)fp4_code_rne(fp4_snap_ref(v[i] * b4.inv_scale));
+        fp4[r * d + kb * 32 + i] = b4.zero ? 8 : (direct == snapped ? direct : 0xEE);
         fp8[r * d + kb * 32 + i] = b8.zero ? 0 : (uint8_t)fp8_code(v[i] * b8.inv_scale, fp8_fmt);
       }
     }

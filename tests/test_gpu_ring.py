@@ -1,0 +1,56 @@
+"""Sequence-parallel ring on real GPUs (one process per GPU, NCCL): each rank's output slice must equal the
+single-GPU fused forward on the whole sequence.  Needs at least two GPUs."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, layout, S, ret):
+    for p in (ROOT, os.path.join(ROOT, "mp-sparse-attn_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+    import mpsa
+    from mpsa.ring import RingSchedule, ring_attention
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        g = torch.Generator().manual_seed(4)
+        B, Hq, Hkv, D = 1, 8, 2, 128
+        q = torch.randn(B, Hq, S, D, generator=g).to(torch.bfloat16).cuda()
+        k = torch.randn(B, Hkv, S, D, generator=g).to(torch.bfloat16).cuda()
+        v = torch.randn(B, Hkv, S, D, generator=g).to(torch.bfloat16).cuda()
+        full = mpsa.attention_forward(q, k, v, causal=True, pv_mode="requant", out_dtype=torch.float32, check=True)
+        sched = RingSchedule(world, rank, layout, True)
+        rows = S // sched.n_blocks
+        take = lambda t: torch.cat([t[:, :, b * rows:(b + 1) * rows] for b in sched.my_blocks], dim=2).contiguous()
+        out = ring_attention(take(q), take(k), take(v), causal=True, layout=layout, out_dtype=torch.float32)
+        mpsa.check_status()
+        ref = take(full)
+        ret[rank] = float((out - ref).norm() / ref.norm())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
+def test_ring_equals_single_gpu(layout):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    ret = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), layout, 2048, ret), nprocs=world, join=True)
+    assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)

@@ -1,0 +1,133 @@
+"""Host-side logic of the sequence-parallel ring on CPU: the schedule, and the ring loop itself run as
+gloo ranks with a reference backend (plain fp32 attention per block pair) in place of the CUDA kernels."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mpsa.ring import DIAG, FULL, RingSchedule, ring_attention
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_schedule_covers_the_causal_triangle_once(world, layout):
+    seen = {}
+    units = []
+    for r in range(world):
+        s = RingSchedule(world, r, layout, True)
+        assert s.source_at(0) == r and sorted(s.source_at(i) for i in range(world)) == list(range(world))
+        for step in range(world):
+            src = s.source_at(step)
+            for qi, ki, kind in s.pairs_at(step):
+                qb, kb = s.my_blocks[qi], s.blocks_of(src)[ki]
+                assert (qb, kb) not in seen
+                seen[(qb, kb)] = kind
+                assert (kind == DIAG) == (qb == kb) and kb <= qb
+        units.append(s.work_units())
+    n = RingSchedule(world, 0, layout, True).n_blocks
+    assert len(seen) == n * (n + 1) // 2
+    if layout == "zigzag":
+        assert max(units) == min(units)              # balanced
+    else:
+        assert units == [r + 0.5 for r in range(world)]
+    # non-causal: every pair, all of kind FULL
+    s = RingSchedule(world, 0, layout, False)
+    assert all(kind == FULL for step in range(world) for _, _, kind in s.pairs_at(step))
+
+
+class RefBackend:
+    """fp32 attention per (query block, key block) with the log2 denominator, and the merge in torch."""
+
+    def __init__(self, rows, D):
+        self.rows, self.D = rows, D
+
+    def prepare_q(self, qb):
+        return qb.float() * (self.D ** -0.5 * 1.4426950408889634)
+
+    def prepare_kv(self, kb, vb):
+        pay = torch.cat([kb.float().reshape(-1), vb.float().reshape(-1)])
+        return (kb.float(), vb.float()), pay
+
+    def split_payload(self, payload, n):
+        return list(payload.chunk(n))
+
+    def partial(self, qq, local_kv, payload, kind):
+        half = payload.numel() // 2
+        B, H = qq.shape[:2]
+        k = payload[:half].view(B, H, self.rows, self.D)
+        v = payload[half:].view(B, H, self.rows, self.D)
+        s = qq @ k.transpose(-1, -2)
+        if kind == DIAG:
+            s = s.masked_fill(torch.triu(torch.ones(self.rows, self.rows, dtype=torch.bool), 1), float("-inf"))
+        m = s.amax(-1, keepdim=True)
+        p = torch.exp2(s - m)
+        l = p.sum(-1, keepdim=True)
+        return (p @ v) / l, (m + torch.log2(l)).squeeze(-1)
+
+    def new_accumulator(self):
+        return None, None
+
+    def merge(self, acc, lse_acc, o, lse):
+        raise NotImplementedError
+
+
+class MergingRefBackend(RefBackend):
+    def __init__(self, rows, D, B, H):
+        super().__init__(rows, D)
+        self.B, self.H = B, H
+
+    def new_accumulator(self):
+        return (torch.zeros(self.B, self.H, self.rows, self.D), torch.full((self.B, self.H, self.rows), float("-inf")))
+
+    def merge(self, acc, lse_acc, o, lse):
+        lm = torch.maximum(lse_acc, lse)
+        wa, wb = torch.exp2(lse_acc - lm), torch.exp2(lse - lm)
+        wa, wb = torch.nan_to_num(wa), torch.nan_to_num(wb)
+        tot = wa + wb
+        acc.copy_(acc * (wa / tot).unsqueeze(-1) + o * (wb / tot).unsqueeze(-1))
+        lse_acc.copy_(lm + torch.log2(tot))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, layout, causal, q, k, v, ref, ret):
+    sys.path.insert(0, os.path.join(os.path.dirname(HERE), "mp-sparse-attn_b200"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sched = RingSchedule(world, rank, layout, causal)
+        S = q.shape[2]
+        rows = S // sched.n_blocks
+        take = lambda t: torch.cat([t[:, :, b * rows:(b + 1) * rows] for b in sched.my_blocks], dim=2)
+        out = ring_attention(take(q), take(k), take(v), causal=causal, layout=layout,
+                             backend=MergingRefBackend(rows, q.shape[-1], q.shape[0], q.shape[1]), out_dtype=torch.float32)
+        err = float((out - take(ref)).abs().max())
+        ret[rank] = err
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,layout,causal", [(2, "contiguous", True), (2, "zigzag", True), (4, "zigzag", True),
+                                                 (3, "contiguous", False)])
+def test_ring_matches_single_process_attention(world, layout, causal):
+    g = torch.Generator().manual_seed(3)
+    B, H, D = 1, 2, 16
+    S = 24 * world
+    q, k, v = (torch.randn(B, H, S, D, generator=g) for _ in range(3))
+    s = (q @ k.transpose(-1, -2)) * D ** -0.5
+    if causal:
+        s = s.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool), 1), float("-inf"))
+    ref = torch.softmax(s, -1) @ v
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), layout, causal, q, k, v, ref, ret), nprocs=world, join=True)
+    assert len(ret) == world and max(ret.values()) < 1e-5, dict(ret)
