@@ -120,7 +120,7 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    S, K, W = args.seq, args.steps, args.warmup
+    S, K, W = args.seq or 32768, args.steps, args.warmup
     q, k, v = make_inputs_device(2 + rank, S, dev)
 
     def step():
@@ -269,7 +269,7 @@ def run_ring(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29533")
         dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
-    S = 131072 if args.seq == 32768 else args.seq
+    S = args.seq or 131072
     sched = RingSchedule(world, rank, args.layout, True)
     s_local = S // world
     g = torch.Generator(device=dev).manual_seed(4 + rank)
@@ -346,7 +346,7 @@ def run_reference(args):
         "unit": "TFLOP/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(base["seconds"] * 1e3, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "mxfp8/mxfp4 emulated in fp32", "data": "synthetic",
-        "config": {"workload": f"cfg3 causal prefill B=1 Hq=32 Hkv=8 D=128 S={args.seq} (bounded sample, see cpu_baseline.sample)"},
+        "config": {"workload": f"cfg3 causal prefill B=1 Hq=32 Hkv=8 D=128 S={args.seq or 32768} (bounded sample, see cpu_baseline.sample)"},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -359,7 +359,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--seq", type=int, default=32768)
+    ap.add_argument("--seq", type=int, default=None, help="sequence length (default 32768; 131072 for --workload ring)")
     ap.add_argument("--workload", default="prefill", choices=["prefill", "ring"],
                     help="prefill: the headline single-GPU workload replicated per GPU; ring: S=131072 causal, "
                          "sequence-sharded over the GPUs (strong scaling)")

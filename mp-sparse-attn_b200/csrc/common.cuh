@@ -1,5 +1,5 @@
-// Shared device-side building blocks for the sm_100a kernels: mbarrier, TMA (bulk and tiled,
-// never multicast), tcgen05 (TMEM allocation, block-scaled MMA, scale-factor copy, loads and
+// Shared device-side building blocks for the sm_100a kernels: mbarrier, TMA (bulk and tiled, each
+// CTA fetching its own tiles), tcgen05 (TMEM allocation, block-scaled MMA, scale-factor copy, loads and
 // stores) and the descriptors they consume.  Every wait has an upper bound: when it expires the
 // waiter records a code in a global status word and the kernel unwinds normally.
 #pragma once
