@@ -99,6 +99,24 @@ int mpsa_quant_v_seq(const void* v, int in_dtype, int B, int H, int Skv, int D, 
  * ours/online_routing.py:68-77. */
 int mpsa_route_band(void* map, int nq, int nk, int tile, int causal, int band, int S, int Skv, void* stream);
 
+/* Router statistic of every visible 128 x 128 score tile, computed from the MXFP4 operands:
+ * stat[b,h,i,j] = mean over the query rows of the row maximum of S = Q4.K4^T (log2 domain, the softmax
+ * scale is already folded into Q by the quantizer).  This is the quantity the reference's kernels compute
+ * per tile as `sum(max(qk, 1)) / BLOCK_M` (ours/mxfp_attn_kernel.py:272-280, ours/online_routing.py:87-112).
+ * Keys beyond Skv and, with causal != 0, keys above the query are left out of the row maximum; a row with no
+ * visible key in the tile counts as 0.  Cells of tiles entirely above the causal diagonal are not written.
+ *   q4,k4 packed MXFP4 codes [B,H,L,64]; q4_sf,k4_sf tiled scales [B,H,ceil(L/128),512] (from mpsa_quant_mx)
+ *   stat  float32 [B,Hq,ceil(S/128),ceil(Skv/128)];  status: device int32, stays 0 unless a wait expired. */
+int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4, const void* k4_sf, void* stat, int B, int Hq,
+                    int Hkv, int S, int Skv, int causal, int* status, void* stream);
+
+/* Online precision map uint8 [B,Hq,nq,nk] (128 x 128 cells) from the statistic above: SKIP above the causal
+ * diagonal, FP8 within `band` tiles of the diagonal, and elsewhere FP8 iff stat[i,j] >= stat[i,0] * tau, else
+ * FP4.  The first key tile is the reference row statistic ("sink"), as in ours/mxfp_attn_kernel.py:272-276,
+ * where the same comparison (with skip_thresh) is meant to drop tiles; here it promotes their precision. */
+int mpsa_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv, int causal, int band, float tau,
+                      void* stream);
+
 /* Fused attention forward.  Replaces block_scaled_batched_attn (ours/mxfp_attn_kernel.py:362-423)
  * and its kernel (:103-359).
  *   q8/q4, k8/k4   codes from mpsa_quant_mx with D padded to 128: fp8 [B,H,L,128], fp4 packed [B,H,L,64]

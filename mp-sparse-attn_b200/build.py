@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "mpsa", "libmpsa.so")
-SOURCES = ["api.cu", "quant.cu", "gemm.cu", "attn.cu"]
+SOURCES = ["api.cu", "quant.cu", "gemm.cu", "attn.cu", "route.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default", "--use_fast_math=false"]
 

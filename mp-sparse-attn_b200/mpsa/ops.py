@@ -227,6 +227,39 @@ def precision_map_band(S: int, Skv: int, causal: bool, band: int = 1, tile: int 
     return m
 
 
+def router_statistic(qq: "QuantizedOperand", kq: "QuantizedOperand", B: int, Hq: int, Hkv: int, S: int, Skv: int,
+                     *, causal: bool, check: bool = False) -> torch.Tensor:
+    """float32 [B,Hq,nq,nk]: mean over the query rows of the row maximum of every visible 128 x 128 tile of
+    the MXFP4 score matrix (ours/mxfp_attn_kernel.py:272-280).  Cells above the causal diagonal hold 0."""
+    if qq.fp4 is None or kq.fp4 is None:
+        raise ValueError("router_statistic needs the MXFP4 form of Q and K")
+    dev = qq.fp4.device
+    nq, nk = -(-S // 128), -(-Skv // 128)
+    stat = torch.zeros((B, Hq, nq, nk), dtype=torch.float32, device=dev)
+    status = status_word(dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().mpsa_route_stat(qq.fp4.data_ptr(), qq.fp4_sf.data_ptr(), kq.fp4.data_ptr(), kq.fp4_sf.data_ptr(),
+                                         stat.data_ptr(), B, Hq, Hkv, S, Skv, int(causal), status.data_ptr(), _stream())
+    _lib.check(rc)
+    if check:
+        check_status(dev)
+    return stat
+
+
+def precision_map_online(stat: torch.Tensor, S: int, Skv: int, *, causal: bool, band: int = 1, tau: float = 1.0) -> torch.Tensor:
+    """uint8 [B,Hq,nq,nk] from router_statistic: band rule, plus FP8 for every other visible tile whose statistic
+    reaches `tau` times that of the row's first key tile."""
+    B, Hq, nq, nk = stat.shape
+    if (nq, nk) != (-(-S // 128), -(-Skv // 128)) or stat.dtype != torch.float32:
+        raise ValueError("stat must be float32 [B, Hq, ceil(S/128), ceil(Skv/128)]")
+    stat = stat.contiguous()
+    m = torch.empty((B, Hq, nq, nk), dtype=torch.uint8, device=stat.device)
+    with torch.cuda.device(stat.device):
+        rc = _lib.load().mpsa_route_online(m.data_ptr(), stat.data_ptr(), B, Hq, S, Skv, int(causal), band, float(tau), _stream())
+    _lib.check(rc)
+    return m
+
+
 def _pad_depth_128(x: torch.Tensor) -> torch.Tensor:
     D = x.shape[-1]
     if D == 128:
@@ -237,9 +270,14 @@ def _pad_depth_128(x: torch.Tensor) -> torch.Tensor:
 def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, band: int = 1,
                       prec_map: Optional[torch.Tensor] = None, uniform: Optional[str] = None,
                       sm_scale: Optional[float] = None, fp8_elem: str = "e5m2",
-                      out_dtype: torch.dtype = torch.bfloat16, pv_mode: str = "fp16", check: bool = False) -> torch.Tensor:
+                      out_dtype: torch.dtype = torch.bfloat16, pv_mode: str = "fp16", check: bool = False,
+                      router: str = "band", tau: float = 1.0) -> torch.Tensor:
     """Quantise Q/K (both MXFP8 and MXFP4 in one pass each), prepare V, build the precision map and
     run the fused forward.  q [B,Hq,S,D], k/v [B,Hkv,Skv,D]; D in {64, 128}.
+
+    router "band": the static diagonal-band map.  router "online": one extra MXFP4 pass over the score tiles
+    (router_statistic) promotes to MXFP8 every tile whose statistic reaches `tau` times that of the row's
+    first key tile (precision_map_online).
 
     pv_mode "fp16": P and V in fp16, the P.V precision of the reference kernel.
     pv_mode "requant": P is re-quantised to the tile's MX format and V is quantised along the sequence."""
@@ -257,6 +295,13 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
         vt = quantize_v_seq(v, fp8_elem)
     else:
         raise ValueError(f"unknown pv_mode {pv_mode!r}")
+    if router == "online":
+        if prec_map is not None or uniform is not None:
+            raise ValueError("router='online' builds its own precision map")
+        stat = router_statistic(qq, kq, B, Hq, Hkv, S, Skv, causal=causal, check=check)
+        prec_map = precision_map_online(stat, S, Skv, causal=causal, band=band, tau=tau)
+    elif router != "band":
+        raise ValueError(f"unknown router {router!r}")
     return attention_forward_quantized(qq, kq, vt, B, Hq, Hkv, S, Skv, D, causal=causal, band=band,
                                        prec_map=prec_map, uniform=uniform, out_dtype=out_dtype, check=check)
 

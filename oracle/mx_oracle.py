@@ -321,6 +321,60 @@ def router_statistic(s_tile: torch.Tensor) -> torch.Tensor:
     return s_tile.amax(dim=-1).sum(dim=-1) / s_tile.shape[-2]
 
 
+def router_statistic_map(q: torch.Tensor, k: torch.Tensor, *, causal: bool, sm_scale: Optional[float] = None,
+                         tile: int = 128) -> torch.Tensor:
+    """float32 [B,Hq,nq,nk]: router_statistic of every visible tile of S = dequant(Q4) @ dequant(K4)^T (the
+    reference quantizer's MXFP4 operands, log2 domain; ours/mxfp_attn_kernel.py:262-280).  Keys beyond the
+    end and, if causal, above the query are left out of the row maximum; a row without a visible key counts
+    as 0; cells entirely above the causal diagonal hold 0.  The masking is this build's: the reference's
+    statistic exists only in its non-causal kernel."""
+    B, Hq, S, D = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    sq = q_side_scale(D, sm_scale)
+    qc, qs = quant_mxfp4_side(q, sq)
+    kc, ks = quant_mxfp4_side(k, 1.0)
+    qd = dequant(qc, qs, "fp4").float()
+    kd = dequant(kc, ks, "fp4").float()
+    nq, nk = -(-S // tile), -(-Skv // tile)
+    off = Skv - S
+    stat = torch.zeros((B, Hq, nq, nk), dtype=torch.float32)
+    rows = torch.arange(S)
+    cols = torch.arange(Skv)
+    vis = (cols[None, :] <= rows[:, None] + off) if causal else torch.ones((S, Skv), dtype=torch.bool)
+    for b in range(B):
+        for h in range(Hq):
+            s = qd[b, h] @ kd[b, h // (Hq // Hkv)].T
+            s = torch.where(vis, s, torch.tensor(float("-inf")))
+            for i in range(nq):
+                r0, r1 = i * tile, min(S, (i + 1) * tile)
+                for j in range(nk):
+                    c0, c1 = j * tile, min(Skv, (j + 1) * tile)
+                    if causal and c0 > (r1 - 1) + off:
+                        continue
+                    mx = s[r0:r1, c0:c1].amax(dim=-1)
+                    mx = torch.where(torch.isinf(mx), torch.zeros_like(mx), mx)
+                    stat[b, h, i, j] = mx.sum() / (r1 - r0)
+    return stat
+
+
+def precision_map_online(stat: torch.Tensor, S: int, Skv: int, *, causal: bool, band: int = 1, tau: float = 1.0,
+                         tile: int = 128) -> torch.Tensor:
+    """uint8 [B,Hq,nq,nk]: the band map, plus FP8 for every other visible tile with
+    stat[i,j] >= stat[i,0] * tau (first key tile = the reference statistic, ours/mxfp_attn_kernel.py:272-276)."""
+    B, Hq, nq, nk = stat.shape
+    base = precision_map_band(nq, nk, causal, band, (Skv - S) // tile)
+    if causal:
+        # tiles the (end-aligned, possibly ragged) diagonal leaves entirely masked
+        i = torch.arange(nq)[:, None]
+        j = torch.arange(nk)[None, :]
+        last_q = torch.clamp((i + 1) * tile - 1, max=S - 1)
+        base = torch.where(j * tile > last_q + (Skv - S), torch.tensor(TILE_SKIP, dtype=torch.uint8), base)
+    promote = stat >= stat[..., :1] * tau
+    m = base.expand(B, Hq, nq, nk).clone()
+    m[(m == TILE_FP4) & promote] = TILE_FP8
+    return m
+
+
 # --------------------------------------------------------------------------------------
 # V operand preparation for P.V (sequence-axis blocks; PARITY UNPINNED)
 # --------------------------------------------------------------------------------------
