@@ -4,9 +4,10 @@
 
 Workload (N=1): causal prefill attention shaped like a Llama-3-8B layer - B=1, Hq=32, Hkv=8,
 D=128, S=32768, bf16 inputs N(0,1) with 5 of the 128 K channels scaled x20, diagonal tiles in
-MXFP8 and the rest in MXFP4, P re-quantised to the tile's format before P.V (V quantised along the
-sequence).  One step = quantise Q and K (both formats, one pass each), quantise V, build the
-precision map and run the fused forward.  Metric: effective attention TFLOP/s =
+MXFP8 and the rest in MXFP4 unless the online router promotes them (statistic of the MXFP4 score tile >=
+TAU x that of the row's first key tile), P re-quantised to the tile's format before P.V (V quantised along
+the sequence).  One step = quantise Q and K (both formats, one pass each), quantise V, compute the router
+statistic, build the precision map and run the fused forward.  Metric: effective attention TFLOP/s =
 4*B*Hq*S^2*D/2 / time.  With N > 1 every rank runs the same workload on its own batch element
 (batch x head sharding, no collective; weak scaling) and the value is the sum over ranks divided by
 the slowest rank's time.
@@ -32,7 +33,11 @@ import torch  # noqa: E402
 
 HQ, HKV, D = 32, 8, 128
 OUTLIERS = 5
-LAUNCHES_PER_STEP = 5      # quant Q, quant K, quant V, precision map, fused forward
+LAUNCHES_PER_STEP = 6      # quant Q, quant K, quant V, router statistic, precision map, fused forward
+TAU = 1.1                  # online router: a tile is promoted to MXFP8 iff its statistic >= TAU x the first key tile's
+# DRAM bytes (read + written) of one launch of the fused forward at S=8192 from an ncu capture
+# (profiles/attn_fwd_requant_cfg3_S8192.md); every term of it grows linearly with S
+ATTN_TRAFFIC_BYTES_S8192 = 105_559_040
 
 
 def attn_flops(B, Hq, S, Dh, causal=True):
@@ -124,7 +129,8 @@ def run_ours(args):
     q, k, v = make_inputs_device(2 + rank, S, dev)
 
     def step():
-        return mpsa.attention_forward(q, k, v, causal=True, out_dtype=torch.bfloat16, pv_mode="requant")
+        return mpsa.attention_forward(q, k, v, causal=True, out_dtype=torch.bfloat16, pv_mode="requant",
+                                      router="online", tau=TAU)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -152,7 +158,26 @@ def run_ours(args):
     # ---- dominant kernel alone (fused forward), operands already quantised -------------
     sq = mpsa.ops.q_side_scale(D)
     qq, kq = mpsa.quantize_mx(q, sq), mpsa.quantize_mx(k, 1.0)
-    pm = mpsa.precision_map_band(S, S, True, 1, 128, dev)
+    stat = mpsa.router_statistic(qq, kq, 1, HQ, HKV, S, S, causal=True)
+    pm = mpsa.precision_map_online(stat, S, S, causal=True, band=1, tau=TAU)
+    n_fp8 = int((pm == mpsa.TILE_FP8).sum())
+    n_fp4 = int((pm == mpsa.TILE_FP4).sum())
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(K):
+            fn()
+        a1.record()
+        torch.cuda.synchronize()
+        return a0.elapsed_time(a1) / K
+
+    route_ms = timed(lambda: mpsa.precision_map_online(mpsa.router_statistic(qq, kq, 1, HQ, HKV, S, S, causal=True),
+                                                       S, S, causal=True, band=1, tau=TAU))
+    del stat
 
     def time_forward(vt):
         for _ in range(2):
@@ -189,7 +214,7 @@ def run_ours(args):
 
     def e2e_step():
         dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
-        o = mxfp_attn_kernel(dq, dk, dv, is_causal=True, block_scale_type="diag_requant", output_dtype=torch.bfloat16)
+        o = mxfp_attn_kernel(dq, dk, dv, is_causal=True, block_scale_type="online_requant", skip_thresh=TAU, output_dtype=torch.bfloat16)
         hout.copy_(o, non_blocking=True)
 
     for _ in range(max(1, min(W, 2))):
@@ -218,24 +243,23 @@ def run_ours(args):
     pk = measured_peaks()
     # blended tensor peak: both products of a diagonal tile at the MXFP8 rate (2x the measured bf16
     # rate), both products of an off-diagonal tile at the MXFP4 rate (4x)
-    nq = S // 128
-    tiles = nq * (nq + 1) // 2
     f_tile = 2.0 * 128 * 128 * D
     base = pk["bf16_sustained"] * 1e12
-    t_peak = HQ * (nq * 2 * f_tile / (2 * base) + (tiles - nq) * 2 * f_tile / (4 * base))
-    executed = HQ * tiles * 2 * f_tile
+    t_peak = n_fp8 * 2 * f_tile / (2 * base) + n_fp4 * 2 * f_tile / (4 * base)
+    executed = (n_fp8 + n_fp4) * 2 * f_tile
     peak_tflops = executed / t_peak / 1e12
     achieved = executed / (attn_ms * 1e-3) / 1e12
     line = {
         "metric": "effective attn TFLOPS, Llama-3-8B shape causal", "value": round(value, 3), "unit": "TFLOP/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8/mxfp4 (fp32 accumulate)", "data": "synthetic",
-        "config": {"workload": f"cfg3 causal prefill B=1 Hq=32 Hkv=8 D=128 S={S} per GPU, diag MXFP8 / off-diag MXFP4, "
-                               "P re-quantised to the tile's format before P.V", "seq_len": S, "l2": "inputs (403 MB per step) larger than L2",
+        "config": {"workload": f"cfg3 causal prefill B=1 Hq=32 Hkv=8 D=128 S={S} per GPU, diag MXFP8 / off-diag MXFP4 with online "
+                               f"promotion to MXFP8 (tau={TAU}), P re-quantised to the tile's format before P.V", "seq_len": S,
+                   "router": {"kind": "online", "tau": TAU, "fp8_tiles": n_fp8, "fp4_tiles": n_fp4, "ms": round(route_ms, 4)}, "l2": "inputs (403 MB per step) larger than L2",
                    "sharding": "batch x head replicas, no collective"},
         "roofline": {"bound": "tensor", "kernel": "attn_fwd_kernel", "achieved": round(achieved, 2),
                      "peak": round(peak_tflops, 1), "unit": "TFLOP/s", "frac": round(achieved / peak_tflops, 4),
-                     "traffic": None, "ms": round(attn_ms, 4), "peak_source": pk["source"] + " bf16 sustained, blended by format",
+                     "traffic": ATTN_TRAFFIC_BYTES_S8192 * S // 8192, "ms": round(attn_ms, 4), "peak_source": pk["source"] + " bf16 sustained, blended by format",
                      "effective_tflops": round(flops_rank / (attn_ms * 1e-3) / 1e12, 2),
                      "fp16_pv_variant": {"ms": round(attn_fp16_ms, 4), "effective_tflops": round(flops_rank / (attn_fp16_ms * 1e-3) / 1e12, 2)},
                      "quantizer": {"bound": "hbm", "achieved": round(HQ * S * D * (2 + 1 + 0.5 + 2 / 32) / (quant_ms * 1e-3) / 1e9, 1),

@@ -104,11 +104,13 @@ int mpsa_route_band(void* map, int nq, int nk, int tile, int causal, int band, i
  * scale is already folded into Q by the quantizer).  This is the quantity the reference's kernels compute
  * per tile as `sum(max(qk, 1)) / BLOCK_M` (ours/mxfp_attn_kernel.py:272-280, ours/online_routing.py:87-112).
  * Keys beyond Skv and, with causal != 0, keys above the query are left out of the row maximum; a row with no
- * visible key in the tile counts as 0.  Cells of tiles entirely above the causal diagonal are not written.
+ * visible key in the tile counts as 0.
  *   q4,k4 packed MXFP4 codes [B,H,L,64]; q4_sf,k4_sf tiled scales [B,H,ceil(L/128),512] (from mpsa_quant_mx)
- *   stat  float32 [B,Hq,ceil(S/128),ceil(Skv/128)];  status: device int32, stays 0 unless a wait expired. */
-int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4, const void* k4_sf, void* stat, int B, int Hq,
-                    int Hkv, int S, int Skv, int causal, int* status, void* stream);
+ *   stat     float32 [B,Hq,ceil(S/128),ceil(Skv/128)], every cell written (0 above the causal diagonal)
+ *   scratch  4 floats per cell of stat (16-byte aligned): the per-warp partial means, added in a fixed order
+ *   status   device int32, stays 0 unless a wait expired. */
+int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4, const void* k4_sf, void* stat, void* scratch,
+                    int B, int Hq, int Hkv, int S, int Skv, int causal, int* status, void* stream);
 
 /* Online precision map uint8 [B,Hq,nq,nk] (128 x 128 cells) from the statistic above: SKIP above the causal
  * diagonal, FP8 within `band` tiles of the diagonal, and elsewhere FP8 iff stat[i,j] >= stat[i,0] * tau, else

@@ -64,12 +64,15 @@ constexpr long long kWaitLimitCycles = 4000000000ll;
 
 // Bounded wait.  Returns false when the limit expired (and records `code` in *status) or when
 // another role already recorded a failure, so that every role unwinds promptly.
+// BACKOFF = false is for pipelines whose phases last a few hundred cycles, where the back-off below would
+// cost more than the wait itself.
+template <bool BACKOFF = true>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
 #if MPSA_WAIT_MODE == 0
   // Reading the global nanosecond timer is slow; doing it once after the first unsuccessful probe
   // doubles as a back-off that keeps a waiting warp out of its scheduler's way.
-  {
+  if (BACKOFF) {
     unsigned long long g0;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g0));
     (void)g0;

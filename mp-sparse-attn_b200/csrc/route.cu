@@ -16,26 +16,42 @@
 
 namespace mpsa {
 
-// 14 K stages: deep prefetch, and more than half of an SM's shared memory, so that one CTA (which takes all 512
+// 12 K stages: deep prefetch, and more than half of an SM's shared memory, so that one CTA (which takes all 512
 // TMEM columns) runs per SM.
-constexpr int RT_BM = 128, RT_BN = 128, RT_KSTAGES = 14;
+constexpr int RT_BM = 128, RT_BN = 128, RT_KSTAGES = 12, RT_MAXH = 2, RT_SBUF = 3;
 constexpr int RT_Q_BYTES = RT_BM * 64, RT_K_BYTES = RT_BN * 64;
-constexpr int RT_OFF_Q = 0;
-constexpr int RT_OFF_K = RT_OFF_Q + RT_Q_BYTES;
-constexpr int RT_OFF_SF = RT_OFF_K + RT_KSTAGES * RT_K_BYTES;      // Q scale tile, then K scale tile per stage
-constexpr int RT_OFF_RED = RT_OFF_SF + (1 + RT_KSTAGES) * 512;     // float [4][4] per-warp partial sums of the last four tiles
-constexpr int RT_OFF_BAR = RT_OFF_RED + 64;
+constexpr int RT_OFF_Q = 0;                                         // Q tiles of the CTA's heads
+constexpr int RT_OFF_K = RT_OFF_Q + RT_MAXH * RT_Q_BYTES;
+constexpr int RT_OFF_SF = RT_OFF_K + RT_KSTAGES * RT_K_BYTES;       // Q scale tile per head, then K scale tile per stage
+constexpr int RT_OFF_BAR = RT_OFF_SF + (RT_MAXH + RT_KSTAGES) * 512;
 constexpr int RT_SMEM = RT_OFF_BAR + 512 + 1024;
-constexpr uint32_t RT_TMEM_COLS = 512, RT_COL_SFQ = 256, RT_COL_SFK = 260;
+// TMEM: three S accumulators (128 columns each), then the scale columns: Q per head, K per issuer x 2
+constexpr uint32_t RT_TMEM_COLS = 512, RT_COL_SFQ = 384, RT_COL_SFK = 392;
 
 struct RouteParams {
-  int B, Hq, Hkv, S, Skv, causal;
+  int B, Hq, Hkv, S, Skv, causal, nh;   // nh: q-heads per CTA (1 or 2; 2 needs an even GQA group)
   const uint8_t* q4_sf; const uint8_t* k4_sf;
-  float* stat;            // [B,Hq,nq,nk]; cells of tiles entirely above the causal diagonal are not written
+  float* part;            // [B,Hq,nq,nk,4] per-warp partial means; cells of tiles above the causal diagonal are not written
   int* status;
 };
 
-__global__ void __launch_bounds__(256, 1)
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// Work of a CTA is a stream of units u = key tile * nh + head.  Unit u uses S accumulator u % 3 and is reduced by
+// warpgroup u & 1 (warps 4-7 / 8-11); with two heads per CTA a K tile is fetched once for both, and each head has
+// its own issuing warp.  A unit's chain (wait, tcgen05.mma, commit, wait, tcgen05.ld, maxima, shuffles) is several
+// times longer than its MMAs, hence three accumulators in flight, two issuers and two reducing warpgroups.
+__global__ void __launch_bounds__(384, 1)
 route_stat_kernel(const __grid_constant__ CUtensorMap tm_q4, const __grid_constant__ CUtensorMap tm_k4,
                   const RouteParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -44,24 +60,27 @@ route_stat_kernel(const __grid_constant__ CUtensorMap tm_q4, const __grid_consta
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;
   uint64_t* k_empty = k_full + RT_KSTAGES;
-  uint64_t* s_full = k_empty + RT_KSTAGES;       // 2
-  uint64_t* s_free = s_full + 2;                 // 2: the statistic warps have read the S buffer
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
-  float* red = reinterpret_cast<float*>(smem + RT_OFF_RED);
+  // One barrier per (reducing warpgroup, accumulator): unit u uses number (u & 1) * 3 + u % 3, phase u / 6, so that
+  // each waiter sees every phase of the barriers it waits on.
+  uint64_t* s_full = k_empty + RT_KSTAGES;       // 2 * RT_SBUF: the unit's MMAs are complete
+  uint64_t* s_free = s_full + 2 * RT_SBUF;       // 2 * RT_SBUF: the four warps of the group have read the accumulator
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2 * RT_SBUF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.S + RT_BM - 1) / RT_BM, nk = (p.Skv + RT_BN - 1) / RT_BN;
-  const int qi = nq - 1 - (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int hk = h / (p.Hq / p.Hkv);
+  const int nh = p.nh;
+  const int qi = nq - 1 - (int)blockIdx.x, h0 = blockIdx.y * nh, b = blockIdx.z;
+  const int hk = h0 / (p.Hq / p.Hkv);
   const int off = p.Skv - p.S;
   // key tiles visible to this query tile (all of them without causality)
   const int last_q = min(p.S - 1, qi * RT_BM + RT_BM - 1);
   const int n_tiles = p.causal ? min(nk, (last_q + off) / RT_BN + 1) : nk;
+  const int n_units = n_tiles * nh;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < RT_KSTAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 4); }
+    for (int s = 0; s < RT_KSTAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], nh); }
+    for (int s = 0; s < 2 * RT_SBUF; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 4); }
     fence_mbar_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, RT_TMEM_COLS);
@@ -76,9 +95,11 @@ route_stat_kernel(const __grid_constant__ CUtensorMap tm_q4, const __grid_consta
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tm_q4); tma_prefetch_desc(&tm_k4);
-      mbar_arrive_expect_tx(q_full, RT_Q_BYTES + 512);
-      tma_load_2d(sQ, &tm_q4, q_full, 0, (b * p.Hq + h) * p.S + qi * RT_BM);
-      bulk_load(sSF, p.q4_sf + ((long long)(b * p.Hq + h) * nq + qi) * 512, 512, q_full);
+      mbar_arrive_expect_tx(q_full, nh * (RT_Q_BYTES + 512));
+      for (int j = 0; j < nh; ++j) {
+        tma_load_2d(sQ + j * RT_Q_BYTES, &tm_q4, q_full, 0, (b * p.Hq + h0 + j) * p.S + qi * RT_BM);
+        bulk_load(sSF + j * 512, p.q4_sf + ((long long)(b * p.Hq + h0 + j) * nq + qi) * 512, 512, q_full);
+      }
       const int k_row0 = (b * p.Hkv + hk) * p.Skv;
       const long long ksf0 = (long long)(b * p.Hkv + hk) * nk * 512;
       bool ok = true;
@@ -89,86 +110,109 @@ route_stat_kernel(const __grid_constant__ CUtensorMap tm_q4, const __grid_consta
         if (!ok) break;
         mbar_arrive_expect_tx(&k_full[s], RT_K_BYTES + 512);
         tma_load_2d(sK + s * RT_K_BYTES, &tm_k4, &k_full[s], 0, k_row0 + t * RT_BN);
-        bulk_load(sSF + (1 + s) * 512, p.k4_sf + ksf0 + (long long)t * 512, 512, &k_full[s]);
+        bulk_load(sSF + (RT_MAXH + s) * 512, p.k4_sf + ksf0 + (long long)t * 512, 512, &k_full[s]);
         issued = t + 1;
       }
-      if (!ok) {
+      if (!ok) {                                 // unwind: let the copies in flight land before the CTA exits
         mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
         for (int t = max(0, issued - RT_KSTAGES); t < issued; ++t)
           mbar_wait(&k_full[t % RT_KSTAGES], (t / RT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
       }
     }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t id0 = idesc_with_sf_id(idesc_block_scaled(1, 1, RT_BM, RT_BN, 1), 0, 0);
-      const uint32_t id1 = idesc_with_sf_id(idesc_block_scaled(1, 1, RT_BM, RT_BN, 1), 2, 2);
-      const uint64_t qd = sdesc_kmajor_sw64(smem_u32(sQ));
-      bool ok = mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
-      if (ok) {
-        tc_fence_after();
-        tc_cp_32x128b_warpx4(tmem + RT_COL_SFQ, sdesc_sf_tile(smem_u32(sSF)));
-      }
-      for (int t = 0; t < n_tiles && ok; ++t) {
-        const int s = t % RT_KSTAGES, bsel = t & 1;
-        ok = mbar_wait(&k_full[s], (t / RT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
-        if (ok && t >= 2) ok = mbar_wait(&s_free[bsel], ((t >> 1) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t sfk = tmem + RT_COL_SFK + bsel * 4;
-        tc_cp_32x128b_warpx4(sfk, sdesc_sf_tile(smem_u32(sSF + (1 + s) * 512)));
-        const uint64_t kd = sdesc_kmajor_sw64(smem_u32(sK + s * RT_K_BYTES));
-        const uint32_t d = tmem + bsel * 128;
-        mma_mxf4(d, qd, kd, id0, tmem + RT_COL_SFQ, sfk, 0);
-        mma_mxf4(d, qd + 2, kd + 2, id1, tmem + RT_COL_SFQ, sfk, 1);
+  } else if (warp == 1 || (warp == 2 && nh == 2)) {
+    // MMA issuer of head j: the whole warp walks the loop, one elected lane issues.
+    const int j = warp - 1;
+    const bool leader = elect_one();
+    const uint32_t id0 = idesc_with_sf_id(idesc_block_scaled(1, 1, RT_BM, RT_BN, 1), 0, 0);
+    const uint32_t id1 = idesc_with_sf_id(idesc_block_scaled(1, 1, RT_BM, RT_BN, 1), 2, 2);
+    const uint64_t qd = sdesc_kmajor_sw64(smem_u32(sQ + j * RT_Q_BYTES));
+    const uint32_t sfq = tmem + RT_COL_SFQ + j * 4;
+    bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA));
+    if (ok) {
+      tc_fence_after();
+      if (leader) tc_cp_32x128b_warpx4(sfq, sdesc_sf_tile(smem_u32(sSF + j * 512)));
+    }
+    for (int t = 0; t < n_tiles && ok; ++t) {
+      const int s = t % RT_KSTAGES;
+      const int u = t * nh + j, bsel = u % RT_SBUF;
+      ok = __all_sync(0xffffffffu, mbar_wait<false>(&k_full[s], (t / RT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t sfk = tmem + RT_COL_SFK + j * 8 + (t & 1) * 4;
+      const uint64_t ksf = sdesc_sf_tile(smem_u32(sSF + (RT_MAXH + s) * 512));
+      if (leader) tc_cp_32x128b_warpx4(sfk, ksf);
+      const uint64_t kd = sdesc_kmajor_sw64(smem_u32(sK + s * RT_K_BYTES));
+      if (u >= RT_SBUF)                          // the accumulator's previous unit, u - 3, has been read
+        ok = __all_sync(0xffffffffu, mbar_wait<false>(&s_free[((u - 3) & 1) * 3 + bsel], ((u - 3) / 6) & 1, p.status, KS_TIMEOUT_PIPE));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d = tmem + bsel * 128;
+      if (leader) {
+        mma_mxf4(d, qd, kd, id0, sfq, sfk, 0);
+        mma_mxf4(d, qd + 2, kd + 2, id1, sfq, sfk, 1);
+        tc_commit(&s_full[(u & 1) * 3 + bsel]);
         tc_commit(&k_empty[s]);
-        tc_commit(&s_full[bsel]);
       }
     }
   } else if (warp >= 4) {
-    const int q = warp & 3;
+    const int q = warp & 3, g = (warp - 4) >> 2;           // TMEM lane quarter, warpgroup
     const int m_glob = qi * RT_BM + q * 32 + lane;
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-    const int valid_rows = min(RT_BM, p.S - qi * RT_BM);
-    float* out = p.stat + ((long long)(b * p.Hq + h) * nq + qi) * nk;
+    const float inv_rows = 1.0f / (float)min(RT_BM, p.S - qi * RT_BM);
+    const bool row_ok = m_glob < p.S;
+    const int lim = p.causal ? min(p.Skv - 1, m_glob + off) : (p.Skv - 1);      // last visible key of this row
+    const int lim_all = p.causal ? min(p.Skv - 1, qi * RT_BM + off) : (p.Skv - 1);  // ... of every row of the tile
     bool ok = true;
-    for (int t = 0; t < n_tiles && ok; ++t) {
-      const int bsel = t & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[bsel], (t >> 1) & 1, p.status, KS_TIMEOUT_MMA));
+    for (int u = g; u < n_units && ok; u += 2) {
+      const int t = u / nh, hh = u - t * nh, bsel = u % RT_SBUF, bar = g * 3 + bsel;
+      ok = __all_sync(0xffffffffu, mbar_wait<false>(&s_full[bar], (u / 6) & 1, p.status, KS_TIMEOUT_MMA));
       if (!ok) break;
       tc_fence_after();
-      float mx = -INFINITY;
       const int n0 = t * RT_BN;
+      // the whole row of the tile goes to registers, so that the accumulator is free again before the arithmetic
+      uint32_t r[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_base + bsel * 128 + c * 32, r[c]);
+      tmem_ld_wait();
+      tc_fence_before();
+      if (lane == 0) mbar_arrive(&s_free[bar]);    // count 4: one per warp of the group
+      float m[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m[i] = -INFINITY;
       // the reference's statistic knows no mask; keys beyond the sequence end (zero padding) and, on
       // the tiles the causal diagonal crosses, keys above the query are left out here
-      const int lim = p.causal ? min(p.Skv - 1, m_glob + off) : (p.Skv - 1);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_base + bsel * 128 + c * 32, r);
-        tmem_ld_wait();
+      if (n0 + RT_BN - 1 <= lim_all) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (n0 + c * 32 + i <= lim) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            m[c * 2 + ((i >> 1) & 1)] = max3(m[c * 2 + ((i >> 1) & 1)], __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (n0 + c * 32 + i <= lim) m[c] = fmaxf(m[c], __uint_as_float(r[c][i]));
       }
-      tc_fence_before();
-      float v = (m_glob < p.S && mx != -INFINITY) ? mx : 0.0f;
+      const float mx = fmaxf(fmaxf(max3(m[0], m[1], m[2]), max3(m[3], m[4], m[5])), fmaxf(m[6], m[7]));
+      float v = (row_ok && mx != -INFINITY) ? mx * inv_rows : 0.0f;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0) {
-        red[(t & 3) * 4 + q] = v;
-        mbar_arrive(&s_free[bsel]);              // S buffer consumed (count 4: one per warp)
-      }
-      // warp 4 (q == 0) adds the four partial sums once all of them are there
-      if (q == 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&s_free[bsel], (t >> 1) & 1, p.status, KS_TIMEOUT_PIPE));
-        if (!ok) break;
-        if (lane == 0) out[t] = (red[(t & 3) * 4] + red[(t & 3) * 4 + 1] + red[(t & 3) * 4 + 2] + red[(t & 3) * 4 + 3]) / (float)valid_rows;
-      }
+      if (lane == 0) p.part[(((long long)(b * p.Hq + h0 + hh) * nq + qi) * nk + t) * 4 + q] = v;
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, RT_TMEM_COLS);
+}
+
+// stat = ((p0 + p1) + p2) + p3: the four per-warp partial means of a tile, added in a fixed order
+__global__ void route_stat_finish_kernel(const float4* part, float* stat, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const float4 v = part[i];
+    stat[i] = ((v.x + v.y) + v.z) + v.w;
+  }
 }
 
 // map[b,h,i,j]: SKIP above the causal diagonal, FP8 inside the band, else FP8 iff stat >= sink * tau, else FP4.
@@ -195,12 +239,12 @@ __global__ void route_online_kernel(uint8_t* map, const float* stat, int nq, int
 
 using namespace mpsa;
 
-extern "C" int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4, const void* k4_sf, void* stat, int B,
-                               int Hq, int Hkv, int S, int Skv, int causal, int* status, void* stream) {
-  if (!q4 || !q4_sf || !k4 || !k4_sf || !stat || !status) return set_error(MPSA_ERR_BAD_ARG, "route_stat: null pointer");
+extern "C" int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4, const void* k4_sf, void* stat,
+                               void* scratch, int B, int Hq, int Hkv, int S, int Skv, int causal, int* status, void* stream) {
+  if (!q4 || !q4_sf || !k4 || !k4_sf || !stat || !scratch || !status) return set_error(MPSA_ERR_BAD_ARG, "route_stat: null pointer");
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || Skv <= 0 || Hq % Hkv) return set_error(MPSA_ERR_BAD_ARG, "route_stat: bad shape");
   if (causal && Skv < S) return set_error(MPSA_ERR_UNSUPPORTED, "route_stat: causal needs Skv >= S");
-  const void* ptrs[] = {q4, q4_sf, k4, k4_sf};
+  const void* ptrs[] = {q4, q4_sf, k4, k4_sf, scratch};
   for (const void* ptr : ptrs)
     if ((uintptr_t)ptr % 16) return set_error(MPSA_ERR_BAD_ARG, "route_stat: tensors must be 16-byte aligned");
   if ((long long)B * Hq * S >= (1ll << 31) || (long long)B * Hkv * Skv >= (1ll << 31))
@@ -211,7 +255,8 @@ extern "C" int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4
     return set_error(MPSA_ERR_LAUNCH, "route_stat: cuTensorMapEncodeTiled failed");
   RouteParams p;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S = S; p.Skv = Skv; p.causal = causal;
-  p.q4_sf = (const uint8_t*)q4_sf; p.k4_sf = (const uint8_t*)k4_sf; p.stat = (float*)stat; p.status = status;
+  p.nh = ((Hq / Hkv) % 2 == 0) ? 2 : 1;
+  p.q4_sf = (const uint8_t*)q4_sf; p.k4_sf = (const uint8_t*)k4_sf; p.part = (float*)scratch; p.status = status;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(route_stat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM) != cudaSuccess)
@@ -219,9 +264,16 @@ extern "C" int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4
     attr_set = true;
   }
   if (Hq > 65535 || B > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "route_stat: Hq and B must be below 65536");
-  dim3 grid((S + RT_BM - 1) / RT_BM, Hq, B);
-  route_stat_kernel<<<grid, 256, RT_SMEM, (cudaStream_t)stream>>>(tq, tk, p);
-  return check_launch("route_stat");
+  const int nq = (S + RT_BM - 1) / RT_BM, nk = (Skv + RT_BN - 1) / RT_BN;
+  const long long cells = (long long)B * Hq * nq * nk;
+  // tiles above the causal diagonal are never visited: their cells read 0
+  if (cudaMemsetAsync(scratch, 0, cells * 16, (cudaStream_t)stream) != cudaSuccess)
+    return set_error(MPSA_ERR_LAUNCH, "route_stat: memset failed");
+  dim3 grid(nq, Hq / p.nh, B);
+  route_stat_kernel<<<grid, 384, RT_SMEM, (cudaStream_t)stream>>>(tq, tk, p);
+  if (int rc = check_launch("route_stat")) return rc;
+  route_stat_finish_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const float4*)scratch, (float*)stat, cells);
+  return check_launch("route_stat_finish");
 }
 
 extern "C" int mpsa_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv, int causal, int band,

@@ -235,11 +235,13 @@ def router_statistic(qq: "QuantizedOperand", kq: "QuantizedOperand", B: int, Hq:
         raise ValueError("router_statistic needs the MXFP4 form of Q and K")
     dev = qq.fp4.device
     nq, nk = -(-S // 128), -(-Skv // 128)
-    stat = torch.zeros((B, Hq, nq, nk), dtype=torch.float32, device=dev)
+    stat = torch.empty((B, Hq, nq, nk), dtype=torch.float32, device=dev)
+    scratch = torch.empty((B, Hq, nq, nk, 4), dtype=torch.float32, device=dev)
     status = status_word(dev)
     with torch.cuda.device(dev):
         rc = _lib.load().mpsa_route_stat(qq.fp4.data_ptr(), qq.fp4_sf.data_ptr(), kq.fp4.data_ptr(), kq.fp4_sf.data_ptr(),
-                                         stat.data_ptr(), B, Hq, Hkv, S, Skv, int(causal), status.data_ptr(), _stream())
+                                         stat.data_ptr(), scratch.data_ptr(), B, Hq, Hkv, S, Skv, int(causal), status.data_ptr(),
+                                         _stream())
     _lib.check(rc)
     if check:
         check_status(dev)

@@ -13,10 +13,13 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
 
     block_scale_type: "mxfp4" / "mxfp8" quantise every tile of Q.K^T to that format (the two modes
     of the reference); "diag" keeps the diagonal tiles in MXFP8 and the rest in MXFP4; "diag_requant"
-    additionally re-quantises P to the tile's format before P.V (V quantised along the sequence).
-    attn_mask, dropout_p, attention_sink, return_sparsity and skip_thresh are accepted and ignored,
-    as in the reference wrapper; is_causal, scale and output_dtype are honoured (the reference
-    ignores them)."""
+    additionally re-quantises P to the tile's format before P.V (V quantised along the sequence);
+    "online" / "online_requant" are the same two with the online router on top of the diagonal rule: a tile
+    is also MXFP8 if its MXFP4 statistic reaches skip_thresh times that of the row's first key tile (the
+    comparison of ours/mxfp_attn_kernel.py:272-280, used here for precision instead of skipping; default 1.1).
+    attn_mask, dropout_p, attention_sink and return_sparsity are accepted and ignored, as in the reference
+    wrapper, and so is skip_thresh outside the online modes; is_causal, scale and output_dtype are honoured
+    (the reference ignores them)."""
     torch.cuda.set_device(v.device)
     if tensor_layout == "NHD":
         q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
@@ -29,12 +32,15 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
     assert q.shape[-1] in [64, 128], "headdim should be in [64, 128]."
     if block_scale_type == "mxfp4":
         uniform = "fp4"
-    elif block_scale_type in ("diag", "diag_requant"):
+    elif block_scale_type in ("diag", "diag_requant", "online", "online_requant"):
         uniform = None
     else:
         uniform = "fp8"
+    online = block_scale_type.startswith("online")
     o = _ops.attention_forward(q, k, v, causal=bool(is_causal), uniform=uniform, sm_scale=scale,
-                               out_dtype=output_dtype, pv_mode="requant" if block_scale_type == "diag_requant" else "fp16")
+                               out_dtype=output_dtype, pv_mode="requant" if block_scale_type.endswith("requant") else "fp16",
+                               router="online" if online else "band",
+                               tau=(1.1 if skip_thresh is None else float(skip_thresh)) if online else 1.0)
     return o.transpose(1, 2) if tensor_layout == "NHD" else o
 
 
