@@ -70,6 +70,14 @@ int mpsa_quant_nvfp4(const void* x, int in_dtype, int rows, int cols, long long 
                      long long scratch_floats, void* codes, long long ldc_bytes, void* scales, void* tensor_scale,
                      void* stream);
 
+/* The same quantizer for an attention operand [B,H,L,D] (strides in elements, innermost contiguous), blocks
+ * along D, ONE tensor scale for the whole operand: codes [B,H,L,D/2], scales [B,H,ceil(L/128),D/64,512] (the
+ * 128-row tiles restart at every head, as mpsa_attn_fwd expects them).  D must be a multiple of 64;
+ * scratch: B*H*ceil(L/128)*ceil(D/512) floats.  No counterpart in the reference. */
+int mpsa_quant_nvfp4_bh(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b, long long xs_h,
+                        long long xs_l, float s, void* scratch, long long scratch_floats, void* codes, void* scales,
+                        void* tensor_scale, void* stream);
+
 /* The same quantizer for callers that cannot allocate device memory (a process whose memory was handed to
  * its own pool at start-up, a plugin barred from the CUDA allocator on its request path, a bare C host):
  * the partial maxima are kept in a 64 KB array built into the library's device image instead of a
@@ -129,6 +137,9 @@ int mpsa_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv
  *   out            [B,Hq,S,D] contiguous
  *   lse            optional fp32 [B,Hq,S]: log2 of each row's softmax denominator (for merging partial results)
  *   fp8_fmt        descriptor format of the fp8 codes: 0 E4M3, 1 E5M2
+ *   fp4_kind       0: the FP4 operands of Q.K^T are MXFP4 (above).  1: NVFP4 from mpsa_quant_nvfp4_bh (q4/k4 the same
+ *                  packed codes, q4_sf/k4_sf [B,H,ceil(L/128),2,512] E4M3 scale tiles); fp4_scale is then the product
+ *                  of the two tensor scales, applied to the scores of the FP4 tiles.  P.V keeps the MX formats.
  *   status         one int32, must be 0 on entry; a kernel whose bounded waits expire stores a
  *                  non-zero code here (1 TMA, 2 MMA, 3 pipeline) and unwinds
  */
@@ -136,7 +147,8 @@ int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void*
                   const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* vt8,
                   const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
                   long long map_sb, long long map_sh, void* out, int out_dtype, void* lse, int B, int Hq, int Hkv,
-                  int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int* status, void* stream);
+                  int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int fp4_kind,
+                  float fp4_scale, int* status, void* stream);
 
 /* Merges a partial attention result into an accumulator: acc fp32 [rows, D] and lse_acc fp32 [rows] are
  * updated in place with part [rows, D] (part_dtype 0 f32, 1 f16, 2 bf16) and lse_part, where every lse is

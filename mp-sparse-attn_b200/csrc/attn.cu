@@ -29,7 +29,7 @@
 // Inside a warpgroup the 128 keys of a tile can further be split over NSPLIT threads per query row,
 // which exchange partial row maxima.  Every thread keeps a partial row sum; the epilogue adds them.
 // TMEM columns: S0/P0 [0,128) S1/P1 [128,256) O [256,384) Q scales [384,392) K scales [392,400)
-// P scales [400,408) V scales [408,416).
+// P scales [400,408) V scales [408,416); with NVFP4 score tiles: Q scales [416,424) K scales [424,440).
 #include "api_internal.h"
 #include "common.cuh"
 #include "tma_host.h"
@@ -49,9 +49,10 @@ constexpr int ATT_OFF_Q8 = 0;
 constexpr int ATT_OFF_Q4 = ATT_OFF_Q8 + ATT_Q8_BYTES;
 constexpr int ATT_OFF_K = ATT_OFF_Q4 + ATT_Q4_BYTES;
 constexpr int ATT_OFF_V = ATT_OFF_K + ATT_KSTAGES * ATT_K_BYTES;
-constexpr int ATT_OFF_SF = ATT_OFF_V + ATT_VSTAGES * ATT_V_BYTES;   // Q8, Q4, K[stages] scale tiles
+constexpr int ATT_OFF_SF = ATT_OFF_V + ATT_VSTAGES * ATT_V_BYTES;   // scale tiles: Q8 (512 B), Q4 (1024), K[stages] (1024 each;
+                                                                    // an NVFP4 operand has two 128x4 tiles per 128 rows)
 constexpr int ATT_MAX_SPLIT = 4, ATT_MAX_WG = 2;
-constexpr int ATT_OFF_PSF = ATT_OFF_SF + (2 + ATT_KSTAGES) * 512;    // P scale tiles [2], V scale tiles [VSTAGES]
+constexpr int ATT_OFF_PSF = ATT_OFF_SF + (3 + 2 * ATT_KSTAGES) * 512;    // P scale tiles [2], V scale tiles [VSTAGES]
 constexpr int ATT_OFF_XMAX = ATT_OFF_PSF + (2 + ATT_VSTAGES) * 512;   // float [WG][2][SPLIT][128] partial row maxima
 constexpr int ATT_OFF_XSUM = ATT_OFF_XMAX + ATT_MAX_WG * 2 * ATT_MAX_SPLIT * 128 * 4;   // float [WG*SPLIT][128] partial sums
 constexpr int ATT_OFF_MROW = ATT_OFF_XSUM + ATT_MAX_WG * ATT_MAX_SPLIT * 128 * 4;       // float [3][128] running row max: per tile parity, and an unsynchronised hint
@@ -62,6 +63,7 @@ constexpr int ATT_SMEM = ATT_OFF_MAP + ATT_MAP_SMEM + 1024;
 constexpr uint32_t ATT_TMEM_COLS = 512;
 constexpr uint32_t ATT_COL_S = 0, ATT_COL_O = 256, ATT_COL_SFQ8 = 384, ATT_COL_SFQ4 = 388, ATT_COL_SFK = 392;
 constexpr uint32_t ATT_COL_SFP = 400, ATT_COL_SFV = 408;
+constexpr uint32_t ATT_COL_SFQN = 416, ATT_COL_SFKN = 424;        // NVFP4 scales: Q 8 columns, K 2 x 8
 constexpr float ATT_RESCALE_LOG2 = 8.0f;
 
 constexpr int TILE_SKIP = 0, TILE_FP8 = 1, TILE_FP4 = 2;
@@ -87,6 +89,7 @@ struct AttnParams {
   const uint8_t* k8_sf; const uint8_t* k4_sf;   // [B,Hkv,nk,512]
   const uint8_t* v8_sf; const uint8_t* v4_sf;   // [B,Hkv,nk,512] (pv_mode 1)
   int pv_mode;                       // 0: P and V in fp16; 1: P and V in the tile's MX format
+  float fp4_scale;                   // NVFP4 score tiles: product of the tensor scales of Q and K
   const uint8_t* map; long long map_sb, map_sh; // [.., nq, nk], strides may be 0 (broadcast)
   void* out; int out_dtype;          // [B,Hq,S,D] contiguous; 0 f32, 1 f16, 2 bf16
   float* lse;                        // optional [B,Hq,S]: log2 of the softmax denominator (incl. the row reference)
@@ -249,7 +252,9 @@ __device__ __forceinline__ uint32_t softmax_block(const uint32_t* sc, float mref
 }
 
 
-template <int NWG, int NSPLIT, int PVQ>
+// NVF4: the FP4 tiles of Q.K^T are NVFP4 (16-element blocks, E4M3 scales, kind::mxf4nvf4) instead of MXFP4; their
+// scores are multiplied by the product of the two tensor scales before the softmax.
+template <int NWG, int NSPLIT, int PVQ, int NVF4>
 __global__ void __launch_bounds__(128 + 128 * NWG * NSPLIT, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant__ CUtensorMap tm_q4,
                 const __grid_constant__ CUtensorMap tm_k8, const __grid_constant__ CUtensorMap tm_k4,
@@ -320,11 +325,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       tma_prefetch_desc(&tm_k4); tma_prefetch_desc(&tm_vt); tma_prefetch_desc(&tm_vt8); tma_prefetch_desc(&tm_vt4);
       const int q_row = (b * p.Hq + h) * p.S + qi * ATT_BM;
       const long long qsf = ((long long)(b * p.Hq + h) * nq + qi) * 512;
-      mbar_arrive_expect_tx(q_full, ATT_Q8_BYTES + ATT_Q4_BYTES + 1024);
+      constexpr int SF4 = NVF4 ? 1024 : 512;       // bytes of FP4 scales per 128 rows
+      mbar_arrive_expect_tx(q_full, ATT_Q8_BYTES + ATT_Q4_BYTES + 512 + SF4);
       tma_load_2d(sQ8, &tm_q8, q_full, 0, q_row);
       tma_load_2d(sQ4, &tm_q4, q_full, 0, q_row);
       bulk_load(sSF, p.q8_sf + qsf, 512, q_full);
-      bulk_load(sSF + 512, p.q4_sf + qsf, 512, q_full);
+      bulk_load(sSF + 512, p.q4_sf + (NVF4 ? 2 * qsf : qsf), SF4, q_full);
 
       const int k_row0 = (b * p.Hkv + hk) * p.Skv;
       const long long ksf0 = (long long)(b * p.Hkv + hk) * nk * 512;
@@ -339,9 +345,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         if (tk >= ATT_KSTAGES) ok = mbar_wait(&k_empty[s], ((tk / ATT_KSTAGES) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
         if (!ok) return false;
         const bool f8 = map_row[jk] == TILE_FP8;
-        mbar_arrive_expect_tx(&k_full[s], (f8 ? ATT_K_BYTES : ATT_K_BYTES / 2) + 512);
+        mbar_arrive_expect_tx(&k_full[s], (f8 ? ATT_K_BYTES + 512 : ATT_K_BYTES / 2 + SF4));
         tma_load_2d(sK + s * ATT_K_BYTES, f8 ? &tm_k8 : &tm_k4, &k_full[s], 0, k_row0 + jk * ATT_BN);
-        bulk_load(sSF + (2 + s) * 512, (f8 ? p.k8_sf : p.k4_sf) + ksf0 + (long long)jk * 512, 512, &k_full[s]);
+        if (f8) bulk_load(sSF + (3 + 2 * s) * 512, p.k8_sf + ksf0 + (long long)jk * 512, 512, &k_full[s]);
+        else bulk_load(sSF + (3 + 2 * s) * 512, p.k4_sf + (ksf0 + (long long)jk * 512) * (SF4 / 512), SF4, &k_full[s]);
         ++tk; ++jk;
         return true;
       };
@@ -399,7 +406,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       const uint64_t k8d0 = sdesc_kmajor_sw128(smem_u32(sK));       // + stage * (ATT_K_BYTES >> 4)
       const uint64_t k4d0 = sdesc_kmajor_sw64(smem_u32(sK));
       const uint64_t vd0 = sdesc_kmajor_sw128(smem_u32(sV));        // + stage * (ATT_V_BYTES >> 4)
-      const uint64_t sfk0 = sdesc_sf_tile(smem_u32(sSF + 2 * 512)); // + stage * (512 >> 4)
+      const uint64_t sfk0 = sdesc_sf_tile(smem_u32(sSF + 3 * 512)); // + stage * (1024 >> 4)
+      const uint32_t idn = idesc_block_scaled(1, 1, ATT_BM, ATT_BN, 0);   // NVFP4: E4M3 scales, four per instruction
       const uint32_t v_half16 = (uint32_t)v_half_bytes >> 4;
       const uint64_t v4d0 = sdesc_kmajor_sw64(smem_u32(sV));        // MXFP4 V^T tile (64-byte rows)
       const uint64_t sfp0 = sdesc_sf_tile(smem_u32(sPSF));          // P scale tiles [2], then V scale tiles per stage
@@ -414,7 +422,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       if (ok) {
         tc_fence_after();
         tc_cp_32x128b_warpx4(tmem + ATT_COL_SFQ8, sdesc_sf_tile(smem_u32(sSF)));
-        tc_cp_32x128b_warpx4(tmem + ATT_COL_SFQ4, sdesc_sf_tile(smem_u32(sSF + 512)));
+        if (NVF4) {
+          tc_cp_32x128b_warpx4(tmem + ATT_COL_SFQN, sdesc_sf_tile(smem_u32(sSF + 512)));
+          tc_cp_32x128b_warpx4(tmem + ATT_COL_SFQN + 4, sdesc_sf_tile(smem_u32(sSF + 1024)));
+        } else {
+          tc_cp_32x128b_warpx4(tmem + ATT_COL_SFQ4, sdesc_sf_tile(smem_u32(sSF + 512)));
+        }
       }
       int jq = 0;                                  // scan position in the map row
       int tq = 0, tp = 0;                          // tiles issued: Q.K^T and P.V
@@ -433,7 +446,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         TRACE(1, tq, 0);
         tc_fence_after();
         const uint32_t sfk = tmem + ATT_COL_SFK + (tq & 1) * 4;
-        tc_cp_32x128b_warpx4(sfk, sfk0 + (uint64_t)(s * (512 >> 4)));
+        if (NVF4 && !f8) {
+          const uint32_t sfkn = tmem + ATT_COL_SFKN + (tq & 1) * 8;
+          tc_cp_32x128b_warpx4(sfkn, sfk0 + (uint64_t)(s * (1024 >> 4)));
+          tc_cp_32x128b_warpx4(sfkn + 4, sfk0 + (uint64_t)(s * (1024 >> 4) + (512 >> 4)));
+        } else {
+          tc_cp_32x128b_warpx4(sfk, sfk0 + (uint64_t)(s * (1024 >> 4)));
+        }
         const uint32_t d = tmem + ATT_COL_S + (tq & 1) * 128;
         if (f8) {
           const uint64_t kd = k8d0 + (uint64_t)(s * (ATT_K_BYTES >> 4));
@@ -442,7 +461,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         } else {
           const uint64_t kd = k4d0 + (uint64_t)(s * (ATT_K_BYTES >> 4));
 #pragma unroll
-          for (int j = 0; j < 2; ++j) mma_mxf4(d, q4d + 2 * j, kd + 2 * j, id4[j], tmem + ATT_COL_SFQ4, sfk, j > 0);
+          for (int j = 0; j < 2; ++j) {
+            if (NVF4) mma_nvf4(d, q4d + 2 * j, kd + 2 * j, idn, tmem + ATT_COL_SFQN + 4 * j, tmem + ATT_COL_SFKN + (tq & 1) * 8 + 4 * j, j > 0);
+            else mma_mxf4(d, q4d + 2 * j, kd + 2 * j, id4[j], tmem + ATT_COL_SFQ4, sfk, j > 0);
+          }
         }
         tc_commit(&k_empty[s]);
         tc_commit(&s_full[tq & 1]);
@@ -546,6 +568,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       const int n0 = j * ATT_BN + g * W;            // first key of this thread's slice
       const bool need_mask = (p.causal && (j * ATT_BN + ATT_BN - 1 > qi * ATT_BM + off)) || (j * ATT_BN + ATT_BN > p.Skv);
       const int lim = p.causal ? min(p.Skv - 1, m_glob + off) : (p.Skv - 1);   // last visible key
+      [[maybe_unused]] const bool nv_tile = NVF4 && map_row[j] == TILE_FP4;     // scores still lack the tensor scales
       // all chunk loads go out up front when the slice and its packed P fit in the register budget
       constexpr int REG_BUDGET = ((16384 / 32) / (1 + NWG * NSPLIT)) >= 255 ? 255 : (((16384 / 32) / (1 + NWG * NSPLIT)) & ~7);
       constexpr bool ALL_UP = (W + W / 2 + 40 <= REG_BUDGET);
@@ -570,6 +593,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       for (int c = 0; c < NCH; ++c) {
         uint32_t* sc = ALL_UP ? (sr + c * 32) : sr;
         if (!ALL_UP || c == 0) tmem_ld_wait();
+        if (NVF4 && nv_tile) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sc[i] = __float_as_uint(__uint_as_float(sc[i]) * p.fp4_scale);
+        }
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
@@ -659,6 +686,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
           tmem_ld_wait();
+          if (NVF4 && nv_tile) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sr[i] = __float_as_uint(__uint_as_float(sr[i]) * p.fp4_scale);
+          }
           if (need_mask) {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
@@ -920,8 +951,8 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
                              const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* vt8,
                              const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
                              long long map_sb, long long map_sh, void* out, int out_dtype, void* lse, int B, int Hq,
-                             int Hkv, int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int* status,
-                             void* stream) {
+                             int Hkv, int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int fp4_kind,
+                             float fp4_scale, int* status, void* stream) {
   if (!q8 || !q8_sf || !q4 || !q4_sf || !k8 || !k8_sf || !k4 || !k4_sf || !map || !out || !status)
     return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: null pointer");
   if (pv_mode != 0 && pv_mode != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: pv_mode must be 0 (fp16 P.V) or 1 (quantised P.V)");
@@ -932,6 +963,8 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   if (D != 64 && D != 128) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: head_dim must be 64 or 128");
   if (out_dtype < 0 || out_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: out_dtype must be 0 (f32), 1 (f16) or 2 (bf16)");
   if (fp8_fmt != 0 && fp8_fmt != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: fp8_fmt must be 0 (E4M3) or 1 (E5M2)");
+  if (fp4_kind != 0 && fp4_kind != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: fp4_kind must be 0 (MXFP4) or 1 (NVFP4)");
+  if (fp4_kind == 1 && !(fp4_scale > 0.0f)) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: NVFP4 needs a positive fp4_scale");
   if (causal && Skv < S) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: causal needs Skv >= S");
   if (Skv_pad < Skv || Skv_pad % 128) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: Skv_pad must be Skv rounded up to 128");
   const void* ptrs[] = {q8, q8_sf, q4, q4_sf, k8, k8_sf, k4, k4_sf, vt, vt8, v8_sf, vt4, v4_sf, out};
@@ -963,6 +996,7 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   p.q8_sf = (const uint8_t*)q8_sf; p.q4_sf = (const uint8_t*)q4_sf;
   p.k8_sf = (const uint8_t*)k8_sf; p.k4_sf = (const uint8_t*)k4_sf;
   p.v8_sf = (const uint8_t*)v8_sf; p.v4_sf = (const uint8_t*)v4_sf; p.pv_mode = pv_mode;
+  p.fp4_scale = fp4_scale;
   p.map = (const uint8_t*)map; p.map_sb = map_sb; p.map_sh = map_sh;
   p.out = out; p.out_dtype = out_dtype; p.lse = (float*)lse; p.status = status;
   // Softmax organisation: warpgroups taking tiles in turn (1 or 2) x threads per query row inside a
@@ -981,10 +1015,12 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
     }
     cudaError_t e = cudaSuccess;
 #define MPSA_SET_SMEM(A, B) \
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM); \
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM); \
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
     MPSA_SET_SMEM(1, 1) MPSA_SET_SMEM(1, 2) MPSA_SET_SMEM(1, 4) MPSA_SET_SMEM(2, 1) MPSA_SET_SMEM(2, 2)
 #undef MPSA_SET_SMEM
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 1, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 2, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
     if (e != cudaSuccess) {
       cfg_of[0] = 0;
       return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
@@ -997,10 +1033,15 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   cudaStream_t st = (cudaStream_t)stream;
   if (pv_mode == 1 && cfg % 10 == 4)
     return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: quantised P.V needs at most 2 softmax threads per query row");
+  if (fp4_kind == 1) {               // NVFP4 score tiles: the default organisation of each P.V mode only
+    if (pv_mode == 0) attn_fwd_kernel<2, 1, 0, 1><<<grid, 384, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
+    else attn_fwd_kernel<2, 2, 1, 1><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
+    return check_launch("attn_fwd");
+  }
 #define MPSA_LAUNCH(A, B, T)                                                                              \
   do {                                                                                                    \
-    if (pv_mode == 0) attn_fwd_kernel<A, B, 0><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p); \
-    else attn_fwd_kernel<A, B, 1><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);         \
+    if (pv_mode == 0) attn_fwd_kernel<A, B, 0, 0><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p); \
+    else attn_fwd_kernel<A, B, 1, 0><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);         \
   } while (0)
   switch (cfg) {
     case 11: MPSA_LAUNCH(1, 1, 256); break;

@@ -381,9 +381,10 @@ __global__ void __launch_bounds__(256) quant_v_seq_kernel(const QuantVParams p) 
 // in a scratch array (no atomics, nothing to zero), stage 2 reduces the partials and quantises.
 struct QuantNvParams {
   const void* x; int rows, cols; long long ld; float s;
+  int H; long long xs_b, xs_h;              // batch (blockIdx.z = b * H + h): input strides in elements; 2-D: H = 1, strides 0
   float* scratch; int n_partials;
-  uint8_t* codes; long long ldc_bytes;      // [rows, cols/2]
-  uint8_t* scales;                          // [ceil(rows/128), cols/64, 512] E4M3 bytes
+  uint8_t* codes; long long ldc_bytes;      // [batch, rows, cols/2]
+  uint8_t* scales;                          // [batch, ceil(rows/128), cols/64, 512] E4M3 bytes
   float* tensor_scale;
 };
 
@@ -391,7 +392,7 @@ template <typename T>
 __global__ void __launch_bounds__(kQuantThreads) nvfp4_amax_kernel(const QuantNvParams p) {
   __shared__ float red[kQuantThreads / 32];
   const int tid = threadIdx.x;
-  const T* xb = reinterpret_cast<const T*>(p.x);
+  const T* xb = reinterpret_cast<const T*>(p.x) + (blockIdx.z / p.H) * p.xs_b + (blockIdx.z % p.H) * p.xs_h;
   float amax = 0.0f;
   // CTA tile: 128 rows x 512 columns, 16 elements per step and thread
   for (int i = tid; i < 128 * 32; i += kQuantThreads) {
@@ -409,7 +410,7 @@ __global__ void __launch_bounds__(kQuantThreads) nvfp4_amax_kernel(const QuantNv
   __syncthreads();
   if (tid == 0) {
     for (int w = 1; w < kQuantThreads / 32; ++w) amax = fmaxf(amax, red[w]);
-    p.scratch[blockIdx.y * gridDim.x + blockIdx.x] = amax;
+    p.scratch[(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x] = amax;
   }
 }
 
@@ -432,12 +433,13 @@ __global__ void __launch_bounds__(kQuantThreads) nvfp4_quant_kernel(const QuantN
     float ts = __fdiv_rn(amax, 2688.0f);              // 6 * 448
     if (ts == 0.0f) ts = 1.0f;
     ts_s = ts;
-    if (blockIdx.x == 0 && blockIdx.y == 0) *p.tensor_scale = ts;
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) *p.tensor_scale = ts;
   }
   __syncthreads();
   const float ts = ts_s;
   const float denom = __fmul_rn(6.0f, ts);
-  const T* xb = reinterpret_cast<const T*>(p.x);
+  const T* xb = reinterpret_cast<const T*>(p.x) + (blockIdx.z / p.H) * p.xs_b + (blockIdx.z % p.H) * p.xs_h;
+  uint8_t* codes = p.codes + (long long)blockIdx.z * p.rows * p.ldc_bytes;
   const int row0 = blockIdx.x * 128, col0 = blockIdx.y * 128;
 #pragma unroll
   for (int i = 0; i < kRunsPerThread; ++i) {
@@ -458,7 +460,7 @@ __global__ void __launch_bounds__(kQuantThreads) nvfp4_quant_kernel(const QuantN
     float y[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) y[j] = (scf == 0.0f) ? 0.0f : __fdiv_rn(v[j], scf);
-    *reinterpret_cast<uint2*>(p.codes + (long long)r * p.ldc_bytes + (c >> 1)) = make_uint2(cvt_e2m1x8(y), cvt_e2m1x8(y + 8));
+    *reinterpret_cast<uint2*>(codes + (long long)r * p.ldc_bytes + (c >> 1)) = make_uint2(cvt_e2m1x8(y), cvt_e2m1x8(y + 8));
     const int blk = (g & 7);                        // block inside the tile: chunk blk / 4, column blk % 4
     sf[blk >> 2][(rl & 31) * 16 + (rl >> 5) * 4 + (blk & 3)] = (uint8_t)s8;
   }
@@ -468,7 +470,7 @@ __global__ void __launch_bounds__(kQuantThreads) nvfp4_quant_kernel(const QuantN
     const int ch = tid >> 5;
     const long long chunk = (long long)blockIdx.y * 2 + ch;
     if (chunk < nchunks)
-      reinterpret_cast<uint4*>(p.scales + ((long long)blockIdx.x * nchunks + chunk) * 512)[tid & 31] =
+      reinterpret_cast<uint4*>(p.scales + (((long long)blockIdx.z * gridDim.x + blockIdx.x) * nchunks + chunk) * 512)[tid & 31] =
           reinterpret_cast<uint4*>(sf[ch])[tid & 31];
   }
 }
@@ -562,7 +564,7 @@ extern "C" int mpsa_quant_v_seq(const void* v, int in_dtype, int B, int H, int S
 
 static int launch_nvfp4(const void* x, int in_dtype, int rows, int cols, long long ld, float s, float* scratch,
                         long long scratch_floats, void* codes, long long ldc_bytes, void* scales, float* tensor_scale,
-                        cudaStream_t st, const char* who) {
+                        cudaStream_t st, const char* who, int B = 1, int H = 1, long long xs_b = 0, long long xs_h = 0) {
   if (!x || !codes || !scales || !tensor_scale || !scratch || rows <= 0 || cols <= 0)
     return set_error(MPSA_ERR_BAD_ARG, "%s: null pointer or non-positive shape", who);
   if (cols % 64) return set_error(MPSA_ERR_UNSUPPORTED, "%s: the quantised axis must be a multiple of 64", who);
@@ -571,14 +573,18 @@ static int launch_nvfp4(const void* x, int in_dtype, int rows, int cols, long lo
   if (((uintptr_t)x % 16) || ((ld * esz) % 16) || ((uintptr_t)codes % 8) || (ldc_bytes % 8) || ldc_bytes < cols / 2 ||
       ((uintptr_t)scales % 16))
     return set_error(MPSA_ERR_BAD_ARG, "%s: misaligned pointer or pitch", who);
-  dim3 g1((rows + 127) / 128, (cols + 511) / 512), g2((rows + 127) / 128, (cols + 127) / 128);
-  const long long n_partials = (long long)g1.x * g1.y;
+  if (B <= 0 || H <= 0 || (long long)B * H > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "%s: batch x heads must be in [1, 65535]", who);
+  if (((xs_b * esz) % 16) || ((xs_h * esz) % 16)) return set_error(MPSA_ERR_BAD_ARG, "%s: misaligned batch stride", who);
+  dim3 g1((rows + 127) / 128, (cols + 511) / 512, B * H), g2((rows + 127) / 128, (cols + 127) / 128, B * H);
+  const long long n_partials = (long long)g1.x * g1.y * g1.z;
+  if (n_partials > 0x7fffffff) return set_error(MPSA_ERR_UNSUPPORTED, "%s: operand too large", who);
   if (n_partials > scratch_floats)
     return set_error(MPSA_ERR_UNSUPPORTED, "%s: needs %lld floats of scratch, %lld available", who, n_partials, scratch_floats);
   if (g1.y > 65535 || g2.y > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "%s: too many columns", who);
   QuantNvParams p;
   p.x = x; p.rows = rows; p.cols = cols; p.ld = ld; p.s = s; p.scratch = scratch; p.n_partials = (int)n_partials;
   p.codes = (uint8_t*)codes; p.ldc_bytes = ldc_bytes; p.scales = (uint8_t*)scales; p.tensor_scale = tensor_scale;
+  p.H = H; p.xs_b = xs_b; p.xs_h = xs_h;
   if (in_dtype == 0) { nvfp4_amax_kernel<__nv_bfloat16><<<g1, kQuantThreads, 0, st>>>(p); nvfp4_quant_kernel<__nv_bfloat16><<<g2, kQuantThreads, 0, st>>>(p); }
   else if (in_dtype == 1) { nvfp4_amax_kernel<__half><<<g1, kQuantThreads, 0, st>>>(p); nvfp4_quant_kernel<__half><<<g2, kQuantThreads, 0, st>>>(p); }
   else { nvfp4_amax_kernel<float><<<g1, kQuantThreads, 0, st>>>(p); nvfp4_quant_kernel<float><<<g2, kQuantThreads, 0, st>>>(p); }
@@ -595,6 +601,14 @@ extern "C" int mpsa_quant_nvfp4(const void* x, int in_dtype, int rows, int cols,
                                 void* tensor_scale, void* stream) {
   return launch_nvfp4(x, in_dtype, rows, cols, ld, s, (float*)scratch, scratch_floats, codes, ldc_bytes, scales,
                       (float*)tensor_scale, (cudaStream_t)stream, "quant_nvfp4");
+}
+
+extern "C" int mpsa_quant_nvfp4_bh(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b, long long xs_h,
+                                   long long xs_l, float s, void* scratch, long long scratch_floats, void* codes,
+                                   void* scales, void* tensor_scale, void* stream) {
+  if (L <= 0 || D <= 0) return set_error(MPSA_ERR_BAD_ARG, "quant_nvfp4_bh: non-positive shape");
+  return launch_nvfp4(x, in_dtype, L, D, xs_l, s, (float*)scratch, scratch_floats, codes, D / 2, scales,
+                      (float*)tensor_scale, (cudaStream_t)stream, "quant_nvfp4_bh", B, H, xs_b, xs_h);
 }
 
 // ---- NVFP4 quantizer for callers that must not allocate ------------------------------------------------

@@ -29,12 +29,14 @@ _SIGNATURES = {
     "mpsa_quant_nvfp4_scratch_floats": ([c_int, c_int], c_int),
     "mpsa_quant_nvfp4": ([c_void_p, c_int, c_int, c_int, c_ll, c_float, c_void_p, c_ll, c_void_p, c_ll, c_void_p,
                           c_void_p, c_void_p], c_int),
+    "mpsa_quant_nvfp4_bh": ([c_void_p, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_float, c_void_p, c_ll,
+                             c_void_p, c_void_p, c_void_p, c_void_p], c_int),
     "mpsa_quant_nvfp4_static": ([c_void_p, c_int, c_int, c_int, c_ll, c_float, c_void_p, c_ll, c_void_p, c_void_p,
                                  c_void_p], c_int),
     "mpsa_quant_v_seq": ([c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int,
                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p], c_int),
-    "mpsa_attn_fwd": ([c_void_p] * 13 + [c_int, c_void_p, c_ll, c_ll, c_void_p, c_int, c_void_p] + [c_int] * 9 +
-                      [c_void_p, c_void_p], c_int),
+    "mpsa_attn_fwd": ([c_void_p] * 13 + [c_int, c_void_p, c_ll, c_ll, c_void_p, c_int, c_void_p] + [c_int] * 10 +
+                      [c_float, c_void_p, c_void_p], c_int),
     "mpsa_attn_merge": ([c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_void_p], c_int),
     "mpsa_gemm_block_scaled": ([c_void_p] * 5 + [c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_int, c_int, c_int,
                                 c_float, c_void_p, c_void_p], c_int),

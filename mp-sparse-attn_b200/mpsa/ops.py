@@ -70,6 +70,8 @@ class QuantizedOperand:
     fp4_scales: Optional[torch.Tensor] = None
     fp4_unpacked: Optional[torch.Tensor] = None  # uint8 [B,H,L,D] one code per byte (reference format)
     fp8_elem: str = "e5m2"
+    fp4_kind: str = "mxfp4"                     # "nvfp4": fp4_sf holds E4M3 scale tiles [B,H,ceil(L/128),D/64,512]
+    fp4_ts: Optional[torch.Tensor] = None       # NVFP4: the fp32 tensor scale (1-element tensor)
 
 
 def _bhld(x: torch.Tensor, tensor_layout: str):
@@ -173,6 +175,38 @@ def quantize_nvfp4(x: torch.Tensor, scale: float = 1.0):
     return codes, scales, ts
 
 
+def quantize_nvfp4_bh(x: torch.Tensor, scale: float = 1.0):
+    """NVFP4 quantisation of an attention operand [B,H,L,D] along D with ONE tensor scale: packed codes
+    [B,H,L,D/2], E4M3 scale tiles [B,H,ceil(L/128),D/64,512] (tiles restart at every head), tensor scale."""
+    _require_cuda(x)
+    x, (B, H, L, D), (sb, sh, sl) = _bhld(x, "HND")
+    dev = x.device
+    nl = -(-L // 128)
+    scratch = torch.empty(B * H * nl * -(-D // 512), dtype=torch.float32, device=dev)
+    codes = torch.empty((B, H, L, D // 2), dtype=torch.uint8, device=dev)
+    scales = torch.empty((B, H, nl, D // 64, 512), dtype=torch.uint8, device=dev)
+    ts = torch.empty(1, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().mpsa_quant_nvfp4_bh(x.data_ptr(), _IN_DTYPE[x.dtype], B, H, L, D, sb, sh, sl, float(scale),
+                                             scratch.data_ptr(), scratch.numel(), codes.data_ptr(), scales.data_ptr(),
+                                             ts.data_ptr(), _stream())
+    _lib.check(rc)
+    return codes, scales, ts
+
+
+def quantize_qk(x: torch.Tensor, scale: float = 1.0, *, fp8_elem="e5m2", fp4_kind="mxfp4") -> QuantizedOperand:
+    """Q or K (depth already padded to 128) in both precisions of the fused forward: MXFP8 and either MXFP4
+    (one pass for both) or NVFP4 (a second quantizer)."""
+    if fp4_kind == "mxfp4":
+        return quantize_mx(x, scale, fp8_elem=fp8_elem)
+    if fp4_kind != "nvfp4":
+        raise ValueError(f"unknown fp4_kind {fp4_kind!r}")
+    out = quantize_mx(x, scale, want_fp4=False, fp8_elem=fp8_elem)
+    out.fp4, out.fp4_sf, out.fp4_ts = quantize_nvfp4_bh(x, scale)
+    out.fp4_kind = "nvfp4"
+    return out
+
+
 def prepare_vt(v: torch.Tensor) -> torch.Tensor:
     """V [B,H,Skv,D] -> fp16 V^T [B,H,D,Skv_pad] (Skv_pad = Skv rounded up to 128, zero filled)."""
     _require_cuda(v)
@@ -273,7 +307,7 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
                       prec_map: Optional[torch.Tensor] = None, uniform: Optional[str] = None,
                       sm_scale: Optional[float] = None, fp8_elem: str = "e5m2",
                       out_dtype: torch.dtype = torch.bfloat16, pv_mode: str = "fp16", check: bool = False,
-                      router: str = "band", tau: float = 1.0) -> torch.Tensor:
+                      router: str = "band", tau: float = 1.0, fp4_kind: str = "mxfp4") -> torch.Tensor:
     """Quantise Q/K (both MXFP8 and MXFP4 in one pass each), prepare V, build the precision map and
     run the fused forward.  q [B,Hq,S,D], k/v [B,Hkv,Skv,D]; D in {64, 128}.
 
@@ -282,15 +316,17 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
     first key tile (precision_map_online).
 
     pv_mode "fp16": P and V in fp16, the P.V precision of the reference kernel.
-    pv_mode "requant": P is re-quantised to the tile's MX format and V is quantised along the sequence."""
+    pv_mode "requant": P is re-quantised to the tile's MX format and V is quantised along the sequence.
+    fp4_kind "nvfp4": the FP4 tiles of Q.K^T use NVFP4 operands (16-element blocks, E4M3 scales, one tensor scale per
+    operand) instead of MXFP4; P.V keeps the MX formats."""
     _require_cuda(q, k, v)
     B, Hq, S, D = q.shape
     _, Hkv, Skv, _ = k.shape
     if D not in (64, 128):
         raise ValueError("headdim should be in [64, 128].")
     sq = q_side_scale(D, sm_scale)
-    qq = quantize_mx(_pad_depth_128(q), sq, fp8_elem=fp8_elem)
-    kq = quantize_mx(_pad_depth_128(k), 1.0, fp8_elem=fp8_elem)
+    qq = quantize_qk(_pad_depth_128(q), sq, fp8_elem=fp8_elem, fp4_kind=fp4_kind)
+    kq = quantize_qk(_pad_depth_128(k), 1.0, fp8_elem=fp8_elem, fp4_kind=fp4_kind)
     if pv_mode == "fp16":
         vt = prepare_vt(v)
     elif pv_mode == "requant":
@@ -298,6 +334,8 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
     else:
         raise ValueError(f"unknown pv_mode {pv_mode!r}")
     if router == "online":
+        if fp4_kind != "mxfp4":
+            raise ValueError("the online router reads MXFP4 operands")
         if prec_map is not None or uniform is not None:
             raise ValueError("router='online' builds its own precision map")
         stat = router_statistic(qq, kq, B, Hq, Hkv, S, Skv, causal=causal, check=check)
@@ -350,7 +388,16 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
     for t, rows, rb in ((q8, B * Hq * S, 128), (q4, B * Hq * S, 64), (k8, B * Hkv * Skv, 128), (k4, B * Hkv * Skv, 64)):
         if t.numel() != rows * rb or not t.is_contiguous():
             raise ValueError("quantised operand has the wrong size (depth must be padded to 128)")
-    for t, n in ((q8s, B * Hq * nq), (q4s, B * Hq * nq), (k8s, B * Hkv * nk), (k4s, B * Hkv * nk)):
+    if qq.fp4_kind != kq.fp4_kind:
+        raise ValueError("Q and K use different FP4 kinds")
+    nvf4 = qq.fp4_kind == "nvfp4"
+    fp4_scale = 0.0
+    if nvf4:
+        if qq.fp4 is None or kq.fp4 is None or qq.fp8 is None or kq.fp8 is None:
+            raise ValueError("NVFP4 score tiles need both the MXFP8 and the NVFP4 form of Q and K")
+        fp4_scale = float(qq.fp4_ts.item()) * float(kq.fp4_ts.item())
+    m4 = 2 if nvf4 else 1                          # 512-byte FP4 scale tiles per 128 rows
+    for t, n in ((q8s, B * Hq * nq), (q4s, B * Hq * nq * m4), (k8s, B * Hkv * nk), (k4s, B * Hkv * nk * m4)):
         if t.numel() != n * 512 or not t.is_contiguous():
             raise ValueError("scale tiles have the wrong size")
     skv_pad = nk * 128
@@ -377,7 +424,8 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
             q8.data_ptr(), q8s.data_ptr(), q4.data_ptr(), q4s.data_ptr(),
             k8.data_ptr(), k8s.data_ptr(), k4.data_ptr(), k4s.data_ptr(),
             *vptrs, prec_map.data_ptr(), msb, msh, out.data_ptr(), _OUT_DTYPE[out_dtype], _ptr(lse),
-            B, Hq, Hkv, S, Skv, D, skv_pad, int(causal), _FP8_DESC[qq.fp8_elem], st.data_ptr(), _stream())
+            B, Hq, Hkv, S, Skv, D, skv_pad, int(causal), _FP8_DESC[qq.fp8_elem], int(nvf4), fp4_scale,
+            st.data_ptr(), _stream())
     _lib.check(rc)
     if check:
         check_status(dev)

@@ -399,7 +399,7 @@ def attention_mxfp(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
                    tile: int = 128, band: int = 1, prec_map: Optional[torch.Tensor] = None,
                    fp8_elem: str = "e5m2", pv_mode: str = "fp16", sm_scale: Optional[float] = None,
                    out_dtype: torch.dtype = torch.float32, uniform: Optional[str] = None,
-                   return_scores: bool = False):
+                   return_scores: bool = False, fp4_kind: str = "mxfp4"):
     """Emulation of the fused forward, composed from the reference's pieces.
 
     q [B,Hq,S,D], k/v [B,Hkv,Skv,D] (bf16/fp16/fp32 CPU tensors).
@@ -418,6 +418,9 @@ def attention_mxfp(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
     5. O = O / l (:355), cast to out_dtype.
     GQA: kv head = q head // (Hq/Hkv) (ours/online_routing.py:160).
     ``uniform`` = "fp8" | "fp4" forces one format for every non-skipped tile.
+    ``fp4_kind`` = "nvfp4": the FP4 tiles of S come from NVFP4 operands (quant_nvfp4 over the whole of Q and
+    of K): S = (codes*block scales) @ (codes*block scales)^T in fp32, then times fp32(ts_q * ts_k).  P.V keeps
+    the MX formats.  PARITY UNPINNED (no NVFP4 in the reference).
     """
     B, Hq, S, D = q.shape
     _, Hkv, Skv, _ = k.shape
@@ -430,6 +433,15 @@ def attention_mxfp(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
     f8 = "fp8e5" if fp8_elem == "e5m2" else "fp8e4"
     Q8, Q4 = dequant(q8c, q8s, f8), dequant(q4c, q4s, "fp4")
     K8, K4 = dequant(k8c, k8s, f8), dequant(k4c, k4s, "fp4")
+    s4_scale = None
+    if fp4_kind == "nvfp4":
+        qc, qs, qts = quant_nvfp4(q, sq)
+        kc, ks, kts = quant_nvfp4(k, 1.0)
+        Q4 = decode_e2m1(qc) * decode_e4m3(qs).repeat_interleave(16, dim=-1)
+        K4 = decode_e2m1(kc) * decode_e4m3(ks).repeat_interleave(16, dim=-1)
+        s4_scale = (qts.double() * kts.double()).to(torch.float32)
+    elif fp4_kind != "mxfp4":
+        raise ValueError(fp4_kind)
     nq, nk = -(-S // tile), -(-Skv // tile)
     if prec_map is None:
         prec_map = precision_map_band(nq, nk, causal, band, (Skv - S) // tile)
@@ -449,6 +461,8 @@ def attention_mxfp(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
             cell = pm.repeat_interleave(tile, 0).repeat_interleave(tile, 1)[:S, :Skv]
             S8 = Q8[b, h] @ K8[b, hk].T
             S4 = Q4[b, h] @ K4[b, hk].T
+            if s4_scale is not None:
+                S4 = S4 * s4_scale
             sc = torch.where(cell == TILE_FP8, S8, S4)
             mask = cell == TILE_SKIP
             if causal:
@@ -536,3 +550,27 @@ def make_qkv(seed: int, B: int, Hq: int, Hkv: int, S: int, D: int, outliers: int
         idx = torch.randperm(D, generator=g)[:outliers]
         k[..., idx] *= 20.0
     return q.to(dtype), k.to(dtype), v.to(dtype)
+
+
+def make_video_qkv(seed: int, H: int, grid: Tuple[int, int, int], D: int, dtype=torch.bfloat16):
+    """Synthetic stand-in for video-DiT self-attention inputs: B=1, S = f*h*w tokens laid out row-major over
+    the (f, h, w) latent grid.  Q, K, V are N(0,1) (drawn in that order from one CPU generator) plus, each
+    separately, a smooth component low[t, c] = (2/8) * sum_{i<8} sin(2*pi*<w_i, pos(t)> + phi[i, c]) with integer
+    wave vectors w_i in {0..3}^3, pos(t) = (f/F, h/Hh, w/W) and phases phi ~ U[0, 2*pi) per head and channel,
+    which correlates neighbouring tokens."""
+    F, Hh, W = grid
+    S = F * Hh * W
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    base = [torch.randn(1, H, S, D, generator=g) for _ in range(3)]
+    ff, hh, ww = torch.meshgrid(torch.arange(F) / F, torch.arange(Hh) / Hh, torch.arange(W) / W, indexing="ij")
+    pos = torch.stack([ff.reshape(-1), hh.reshape(-1), ww.reshape(-1)], dim=-1)          # [S, 3]
+    out = []
+    for x in base:
+        wv = torch.randint(0, 4, (8, 3), generator=g).to(torch.float32)
+        phi = torch.rand(8, H, 1, D, generator=g) * (2 * torch.pi)
+        arg = 2 * torch.pi * (pos @ wv.T)                                                  # [S, 8]
+        low = torch.zeros(H, S, D)
+        for i in range(8):
+            low += torch.sin(arg[:, i].reshape(1, S, 1) + phi[i])
+        out.append((x + 0.25 * low.unsqueeze(0)).to(dtype))
+    return tuple(out)
