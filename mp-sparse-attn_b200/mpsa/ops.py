@@ -457,6 +457,82 @@ def diagonal_tiled_attention(q, k, v, causal=True, pv_mode="requant"):
                              out_dtype=q.dtype if q.dtype != torch.float32 else torch.float32)
 
 
+class _HostPipeline:
+    """Streams and staging buffers of attention_forward_host for one device and one chunk shape."""
+
+    def __init__(self, dev, shapes, dtype, slots=2):
+        self.h2d, self.d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        self.slots = [tuple(torch.empty(sh, dtype=dtype, device=dev) for sh in shapes) for _ in range(slots)]
+        self.loaded = [torch.cuda.Event() for _ in range(slots)]      # the slot's inputs have arrived
+        self.consumed = [torch.cuda.Event() for _ in range(slots)]    # the forward that read the slot is done
+
+
+_host_pipes = {}
+
+
+def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, out: Optional[torch.Tensor] = None,
+                           device=None, out_dtype: torch.dtype = torch.bfloat16, **kw) -> torch.Tensor:
+    """The fused forward for operands that live in (pinned) HOST memory: q [B,Hq,S,D], k/v [B,Hkv,S,D] CPU tensors,
+    result a pinned CPU tensor [B,Hq,S,D].  The work is cut into (batch, KV group) chunks - independent units of
+    the path - and pipelined over three streams: while chunk i is computed, the inputs of chunk i+1 cross PCIe
+    and the output of chunk i-1 goes back, so that a call costs about max(copy, compute) rather than their sum.
+    Keyword arguments are those of attention_forward."""
+    if q.is_cuda or k.is_cuda or v.is_cuda:
+        raise ValueError("attention_forward_host expects CPU tensors; use attention_forward for device tensors")
+    B, Hq, S, D = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    if Hq % Hkv:
+        raise ValueError("Hq must be a multiple of Hkv")
+    grp = Hq // Hkv
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    q, k, v = (t if t.is_contiguous() else t.contiguous() for t in (q, k, v))
+    q, k, v = (t if t.is_pinned() else t.pin_memory() for t in (q, k, v))
+    if out is None:
+        out = torch.empty((B, Hq, S, D), dtype=out_dtype).pin_memory()
+    elif out.is_cuda or out.dtype != out_dtype or tuple(out.shape) != (B, Hq, S, D) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous CPU tensor [B,Hq,S,D] of out_dtype")
+    shapes = ((1, grp, S, D), (1, 1, Skv, D), (1, 1, Skv, D))
+    key = (dev.index, shapes, q.dtype)
+    pipe = _host_pipes.get(key)
+    if pipe is None:
+        _host_pipes.clear()                       # one shape at a time: the staging buffers are large
+        pipe = _host_pipes[key] = _HostPipeline(dev, shapes, q.dtype)
+    main = torch.cuda.current_stream(dev)
+    start = torch.cuda.Event()
+    start.record(main)
+    pipe.h2d.wait_event(start)                    # the caller's earlier work on these buffers comes first
+    pipe.d2h.wait_event(start)
+    keep = []
+    n = 0
+    for b in range(B):
+        for g in range(Hkv):
+            slot = n % len(pipe.slots)
+            dq, dk, dv = pipe.slots[slot]
+            with torch.cuda.stream(pipe.h2d):
+                if n >= len(pipe.slots):
+                    pipe.h2d.wait_event(pipe.consumed[slot])
+                dq.copy_(q[b:b + 1, g * grp:(g + 1) * grp], non_blocking=True)
+                dk.copy_(k[b:b + 1, g:g + 1], non_blocking=True)
+                dv.copy_(v[b:b + 1, g:g + 1], non_blocking=True)
+                pipe.loaded[slot].record(pipe.h2d)
+            main.wait_event(pipe.loaded[slot])
+            o = attention_forward(dq, dk, dv, causal=causal, out_dtype=out_dtype, **kw)
+            pipe.consumed[slot].record(main)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(pipe.d2h):
+                pipe.d2h.wait_event(done)
+                out[b:b + 1, g * grp:(g + 1) * grp].copy_(o, non_blocking=True)
+            keep.append(o)                        # alive until the copies are ordered behind `main` below
+            n += 1
+    fin = torch.cuda.Event()
+    fin.record(pipe.d2h)
+    main.wait_event(fin)
+    for o in keep:
+        o.record_stream(pipe.d2h)
+    return out
+
+
 _GEMM_MODE = {"mxfp8": 0, "mxfp4": 1, "nvfp4": 2}
 
 

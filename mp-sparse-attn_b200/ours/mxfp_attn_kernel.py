@@ -8,7 +8,7 @@ from mpsa import ops as _ops
 @torch.compiler.disable
 def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
                      is_causal=False, scale=None, smooth_k=False, attention_sink=False, tensor_layout="HND",
-                     output_dtype=torch.float16, return_sparsity=False, block_scale_type="mxfp4", skip_thresh=None):
+                     output_dtype=torch.float16, return_sparsity=False, block_scale_type="mxfp4", skip_thresh=None, out=None):
     """q [B,Hq,S,D], k/v [B,Hkv,Skv,D] (HND) or [B,S,H,D] (NHD) -> o in q's layout.
 
     block_scale_type: "mxfp4" / "mxfp8" quantise every tile of Q.K^T to that format (the two modes
@@ -20,7 +20,11 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
     attn_mask, dropout_p, attention_sink and return_sparsity are accepted and ignored, as in the reference
     wrapper, and so is skip_thresh outside the online modes; is_causal, scale and output_dtype are honoured
     (the reference ignores them)."""
-    torch.cuda.set_device(v.device)
+    host = not v.is_cuda
+    if host and tensor_layout != "HND":
+        raise ValueError("host tensors are taken in the HND layout only")
+    if not host:
+        torch.cuda.set_device(v.device)
     if tensor_layout == "NHD":
         q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
     elif tensor_layout != "HND":
@@ -37,10 +41,16 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
     else:
         uniform = "fp8"
     online = block_scale_type.startswith("online")
-    o = _ops.attention_forward(q, k, v, causal=bool(is_causal), uniform=uniform, sm_scale=scale,
-                               out_dtype=output_dtype, pv_mode="requant" if block_scale_type.endswith("requant") else "fp16",
-                               router="online" if online else "band",
-                               tau=(1.1 if skip_thresh is None else float(skip_thresh)) if online else 1.0)
+    kw = dict(causal=bool(is_causal), uniform=uniform, sm_scale=scale, out_dtype=output_dtype,
+              pv_mode="requant" if block_scale_type.endswith("requant") else "fp16",
+              router="online" if online else "band",
+              tau=(1.1 if skip_thresh is None else float(skip_thresh)) if online else 1.0)
+    if host:
+        o = _ops.attention_forward_host(q, k, v, out=out, **kw)      # `out`: a pinned CPU tensor to fill (optional)
+    else:
+        if out is not None:
+            raise ValueError("out= is for host tensors only")
+        o = _ops.attention_forward(q, k, v, **kw)
     return o.transpose(1, 2) if tensor_layout == "NHD" else o
 
 

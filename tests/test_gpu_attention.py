@@ -174,3 +174,21 @@ def test_requant_pv_gqa_outliers_and_ragged():
     q, k, v = O.make_qkv(0, 1, 4, 4, 512, 64)
     ref = O.attention_mxfp(q, k, v, causal=True, pv_mode="requant")
     _check(_run(q, k, v, True, pv_mode="requant"), ref, "requant d64")
+
+
+def test_host_tensors_are_streamed():
+    """CPU tensors through the reference-facing call: chunked over KV groups on three streams, same result as the
+    device call on the same inputs (bit for bit: the chunks are independent units of the path)."""
+    import mpsa
+    from ours.mxfp_attn_kernel import mxfp_attn_kernel
+    q, k, v = O.make_qkv(7, 2, 8, 2, 512, 128, outliers=3)
+    dev_out = mpsa.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal=True, out_dtype=torch.bfloat16,
+                                     pv_mode="requant", check=True).cpu()
+    for _ in range(2):                            # second call reuses the staging buffers
+        host_out = mxfp_attn_kernel(q, k, v, is_causal=True, block_scale_type="diag_requant", output_dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        assert not host_out.is_cuda and torch.equal(host_out, dev_out)
+    buf = torch.empty_like(host_out).pin_memory()
+    r = mxfp_attn_kernel(q, k, v, is_causal=True, block_scale_type="diag_requant", output_dtype=torch.bfloat16, out=buf)
+    torch.cuda.synchronize()
+    assert r is buf and torch.equal(buf, dev_out)
