@@ -29,7 +29,8 @@
 // Inside a warpgroup the 128 keys of a tile can further be split over NSPLIT threads per query row,
 // which exchange partial row maxima.  Every thread keeps a partial row sum; the epilogue adds them.
 // TMEM columns: S0/P0 [0,128) S1/P1 [128,256) O [256,384) Q scales [384,392) K scales [392,400)
-// P scales [400,408) V scales [408,416); with NVFP4 score tiles: Q scales [416,424) K scales [424,440).
+// P scales [400,408) V scales [408,416); with NVFP4 score tiles: Q scales [416,424) K scales [424,440);
+// quantised P [448,512) (two buffers; fp16 P overwrites S in place instead).
 #include "api_internal.h"
 #include "common.cuh"
 #include "tma_host.h"
@@ -64,6 +65,7 @@ constexpr uint32_t ATT_TMEM_COLS = 512;
 constexpr uint32_t ATT_COL_S = 0, ATT_COL_O = 256, ATT_COL_SFQ8 = 384, ATT_COL_SFQ4 = 388, ATT_COL_SFK = 392;
 constexpr uint32_t ATT_COL_SFP = 400, ATT_COL_SFV = 408;
 constexpr uint32_t ATT_COL_SFQN = 416, ATT_COL_SFKN = 424;        // NVFP4 scales: Q 8 columns, K 2 x 8
+constexpr uint32_t ATT_COL_P = 448;                              // quantised P: 2 buffers of 32 columns (128 keys x 1 byte)
 constexpr float ATT_RESCALE_LOG2 = 8.0f;
 
 constexpr int TILE_SKIP = 0, TILE_FP8 = 1, TILE_FP4 = 2;
@@ -275,7 +277,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   uint64_t* x_bar = pv_done + 2;                   // [WG][2][4] partial-max exchange inside a warpgroup
   uint64_t* m_bar = x_bar + ATT_MAX_WG * 8;        // [2][4] running-max hand-over, per tile parity and row quarter
   uint64_t* l_bar = m_bar + 8;                     // [4] partial-sum exchange in the epilogue
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(l_bar + 4);
+  uint64_t* s_free = l_bar + 4;                    // 2: quantised P.V only - every softmax thread is done with the S buffer
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
   float* xmax = reinterpret_cast<float*>(smem + ATT_OFF_XMAX);
   float* xsum = reinterpret_cast<float*>(smem + ATT_OFF_XSUM);
   float* mrow = reinterpret_cast<float*>(smem + ATT_OFF_MROW);
@@ -298,7 +301,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     mbar_init(q_full, 1);
     for (int s = 0; s < ATT_KSTAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
     for (int s = 0; s < ATT_VSTAGES; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 128 * NSPLIT); mbar_init(&pv_done[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 128 * NSPLIT); mbar_init(&pv_done[s], 1); mbar_init(&s_free[s], 128 * NSPLIT); }
     for (int s = 0; s < ATT_MAX_WG * 8; ++s) mbar_init(&x_bar[s], NSPLIT);
     for (int s = 0; s < 8; ++s) mbar_init(&m_bar[s], NSPLIT);
     for (int s = 0; s < 4; ++s) mbar_init(&l_bar[s], NSPLIT * NWG);
@@ -482,15 +485,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       }
       while (ok && tp < tq) {
         const int bsel = tp & 1, s = tp % ATT_VSTAGES;
+        if (PVQ && jn >= 0) {
+          // Quantised P lives in its own TMEM columns, so the S buffer is free as soon as the softmax threads
+          // have read it: Q.K^T of tile tp+2 goes out BEFORE P.V of tile tp and runs while P is still being stored.
+          wait_k();
+          if (ok) ok = mbar_wait(&s_free[bsel], (tp >> 1) & 1, p.status, KS_TIMEOUT_PIPE);
+          if (!ok) break;
+          issue_qk();
+          find_next();
+        }
         ok = mbar_wait(&v_full[s], (tp / ATT_VSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
-        if (ok && jn >= 0) wait_k();
+        if (!PVQ && ok && jn >= 0) wait_k();
         if (!ok) break;
         TRACE(1, tp, 2);
         ok = mbar_wait(&p_ready[bsel], (tp >> 1) & 1, p.status, KS_TIMEOUT_PIPE);
         if (!ok) break;
         TRACE(1, tp, 3);
         tc_fence_after();
-        const uint32_t ptm = tmem + ATT_COL_S + bsel * 128;     // P, see the softmax role for its columns
+        const uint32_t ptm = PVQ ? tmem + ATT_COL_P + bsel * 32 : tmem + ATT_COL_S + bsel * 128;   // P, see the softmax role for its columns
         const uint32_t acc0 = tp > 0 ? 1u : 0u;
         if (PVQ == 0) {
           const uint64_t vd = vd0 + (uint64_t)(s * (ATT_V_BYTES >> 4));
@@ -508,15 +520,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
             const uint64_t vd = vd0 + (uint64_t)(s * (ATT_V_BYTES >> 4));
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {                     // 32 keys per instruction, 8 TMEM columns of P
-              const uint32_t pcol = ((ks * 32) / PW) * PW + ((ks * 32) % PW) / 4;
-              mma_mxf8f6f4_ts(tmem + ATT_COL_O, ptm + pcol, vd + 2 * ks, idp8[ks], sfp, sfv, ks > 0 ? 1u : acc0);
+              mma_mxf8f6f4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp8[ks], sfp, sfv, ks > 0 ? 1u : acc0);
             }
           } else {
             const uint64_t vd = v4d0 + (uint64_t)(s * (ATT_V_BYTES >> 4));
 #pragma unroll
             for (int ks = 0; ks < 2; ++ks) {                     // 64 keys per instruction, 8 TMEM columns of P
-              const uint32_t pcol = ((ks * 64) / PW) * PW + ((ks * 64) % PW) / 8;
-              mma_mxf4_ts(tmem + ATT_COL_O, ptm + pcol, vd + 2 * ks, idp4[ks], sfp, sfv, ks > 0 ? 1u : acc0);
+              mma_mxf4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp4[ks], sfp, sfv, ks > 0 ? 1u : acc0);
             }
           }
         }
@@ -524,7 +534,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         tc_commit(&pv_done[bsel]);
         TRACE(1, tp, 4);
         ++tp;
-        if (jn >= 0) {
+        if (!PVQ && jn >= 0) {
           issue_qk();
           find_next();
         }
@@ -715,18 +725,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       }
       l_run += lsum0 + lsum1;
       if (tracer) TRACE(trole, t, 4);
-      // P overwrites S inside this thread's own slice: key k of the tile sits in column
+      if (PVQ) {
+        tc_fence_before();
+        mbar_arrive(&s_free[bsel]);                 // this thread will not read the S buffer again
+        if (t >= 2) {                               // the P buffer and its scale tile: P.V of tile t-2 has read them
+          ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[bsel], ((t - 2) >> 1) & 1, p.status, KS_TIMEOUT_MMA));
+          if (!ok) break;
+          tc_fence_after();
+        }
+      }
+      // fp16 P overwrites S inside this thread's own slice: key k of the tile sits in column
       // (k / W) * W + (k % W) / e with e = 2 (fp16), 4 (MXFP8) or 8 (MXFP4) elements per 32-bit column
       if (pmode == 0) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c) tmem_st16p(slice_addr + c * 16, pk + c * 16);
       } else {
+        // quantised P has its own buffer: key k of the tile in column k / 4 (MXFP8) or k / 8 (MXFP4)
+        const uint32_t p_addr = tmem + lane_base + ATT_COL_P + bsel * 32;
         if (pmode == 3) {
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) tmem_st4p(slice_addr + c * 4, pk + c * 4);
+          for (int c = 0; c < NCH; ++c) tmem_st4p(p_addr + g * (W / 8) + c * 4, pk + c * 4);
         } else {
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) tmem_st8p(slice_addr + c * 8, pk + c * 8);
+          for (int c = 0; c < NCH; ++c) tmem_st8p(p_addr + g * (W / 4) + c * 8, pk + c * 8);
         }
         // this row's block scales go into the 128x4 scale tile of the S buffer, which the MMA warp
         // copies to TMEM: row r, block k at byte (r % 32) * 16 + (r / 32) * 4 + k
