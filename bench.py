@@ -377,6 +377,58 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_gemm(args):
+    """Standalone block-scaled GEMM C[M,N] = A[M,K] . B[N,K]^T, M = N = K = --size (default 8192), bf16 N(0,1)
+    operands from seed 1 quantised along K three ways; prints one JSON line with the three variants and the
+    library bf16 GEMM of the same shape beside them."""
+    import mpsa
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    n = args.size
+    K, W = args.steps, args.warmup
+    g = torch.Generator(device=dev).manual_seed(1)
+    a = torch.randn(n, n, generator=g, device=dev).to(torch.bfloat16)
+    b = torch.randn(n, n, generator=g, device=dev).to(torch.bfloat16)
+    qa, qb = mpsa.quantize_mx(a.view(1, 1, n, n), 1.0), mpsa.quantize_mx(b.view(1, 1, n, n), 1.0)
+    na, sa, tsa = mpsa.quantize_nvfp4(a)
+    nb, sb, tsb = mpsa.quantize_nvfp4(b)
+    alpha = float(tsa.item()) * float(tsb.item())
+
+    def timed(fn):
+        for _ in range(max(W, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / K
+
+    variants = {
+        "mxfp8": lambda: mpsa.gemm_block_scaled(qa.fp8.view(n, n), qa.fp8_sf, qb.fp8.view(n, n), qb.fp8_sf, torch.bfloat16, n, n, n, "mxfp8"),
+        "mxfp4": lambda: mpsa.gemm_block_scaled(qa.fp4.view(n, n // 2), qa.fp4_sf, qb.fp4.view(n, n // 2), qb.fp4_sf, torch.bfloat16, n, n, n, "mxfp4"),
+        "nvfp4": lambda: mpsa.gemm_block_scaled(na, sa, nb, sb, torch.bfloat16, n, n, n, "nvfp4", alpha=alpha),
+    }
+    pk = measured_peaks()
+    flops = 2.0 * n * n * n
+    res = {}
+    for name, fn in variants.items():
+        ms = timed(fn)
+        mult = 2.0 if name == "mxfp8" else 4.0
+        res[name] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                     "frac_of_peak": round(flops / ms / 1e9 / (mult * pk["bf16"]), 4)}
+    mpsa.check_status(dev)
+    ms = timed(lambda: a @ b.T)
+    res["library_bf16"] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1)}
+    print(json.dumps({"metric": "block-scaled GEMM TFLOPS", "unit": "TFLOP/s", "value": res["mxfp8"]["tflops"], "n_gpus": 1,
+                      "steps": K, "warmup": max(W, 3), "higher_is_better": True, "dtype": "mxfp8 / mxfp4 / nvfp4 (fp32 accumulate)",
+                      "data": "synthetic", "config": {"workload": f"cfg2 GEMM M=N=K={n}, operands quantised along K, bf16 out"},
+                      "variants": res, "peak": {"bf16_burst_tflops": pk["bf16"], "mxfp8": "2x", "fp4": "4x", "source": pk["source"]},
+                      "gpu_launches": 3 * K}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -384,9 +436,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seq", type=int, default=None, help="sequence length (default 32768; 131072 for --workload ring)")
-    ap.add_argument("--workload", default="prefill", choices=["prefill", "ring"],
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "ring", "gemm"],
                     help="prefill: the headline single-GPU workload replicated per GPU; ring: S=131072 causal, "
-                         "sequence-sharded over the GPUs (strong scaling)")
+                         "sequence-sharded over the GPUs (strong scaling); gemm: the standalone block-scaled GEMM (1 GPU)")
+    ap.add_argument("--size", type=int, default=8192, help="M = N = K of --workload gemm")
     ap.add_argument("--layout", default="zigzag", choices=["contiguous", "zigzag"])
     args = ap.parse_args()
     if args.impl == "reference":
@@ -396,6 +449,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
     if args.workload == "ring":
         run_ring(args)
+    elif args.workload == "gemm":
+        run_gemm(args)
     else:
         run_ours(args)
 
