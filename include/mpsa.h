@@ -169,6 +169,13 @@ int mpsa_gemm_block_scaled(const void* a, const void* a_scale, const void* b, co
                            int N, int K, long long lda_bytes, long long ldb_bytes, long long ldc, int mode,
                            int a_fmt, int b_fmt, int out_dtype, float alpha, int* status, void* stream);
 
+/* The same product for `batch` independent problems laid out one after the other, all contiguous:
+ * a [batch,M,K/epb], b [batch,N,K/epb], scale tiles [batch,ceil(rows/128),K/vec/4,512], c [batch,M,N].
+ * Replaces block_scaled_batched_matmul (ours/batched_block_scaled_matmul.py:183-236) with batch = B*H. */
+int mpsa_gemm_block_scaled_batched(const void* a, const void* a_scale, const void* b, const void* b_scale, void* c,
+                                   int batch, int M, int N, int K, int mode, int a_fmt, int b_fmt, int out_dtype,
+                                   float alpha, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -123,6 +123,9 @@ gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       tma_prefetch_desc(&tmap_b);
       const int mt = blockIdx.x, nt0 = blockIdx.y * 2;
       const int n_row_tiles = (p.N + 127) / 128;
+      // batched launch (blockIdx.z): operands, scale tiles and C of the batches lie one after the other
+      const uint8_t* sfa_z = p.sfa + (long long)blockIdx.z * ((p.M + 127) / 128) * p.nchunks * 512;
+      const uint8_t* sfb_z = p.sfb + (long long)blockIdx.z * n_row_tiles * p.nchunks * 512;
       int issued = 0;
       bool ok = true;
       for (int kt = 0; kt < KT && ok; ++kt) {
@@ -135,12 +138,12 @@ gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         const int nbt = min(2, n_row_tiles - nt0);              // valid B row tiles
         const uint32_t bytes = GEMM_A_BYTES + GEMM_B_BYTES + (uint32_t)ncv * 512u * (1 + nbt);
         mbar_arrive_expect_tx(&full[s], bytes);
-        tma_load_2d(st, &tmap_a, &full[s], kt * GEMM_SLAB, m0);
-        tma_load_2d(st + GEMM_A_BYTES, &tmap_b, &full[s], kt * GEMM_SLAB, n0);
-        bulk_load(st + GEMM_A_BYTES + GEMM_B_BYTES, p.sfa + ((long long)mt * p.nchunks + c0) * 512, ncv * 512, &full[s]);
+        tma_load_2d(st, &tmap_a, &full[s], kt * GEMM_SLAB, (int)blockIdx.z * p.M + m0);
+        tma_load_2d(st + GEMM_A_BYTES, &tmap_b, &full[s], kt * GEMM_SLAB, (int)blockIdx.z * p.N + n0);
+        bulk_load(st + GEMM_A_BYTES + GEMM_B_BYTES, sfa_z + ((long long)mt * p.nchunks + c0) * 512, ncv * 512, &full[s]);
         for (int t = 0; t < nbt; ++t)
           bulk_load(st + GEMM_A_BYTES + GEMM_B_BYTES + GEMM_SFA_BYTES + t * nc_stage * 512,
-                    p.sfb + ((long long)(nt0 + t) * p.nchunks + c0) * 512, ncv * 512, &full[s]);
+                    sfb_z + ((long long)(nt0 + t) * p.nchunks + c0) * 512, ncv * 512, &full[s]);
         issued = kt + 1;
       }
       if (!ok) {
@@ -211,7 +214,7 @@ gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-          store_row32(p.c, (long long)row * p.ldc + col, p.out_dtype, v, min(32, p.N - col));
+          store_row32(p.c, ((long long)blockIdx.z * p.M + row) * p.ldc + col, p.out_dtype, v, min(32, p.N - col));
         }
       }
     }
@@ -225,13 +228,14 @@ gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
 using namespace mpsa;
 
-extern "C" int mpsa_gemm_block_scaled(const void* a, const void* a_scale, const void* b, const void* b_scale,
-                                      void* c, int M, int N, int K, long long lda_bytes, long long ldb_bytes,
-                                      long long ldc, int mode, int a_fmt, int b_fmt, int out_dtype, float alpha,
-                                      int* status, void* stream) {
+static int launch_gemm(const void* a, const void* a_scale, const void* b, const void* b_scale, void* c, int batch, int M,
+                       int N, int K, long long lda_bytes, long long ldb_bytes, long long ldc, int mode, int a_fmt, int b_fmt,
+                       int out_dtype, float alpha, int* status, void* stream) {
   if (!a || !b || !a_scale || !b_scale || !c || !status)
     return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: null pointer");
-  if (M <= 0 || N <= 0 || K <= 0) return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: non-positive shape");
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: non-positive shape");
+  if (batch > 65535 || (long long)batch * M >= (1ll << 31) || (long long)batch * N >= (1ll << 31))
+    return set_error(MPSA_ERR_UNSUPPORTED, "gemm_block_scaled: batch too large");
   if (mode < 0 || mode > 2) return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: mode must be 0 (mxfp8), 1 (mxfp4) or 2 (nvfp4)");
   if (out_dtype < 0 || out_dtype > 3) return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: out_dtype must be 0..3");
   const int chunk = mode == 2 ? 64 : 128;
@@ -245,8 +249,8 @@ extern "C" int mpsa_gemm_block_scaled(const void* a, const void* a_scale, const 
     return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: operands need 16-byte aligned bases and row pitches >= K bytes");
   if (ldc < N) return set_error(MPSA_ERR_BAD_ARG, "gemm_block_scaled: ldc < N");
   CUtensorMap ta, tb;
-  if (make_tmap_2d_bytes(&ta, a, kbytes, M, lda_bytes, GEMM_SLAB, GEMM_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
-      make_tmap_2d_bytes(&tb, b, kbytes, N, ldb_bytes, GEMM_SLAB, GEMM_BN, CU_TENSOR_MAP_SWIZZLE_128B))
+  if (make_tmap_2d_bytes(&ta, a, kbytes, (uint64_t)batch * M, lda_bytes, GEMM_SLAB, GEMM_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      make_tmap_2d_bytes(&tb, b, kbytes, (uint64_t)batch * N, ldb_bytes, GEMM_SLAB, GEMM_BN, CU_TENSOR_MAP_SWIZZLE_128B))
     return set_error(MPSA_ERR_LAUNCH, "gemm_block_scaled: cuTensorMapEncodeTiled failed");
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.mode = mode; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
@@ -258,8 +262,24 @@ extern "C" int mpsa_gemm_block_scaled(const void* a, const void* a_scale, const 
       return set_error(MPSA_ERR_LAUNCH, "gemm_block_scaled: cannot reserve %d bytes of shared memory", GEMM_SMEM);
     attr_set = true;
   }
-  dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + GEMM_BN - 1) / GEMM_BN);
+  dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + GEMM_BN - 1) / GEMM_BN, batch);
   if (grid.y > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "gemm_block_scaled: N too large");
   gemm_block_scaled_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ta, tb, p);
   return check_launch("gemm_block_scaled");
+}
+
+extern "C" int mpsa_gemm_block_scaled(const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                      void* c, int M, int N, int K, long long lda_bytes, long long ldb_bytes,
+                                      long long ldc, int mode, int a_fmt, int b_fmt, int out_dtype, float alpha,
+                                      int* status, void* stream) {
+  return launch_gemm(a, a_scale, b, b_scale, c, 1, M, N, K, lda_bytes, ldb_bytes, ldc, mode, a_fmt, b_fmt, out_dtype, alpha,
+                     status, stream);
+}
+
+extern "C" int mpsa_gemm_block_scaled_batched(const void* a, const void* a_scale, const void* b, const void* b_scale,
+                                              void* c, int batch, int M, int N, int K, int mode, int a_fmt, int b_fmt,
+                                              int out_dtype, float alpha, int* status, void* stream) {
+  const long long kbytes = K / (mode == 0 ? 1 : 2);
+  return launch_gemm(a, a_scale, b, b_scale, c, batch, M, N, K, kbytes, kbytes, N, mode, a_fmt, b_fmt, out_dtype, alpha,
+                     status, stream);
 }

@@ -562,3 +562,40 @@ def gemm_block_scaled(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b
     if check:
         check_status(a.device)
     return c
+
+
+def gemm_block_scaled_batched(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor,
+                              out_dtype: torch.dtype, M: int, N: int, K: int, mode: str, *, a_elem="e5m2", b_elem="e5m2",
+                              alpha: float = 1.0, check: bool = False) -> torch.Tensor:
+    """C[..., M, N] = alpha * (A.sa)(B.sb)^T for every leading index: a [..., M, K/epb], b [..., N, K/epb] bytes,
+    scale tiles [..., rows/128, K/vec/4, 32,4,4]; one launch for all problems."""
+    _require_cuda(a, b, a_scale, b_scale)
+    if mode not in _GEMM_MODE:
+        raise ValueError(f"Invalid block scale type: {mode}")
+    if out_dtype not in _OUT_DTYPE:
+        raise ValueError(f"Unsupported dtype: {out_dtype}")
+    lead = tuple(a.shape[:-2])
+    if tuple(b.shape[:-2]) != lead:
+        raise ValueError("a and b need the same leading (batch) dimensions")
+    batch = 1
+    for d in lead:
+        batch *= d
+    a, b, a_scale, b_scale = a.contiguous(), b.contiguous(), a_scale.contiguous(), b_scale.contiguous()
+    epb = 1 if mode == "mxfp8" else 2
+    vec = 16 if mode == "nvfp4" else 32
+    if a.shape[-2] != M or b.shape[-2] != N or a.shape[-1] * a.element_size() != K // epb or b.shape[-1] * b.element_size() != K // epb:
+        raise ValueError("operand shapes do not match M, N, K")
+    for t, rows in ((a_scale, M), (b_scale, N)):
+        if t.numel() * t.element_size() != batch * (-(-rows // 128)) * (K // vec // 4) * 512:
+            raise ValueError("scale tiles have the wrong size")
+    c = torch.empty((*lead, M, N), dtype=out_dtype, device=a.device)
+    st = status_word(a.device)
+    with torch.cuda.device(a.device):
+        rc = _lib.load().mpsa_gemm_block_scaled_batched(
+            a.data_ptr(), a_scale.data_ptr(), b.data_ptr(), b_scale.data_ptr(), c.data_ptr(), batch, M, N, K,
+            _GEMM_MODE[mode], _FP8_DESC[a_elem], _FP8_DESC[b_elem], _OUT_DTYPE[out_dtype], float(alpha), st.data_ptr(),
+            _stream())
+    _lib.check(rc)
+    if check:
+        check_status(a.device)
+    return c

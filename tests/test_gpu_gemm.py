@@ -105,3 +105,38 @@ def test_quantizer_feeds_gemm_full_k():
         m = O.parity_metrics(out.cpu(), ref)
         assert m["cos"] >= 0.9999 and m["rel_l2"] <= 1e-2, m
         torch.testing.assert_close(out.cpu(), ref, atol=2e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("mode,M,N,K", [("mxfp8", 128, 256, 256), ("mxfp4", 200, 300, 256), ("mxfp8", 384, 130, 128)])
+def test_batched_gemm_equals_per_problem_gemm(mode, M, N, K):
+    """One batched launch over [B,H] problems (quantizer output fed straight in, ragged M and N included) gives
+    bit for bit what the 2-D entry gives problem by problem."""
+    import mpsa
+    B, H = 2, 3
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn(B, H, M, K, generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(B, H, N, K, generator=g).to(torch.bfloat16).cuda()
+    qa, qb = mpsa.quantize_mx(a, 1.0), mpsa.quantize_mx(b, 1.0)
+    ca, cb, fa, fb = (qa.fp8, qb.fp8, qa.fp8_sf, qb.fp8_sf) if mode == "mxfp8" else (qa.fp4, qb.fp4, qa.fp4_sf, qb.fp4_sf)
+    out = mpsa.gemm_block_scaled_batched(ca, fa, cb, fb, torch.float32, M, N, K, mode, check=True)
+    assert tuple(out.shape) == (B, H, M, N)
+    for i in range(B):
+        for j in range(H):
+            one = mpsa.gemm_block_scaled(ca[i, j], fa[i, j], cb[i, j], fb[i, j], torch.float32, M, N, K, mode, check=True)
+            assert torch.equal(out[i, j], one)
+
+
+def test_batched_reference_entry_points():
+    """initialize_block_scaled_batched_from_tensor + block_scaled_batched_matmul (the reference's batched module)
+    against the emulation (A*sa) @ (B*sb)^T, tolerance of the reference's own GEMM check (1e-3, 1e-3)."""
+    from ours.batched_block_scaled_matmul import block_scaled_batched_matmul, initialize_block_scaled_batched_from_tensor
+    torch.manual_seed(7)
+    B, H, M, N, K = 2, 2, 128, 256, 256
+    for kind in ("mxfp8", "mxfp4"):
+        a_t = torch.randn((B, H, M, K), dtype=torch.float16, device="cuda")
+        b_t = torch.randn((B, H, N, K), dtype=torch.float16, device="cuda")
+        a_s = torch.rand((B, H, M // 128, K // 32 // 4, 32, 4, 4), device="cuda") + 1e-8
+        b_s = torch.rand((B, H, N // 128, K // 32 // 4, 32, 4, 4), device="cuda") + 1e-8
+        a, sa, b, sb, cfg, (ref, _, _) = initialize_block_scaled_batched_from_tensor(a_t, b_t, a_s, b_s, kind, compute_reference=True)
+        out = block_scaled_batched_matmul(a, sa, b, sb, torch.float32, B, H, M, N, K, cfg)
+        torch.testing.assert_close(out, ref, atol=1e-3, rtol=1e-3)
