@@ -214,7 +214,7 @@ def run_ours(args):
 
     def e2e_step():
         # host tensors in, host tensor out: the call streams the (batch, KV group) chunks through the GPU
-        mxfp_attn_kernel(hq, hk, hv, is_causal=True, block_scale_type="online_requant", skip_thresh=TAU,
+        mxfp_attn_kernel(hq, hk, hv, is_causal=True, block_scale_type="online_requant", promote_thresh=TAU,
                          output_dtype=torch.bfloat16, out=hout)
 
     for _ in range(max(1, min(W, 2))):

@@ -122,10 +122,11 @@ int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4, const voi
 
 /* Online precision map uint8 [B,Hq,nq,nk] (128 x 128 cells) from the statistic above: SKIP above the causal
  * diagonal, FP8 within `band` tiles of the diagonal, and elsewhere FP8 iff stat[i,j] >= stat[i,0] * tau, else
- * FP4.  The first key tile is the reference row statistic ("sink"), as in ours/mxfp_attn_kernel.py:272-276,
- * where the same comparison (with skip_thresh) is meant to drop tiles; here it promotes their precision. */
+ * FP4.  The first key tile is the reference row statistic ("sink"), as in ours/mxfp_attn_kernel.py:272-276.
+ * With use_skip != 0 the reference's own rule is applied on top: a tile outside the band is processed only if
+ * it is the row's first one or stat[i,j] >= stat[i,0] * skip_tau (:276-297), otherwise it is SKIP. */
 int mpsa_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv, int causal, int band, float tau,
-                      void* stream);
+                      float skip_tau, int use_skip, void* stream);
 
 /* Fused attention forward.  Replaces block_scaled_batched_attn (ours/mxfp_attn_kernel.py:362-423)
  * and its kernel (:103-359).

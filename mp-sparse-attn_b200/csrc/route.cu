@@ -215,9 +215,10 @@ __global__ void route_stat_finish_kernel(const float4* part, float* stat, long l
   }
 }
 
-// map[b,h,i,j]: SKIP above the causal diagonal, FP8 inside the band, else FP8 iff stat >= sink * tau, else FP4.
+// map[b,h,i,j]: SKIP above the causal diagonal, FP8 inside the band, else FP8 iff stat >= sink * tau, else FP4;
+// with use_skip, tiles outside the band whose statistic is below sink * skip_tau are SKIP as well.
 __global__ void route_online_kernel(uint8_t* map, const float* stat, int nq, int nk, int tile, int causal, int band,
-                                    float tau, int S, int Skv) {
+                                    float tau, float skip_tau, int use_skip, int S, int Skv) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x, i = blockIdx.y;
   const long long bh = blockIdx.z;
   if (j >= nk) return;
@@ -230,7 +231,11 @@ __global__ void route_online_kernel(uint8_t* map, const float* stat, int nq, int
   } else if (abs(i + off / tile - j) < band) {
     v = 1;
   } else {
-    v = (stat[row + j] >= stat[row] * tau) ? 1 : 2;
+    const float st = stat[row + j], sink = stat[row];
+    v = (st >= sink * tau) ? 1 : 2;
+    // the reference's own use of the statistic: a tile is processed iff it is the row's first one or
+    // stat >= sink * skip_thresh (ours/mxfp_attn_kernel.py:276-280); the band is always processed
+    if (use_skip && j > 0 && !(st >= sink * skip_tau)) v = 0;
   }
   map[row + j] = v;
 }
@@ -277,12 +282,12 @@ extern "C" int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4
 }
 
 extern "C" int mpsa_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv, int causal, int band,
-                                 float tau, void* stream) {
+                                 float tau, float skip_tau, int use_skip, void* stream) {
   if (!map || !stat || B <= 0 || Hq <= 0 || S <= 0 || Skv <= 0 || band < 0) return set_error(MPSA_ERR_BAD_ARG, "route_online: bad argument");
   const int nq = (S + 127) / 128, nk = (Skv + 127) / 128;
   if (nq > 65535 || (long long)B * Hq > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "route_online: too many tiles or heads");
   dim3 grid((nk + 127) / 128, nq, B * Hq);
   route_online_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((uint8_t*)map, (const float*)stat, nq, nk, 128, causal, band,
-                                                             tau, S, Skv);
+                                                             tau, skip_tau, use_skip, S, Skv);
   return check_launch("route_online");
 }

@@ -25,7 +25,7 @@ _SIGNATURES = {
                          c_void_p], c_int),
     "mpsa_route_band": ([c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p], c_int),
     "mpsa_route_stat": ([c_void_p] * 6 + [c_int] * 6 + [c_void_p, c_void_p], c_int),
-    "mpsa_route_online": ([c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p], c_int),
+    "mpsa_route_online": ([c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p], c_int),
     "mpsa_quant_nvfp4_scratch_floats": ([c_int, c_int], c_int),
     "mpsa_quant_nvfp4": ([c_void_p, c_int, c_int, c_int, c_ll, c_float, c_void_p, c_ll, c_void_p, c_ll, c_void_p,
                           c_void_p, c_void_p], c_int),

@@ -282,16 +282,21 @@ def router_statistic(qq: "QuantizedOperand", kq: "QuantizedOperand", B: int, Hq:
     return stat
 
 
-def precision_map_online(stat: torch.Tensor, S: int, Skv: int, *, causal: bool, band: int = 1, tau: float = 1.0) -> torch.Tensor:
+def precision_map_online(stat: torch.Tensor, S: int, Skv: int, *, causal: bool, band: int = 1, tau: float = 1.0,
+                         skip_thresh: Optional[float] = None) -> torch.Tensor:
     """uint8 [B,Hq,nq,nk] from router_statistic: band rule, plus FP8 for every other visible tile whose statistic
-    reaches `tau` times that of the row's first key tile."""
+    reaches `tau` times that of the row's first key tile.  skip_thresh (the reference's use of the statistic,
+    ours/mxfp_attn_kernel.py:276-297): a tile outside the band is processed only if it is the row's first one or its
+    statistic reaches skip_thresh times the first tile's; otherwise it is SKIP."""
     B, Hq, nq, nk = stat.shape
     if (nq, nk) != (-(-S // 128), -(-Skv // 128)) or stat.dtype != torch.float32:
         raise ValueError("stat must be float32 [B, Hq, ceil(S/128), ceil(Skv/128)]")
     stat = stat.contiguous()
     m = torch.empty((B, Hq, nq, nk), dtype=torch.uint8, device=stat.device)
     with torch.cuda.device(stat.device):
-        rc = _lib.load().mpsa_route_online(m.data_ptr(), stat.data_ptr(), B, Hq, S, Skv, int(causal), band, float(tau), _stream())
+        rc = _lib.load().mpsa_route_online(m.data_ptr(), stat.data_ptr(), B, Hq, S, Skv, int(causal), band, float(tau),
+                                           0.0 if skip_thresh is None else float(skip_thresh), int(skip_thresh is not None),
+                                           _stream())
     _lib.check(rc)
     return m
 
@@ -307,13 +312,15 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
                       prec_map: Optional[torch.Tensor] = None, uniform: Optional[str] = None,
                       sm_scale: Optional[float] = None, fp8_elem: str = "e5m2",
                       out_dtype: torch.dtype = torch.bfloat16, pv_mode: str = "fp16", check: bool = False,
-                      router: str = "band", tau: float = 1.0, fp4_kind: str = "mxfp4") -> torch.Tensor:
+                      router: str = "band", tau: float = 1.0, fp4_kind: str = "mxfp4",
+                      skip_thresh: Optional[float] = None, return_sparsity: bool = False):
     """Quantise Q/K (both MXFP8 and MXFP4 in one pass each), prepare V, build the precision map and
     run the fused forward.  q [B,Hq,S,D], k/v [B,Hkv,Skv,D]; D in {64, 128}.
 
     router "band": the static diagonal-band map.  router "online": one extra MXFP4 pass over the score tiles
     (router_statistic) promotes to MXFP8 every tile whose statistic reaches `tau` times that of the row's
-    first key tile (precision_map_online).
+    first key tile (precision_map_online); with skip_thresh it also drops the tiles the reference's router would
+    drop.  return_sparsity: also return the share of visible tiles dropped.
 
     pv_mode "fp16": P and V in fp16, the P.V precision of the reference kernel.
     pv_mode "requant": P is re-quantised to the tile's MX format and V is quantised along the sequence.
@@ -339,11 +346,20 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
         if prec_map is not None or uniform is not None:
             raise ValueError("router='online' builds its own precision map")
         stat = router_statistic(qq, kq, B, Hq, Hkv, S, Skv, causal=causal, check=check)
-        prec_map = precision_map_online(stat, S, Skv, causal=causal, band=band, tau=tau)
+        prec_map = precision_map_online(stat, S, Skv, causal=causal, band=band, tau=tau, skip_thresh=skip_thresh)
     elif router != "band":
         raise ValueError(f"unknown router {router!r}")
-    return attention_forward_quantized(qq, kq, vt, B, Hq, Hkv, S, Skv, D, causal=causal, band=band,
-                                       prec_map=prec_map, uniform=uniform, out_dtype=out_dtype, check=check)
+    elif skip_thresh is not None:
+        raise ValueError("skip_thresh needs router='online'")
+    out = attention_forward_quantized(qq, kq, vt, B, Hq, Hkv, S, Skv, D, causal=causal, band=band,
+                                      prec_map=prec_map, uniform=uniform, out_dtype=out_dtype, check=check)
+    if not return_sparsity:
+        return out
+    # share of the causally visible tiles that the router dropped
+    band_map = precision_map_band(S, Skv, causal, band, 128, q.device)
+    pm = band_map if prec_map is None else prec_map
+    visible = int((band_map != TILE_SKIP).sum()) * (pm.numel() // band_map.numel())
+    return out, 1.0 - float((pm != TILE_SKIP).sum()) / max(visible, 1)
 
 
 def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, B: int, Hq: int,

@@ -8,17 +8,20 @@ from mpsa import ops as _ops
 @torch.compiler.disable
 def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
                      is_causal=False, scale=None, smooth_k=False, attention_sink=False, tensor_layout="HND",
-                     output_dtype=torch.float16, return_sparsity=False, block_scale_type="mxfp4", skip_thresh=None, out=None):
+                     output_dtype=torch.float16, return_sparsity=False, block_scale_type="mxfp4", skip_thresh=None, out=None,
+                     promote_thresh=None):
     """q [B,Hq,S,D], k/v [B,Hkv,Skv,D] (HND) or [B,S,H,D] (NHD) -> o in q's layout.
 
     block_scale_type: "mxfp4" / "mxfp8" quantise every tile of Q.K^T to that format (the two modes
     of the reference); "diag" keeps the diagonal tiles in MXFP8 and the rest in MXFP4; "diag_requant"
     additionally re-quantises P to the tile's format before P.V (V quantised along the sequence);
     "online" / "online_requant" are the same two with the online router on top of the diagonal rule: a tile
-    is also MXFP8 if its MXFP4 statistic reaches skip_thresh times that of the row's first key tile (the
-    comparison of ours/mxfp_attn_kernel.py:272-280, used here for precision instead of skipping; default 1.1).
-    attn_mask, dropout_p, attention_sink and return_sparsity are accepted and ignored, as in the reference
-    wrapper, and so is skip_thresh outside the online modes; is_causal, scale and output_dtype are honoured
+    is also MXFP8 if its MXFP4 statistic reaches promote_thresh (default 1.1) times that of the row's first key
+    tile, and, when skip_thresh is given, a tile outside the band is dropped unless it is the row's first one or
+    its statistic reaches skip_thresh times the first tile's - the reference's rule
+    (ours/mxfp_attn_kernel.py:272-297).  return_sparsity then also returns the share of visible tiles dropped.
+    attn_mask, dropout_p and attention_sink are accepted and ignored, as in the reference wrapper, and so are
+    skip_thresh and return_sparsity outside the online modes; is_causal, scale and output_dtype are honoured
     (the reference ignores them)."""
     host = not v.is_cuda
     if host and tensor_layout != "HND":
@@ -44,13 +47,17 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
     kw = dict(causal=bool(is_causal), uniform=uniform, sm_scale=scale, out_dtype=output_dtype,
               pv_mode="requant" if block_scale_type.endswith("requant") else "fp16",
               router="online" if online else "band",
-              tau=(1.1 if skip_thresh is None else float(skip_thresh)) if online else 1.0)
+              tau=(1.1 if promote_thresh is None else float(promote_thresh)) if online else 1.0,
+              skip_thresh=skip_thresh if online else None)
     if host:
         o = _ops.attention_forward_host(q, k, v, out=out, **kw)      # `out`: a pinned CPU tensor to fill (optional)
     else:
         if out is not None:
             raise ValueError("out= is for host tensors only")
-        o = _ops.attention_forward(q, k, v, **kw)
+        o = _ops.attention_forward(q, k, v, return_sparsity=bool(return_sparsity and online), **kw)
+        if return_sparsity and online:
+            o, sparsity = o
+            return (o.transpose(1, 2) if tensor_layout == "NHD" else o), sparsity
     return o.transpose(1, 2) if tensor_layout == "NHD" else o
 
 

@@ -358,7 +358,7 @@ def router_statistic_map(q: torch.Tensor, k: torch.Tensor, *, causal: bool, sm_s
 
 
 def precision_map_online(stat: torch.Tensor, S: int, Skv: int, *, causal: bool, band: int = 1, tau: float = 1.0,
-                         tile: int = 128) -> torch.Tensor:
+                         tile: int = 128, skip_thresh: Optional[float] = None) -> torch.Tensor:
     """uint8 [B,Hq,nq,nk]: the band map, plus FP8 for every other visible tile with
     stat[i,j] >= stat[i,0] * tau (first key tile = the reference statistic, ours/mxfp_attn_kernel.py:272-276)."""
     B, Hq, nq, nk = stat.shape
@@ -372,6 +372,13 @@ def precision_map_online(stat: torch.Tensor, S: int, Skv: int, *, causal: bool, 
     promote = stat >= stat[..., :1] * tau
     m = base.expand(B, Hq, nq, nk).clone()
     m[(m == TILE_FP4) & promote] = TILE_FP8
+    if skip_thresh is not None:
+        # the reference's router: a tile is processed iff it is the first one or stat >= sink * skip_thresh
+        # (ours/mxfp_attn_kernel.py:276-280); tiles inside the band are never dropped here
+        keep = stat >= stat[..., :1] * skip_thresh
+        keep[..., 0] = True
+        outside = base.expand(B, Hq, nq, nk) == TILE_FP4
+        m[outside & ~keep] = TILE_SKIP
     return m
 
 

@@ -82,3 +82,25 @@ def test_bad_arguments():
     st = torch.zeros((1, 1, 2, 3), dtype=torch.float32, device="cuda")
     with pytest.raises(ValueError):
         mpsa.precision_map_online(st, 256, 256, causal=True)
+
+
+def test_tile_skipping_rule():
+    """The reference's router proper: outside the band a tile is processed iff it is the row's first one or its
+    statistic reaches skip_thresh times the first tile's.  Map identical to the oracle's from the same statistic;
+    the forward under that map equals the oracle's emulation; the reported sparsity counts the dropped tiles."""
+    import mpsa
+    from ours.mxfp_attn_kernel import mxfp_attn_kernel
+    q, k, v = O.make_qkv(16, 1, 4, 2, 1024, 128, outliers=3)
+    stat = _stat(q, k, 1024, 1024, 128, True)
+    pm = mpsa.precision_map_online(stat, 1024, 1024, causal=True, band=1, tau=1.1, skip_thresh=1.0)
+    exp = O.precision_map_online(stat.cpu(), 1024, 1024, causal=True, band=1, tau=1.1, skip_thresh=1.0)
+    assert torch.equal(pm.cpu(), exp)
+    band = O.precision_map_band(8, 8, True, 1)
+    dropped = int(((pm.cpu() == O.TILE_SKIP) & (band != O.TILE_SKIP)).sum())
+    assert dropped > 0 and bool((pm.cpu()[..., 0] != O.TILE_SKIP).all())
+    ref = O.attention_mxfp(q, k, v, causal=True, prec_map=exp, pv_mode="requant")
+    out, sparsity = mxfp_attn_kernel(q.cuda(), k.cuda(), v.cuda(), is_causal=True, block_scale_type="online_requant",
+                                     skip_thresh=1.0, promote_thresh=1.1, output_dtype=torch.float32, return_sparsity=True)
+    m = O.parity_metrics(out.cpu(), ref)
+    assert m["cos"] >= 0.9999 and m["rel_l2"] <= 1e-2, m
+    assert abs(sparsity - dropped / (4 * 36)) < 1e-6
