@@ -474,16 +474,40 @@ def diagonal_tiled_attention(q, k, v, causal=True, pv_mode="requant"):
 
 
 class _HostPipeline:
-    """Streams and staging buffers of attention_forward_host for one device and one chunk shape."""
+    """Streams and staging buffers of attention_forward_host for one device and one problem shape."""
 
-    def __init__(self, dev, shapes, dtype, slots=2):
+    def __init__(self, dev, grp, S, Skv, D, dtype, slots=2):
         self.h2d, self.d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-        self.slots = [tuple(torch.empty(sh, dtype=dtype, device=dev) for sh in shapes) for _ in range(slots)]
-        self.loaded = [torch.cuda.Event() for _ in range(slots)]      # the slot's inputs have arrived
-        self.consumed = [torch.cuda.Event() for _ in range(slots)]    # the forward that read the slot is done
+        self.q = [torch.empty((1, grp, S, D), dtype=dtype, device=dev) for _ in range(slots)]
+        self.kv = [(torch.empty((1, 1, Skv, D), dtype=dtype, device=dev), torch.empty((1, 1, Skv, D), dtype=dtype, device=dev))
+                   for _ in range(slots)]
+        self.q_loaded = [torch.cuda.Event() for _ in range(slots)]     # the slot's queries have arrived
+        self.q_consumed = [torch.cuda.Event() for _ in range(slots)]   # the forward that read them is done
+        self.kv_loaded = [torch.cuda.Event() for _ in range(slots)]
+        self.kv_consumed = [torch.cuda.Event() for _ in range(slots)]
 
 
 _host_pipes = {}
+
+
+def _host_chunks(B, Hkv, grp):
+    """(batch, KV group, first q-head of the group, number of q-heads) in processing order.  A KV group is the
+    unit; the first and the last group are cut into smaller pieces so that the pipeline fills and drains quickly."""
+    out = []
+    n = B * Hkv
+    for i in range(n):
+        b, g = divmod(i, Hkv)
+        if grp >= 4 and n > 1 and i == 0:
+            sizes = [1, 1, grp - 2]
+        elif grp >= 4 and n > 1 and i == n - 1:
+            sizes = [grp - 2, 1, 1]
+        else:
+            sizes = [grp]
+        h = 0
+        for sz in sizes:
+            out.append((b, g, h, sz))
+            h += sz
+    return out
 
 
 def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, out: Optional[torch.Tensor] = None,
@@ -507,40 +531,50 @@ def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
         out = torch.empty((B, Hq, S, D), dtype=out_dtype).pin_memory()
     elif out.is_cuda or out.dtype != out_dtype or tuple(out.shape) != (B, Hq, S, D) or not out.is_contiguous():
         raise ValueError("out must be a contiguous CPU tensor [B,Hq,S,D] of out_dtype")
-    shapes = ((1, grp, S, D), (1, 1, Skv, D), (1, 1, Skv, D))
-    key = (dev.index, shapes, q.dtype)
+    key = (dev.index, grp, S, Skv, D, q.dtype)
     pipe = _host_pipes.get(key)
     if pipe is None:
         _host_pipes.clear()                       # one shape at a time: the staging buffers are large
-        pipe = _host_pipes[key] = _HostPipeline(dev, shapes, q.dtype)
+        pipe = _host_pipes[key] = _HostPipeline(dev, grp, S, Skv, D, q.dtype)
     main = torch.cuda.current_stream(dev)
     start = torch.cuda.Event()
     start.record(main)
     pipe.h2d.wait_event(start)                    # the caller's earlier work on these buffers comes first
     pipe.d2h.wait_event(start)
     keep = []
-    n = 0
-    for b in range(B):
-        for g in range(Hkv):
-            slot = n % len(pipe.slots)
-            dq, dk, dv = pipe.slots[slot]
-            with torch.cuda.stream(pipe.h2d):
-                if n >= len(pipe.slots):
-                    pipe.h2d.wait_event(pipe.consumed[slot])
-                dq.copy_(q[b:b + 1, g * grp:(g + 1) * grp], non_blocking=True)
+    chunks = _host_chunks(B, Hkv, grp)
+    n_kv = -1                                      # KV groups uploaded so far - 1
+    for n, (b, g, h0, nh) in enumerate(chunks):
+        qs = n % len(pipe.q)
+        dq = pipe.q[qs][:, :nh]
+        new_kv = h0 == 0
+        if new_kv:
+            n_kv += 1
+        ks = n_kv % len(pipe.kv)
+        dk, dv = pipe.kv[ks]
+        with torch.cuda.stream(pipe.h2d):
+            if new_kv:
+                if n_kv >= len(pipe.kv):
+                    pipe.h2d.wait_event(pipe.kv_consumed[ks])
                 dk.copy_(k[b:b + 1, g:g + 1], non_blocking=True)
                 dv.copy_(v[b:b + 1, g:g + 1], non_blocking=True)
-                pipe.loaded[slot].record(pipe.h2d)
-            main.wait_event(pipe.loaded[slot])
-            o = attention_forward(dq, dk, dv, causal=causal, out_dtype=out_dtype, **kw)
-            pipe.consumed[slot].record(main)
-            done = torch.cuda.Event()
-            done.record(main)
-            with torch.cuda.stream(pipe.d2h):
-                pipe.d2h.wait_event(done)
-                out[b:b + 1, g * grp:(g + 1) * grp].copy_(o, non_blocking=True)
-            keep.append(o)                        # alive until the copies are ordered behind `main` below
-            n += 1
+                pipe.kv_loaded[ks].record(pipe.h2d)
+            if n >= len(pipe.q):
+                pipe.h2d.wait_event(pipe.q_consumed[qs])
+            dq.copy_(q[b:b + 1, g * grp + h0:g * grp + h0 + nh], non_blocking=True)
+            pipe.q_loaded[qs].record(pipe.h2d)
+        main.wait_event(pipe.kv_loaded[ks])
+        main.wait_event(pipe.q_loaded[qs])
+        o = attention_forward(dq, dk, dv, causal=causal, out_dtype=out_dtype, **kw)
+        pipe.q_consumed[qs].record(main)
+        if n + 1 == len(chunks) or chunks[n + 1][2] == 0:
+            pipe.kv_consumed[ks].record(main)      # the group's last piece has read K and V
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(pipe.d2h):
+            pipe.d2h.wait_event(done)
+            out[b:b + 1, g * grp + h0:g * grp + h0 + nh].copy_(o, non_blocking=True)
+        keep.append(o)                            # alive until the copies are ordered behind `main` below
     fin = torch.cuda.Event()
     fin.record(pipe.d2h)
     main.wait_event(fin)
