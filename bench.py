@@ -334,30 +334,47 @@ def run_ring(args):
 
 
 def cpu_baseline(steps=1, warmup=0, budget_s=25.0):
-    """The oracle (CPU restatement of the reference's algorithm, PyTorch on all host cores) on the
-    workload's head layout at S=8192: quantise, emulate both products, softmax, P.V.  The number of
-    KV groups in the sample (1..8, four query heads each) is chosen from a one-group calibration
-    pass so that all passes together take about `budget_s` seconds."""
+    """The oracle (CPU restatement of the reference's algorithm, PyTorch on all host cores) doing what one step of the
+    GPU arm does on a bounded sample of the workload: quantise Q and K, router statistic from the MXFP4 product, online
+    precision map, both products emulated tile by tile, softmax, P re-quantised, P.V.  The sample (sequence length
+    2048..8192, 1..8 KV groups of the workload's head layout, 4 or 1 query heads per group) is the largest one whose
+    predicted time - scaled from a small calibration pass by S^2 x heads - fits budget_s / (steps + warmup)."""
     from oracle import mx_oracle as O
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    S = 8192
-    q, k, v = O.make_qkv(2, 1, HQ, HKV, S, D, outliers=OUTLIERS)
+
+    def one_pass(q, k, v):
+        S = q.shape[2]
+        stat = O.router_statistic_map(q, k, causal=True)
+        pm = O.precision_map_online(stat, S, S, causal=True, band=1, tau=TAU)
+        return O.attention_mxfp(q, k, v, causal=True, prec_map=pm, pv_mode="requant")
+
+    S0 = 2048
+    q, k, v = O.make_qkv(2, 1, 4, 1, S0, D, outliers=OUTLIERS)
     t0 = time.perf_counter()
-    O.attention_mxfp(q[:, :4], k[:, :1], v[:, :1], causal=True)
-    t1 = time.perf_counter() - t0
-    groups = int(max(1, min(HKV, budget_s / max(t1, 1e-3) / max(1, steps + warmup))))
-    q, k, v = q[:, :4 * groups], k[:, :groups], v[:, :groups]
+    one_pass(q, k, v)
+    t_cal = time.perf_counter() - t0                 # 4 query heads, 1 KV group, S0
+    per_pass = budget_s / max(1, steps + warmup)
+    S, groups, hq = S0, 1, 1
+    found = False
+    for s_ in (8192, 4096, 2048):
+        for g_ in (8, 4, 2, 1):
+            for h_ in (4, 1):
+                if not found and t_cal * (s_ / S0) ** 2 * g_ * (h_ / 4.0) <= per_pass:
+                    S, groups, hq, found = s_, g_, h_, True
+    q, k, v = O.make_qkv(2, 1, HQ, HKV, S, D, outliers=OUTLIERS)
+    q = torch.cat([q[:, 4 * g:4 * g + hq] for g in range(groups)], dim=1)
+    k, v = k[:, :groups], v[:, :groups]
     for _ in range(warmup):
-        O.attention_mxfp(q, k, v, causal=True)
+        one_pass(q, k, v)
     t0 = time.perf_counter()
     for _ in range(steps):
-        O.attention_mxfp(q, k, v, causal=True)
+        one_pass(q, k, v)
     dt = (time.perf_counter() - t0) / steps
-    val = attn_flops(1, 4 * groups, S, D) / dt / 1e12
+    val = attn_flops(1, hq * groups, S, D) / dt / 1e12
     return {"value": round(val, 5), "unit": "TFLOP/s", "cores": cores, "kind": "port",
-            "sample": f"B=1 Hq={4 * groups} Hkv={groups} D={D} S={S} causal ({groups} of the workload's 8 KV groups at a "
-                      f"quarter of its length), {dt:.2f} s per pass", "seconds": round(dt, 3)}
+            "sample": f"B=1 Hq={hq * groups} Hkv={groups} D={D} S={S} causal (of the workload's 32 query heads in 8 KV groups at "
+                      f"S=32768), online router tau={TAU}, re-quantised P.V, {dt:.2f} s per pass", "seconds": round(dt, 3)}
 
 
 def run_reference(args):

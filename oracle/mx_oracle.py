@@ -341,19 +341,16 @@ def router_statistic_map(q: torch.Tensor, k: torch.Tensor, *, causal: bool, sm_s
     rows = torch.arange(S)
     cols = torch.arange(Skv)
     vis = (cols[None, :] <= rows[:, None] + off) if causal else torch.ones((S, Skv), dtype=torch.bool)
+    ninf = torch.tensor(float("-inf"))
+    n_rows = torch.clamp(S - torch.arange(nq) * tile, max=tile).to(torch.float32)       # valid rows per query tile
     for b in range(B):
         for h in range(Hq):
             s = qd[b, h] @ kd[b, h // (Hq // Hkv)].T
-            s = torch.where(vis, s, torch.tensor(float("-inf")))
-            for i in range(nq):
-                r0, r1 = i * tile, min(S, (i + 1) * tile)
-                for j in range(nk):
-                    c0, c1 = j * tile, min(Skv, (j + 1) * tile)
-                    if causal and c0 > (r1 - 1) + off:
-                        continue
-                    mx = s[r0:r1, c0:c1].amax(dim=-1)
-                    mx = torch.where(torch.isinf(mx), torch.zeros_like(mx), mx)
-                    stat[b, h, i, j] = mx.sum() / (r1 - r0)
+            s = torch.where(vis, s, ninf)
+            s = torch.nn.functional.pad(s, (0, nk * tile - Skv, 0, nq * tile - S), value=float("-inf"))
+            mx = s.view(nq, tile, nk, tile).amax(dim=-1)                                   # [nq, tile, nk] row maxima
+            mx = torch.where(torch.isinf(mx), torch.zeros_like(mx), mx)                   # no visible key: counts 0
+            stat[b, h] = mx.sum(dim=1) / n_rows[:, None]
     return stat
 
 
