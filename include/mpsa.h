@@ -141,6 +141,11 @@ int mpsa_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv
  *   fp4_kind       0: the FP4 operands of Q.K^T are MXFP4 (above).  1: NVFP4 from mpsa_quant_nvfp4_bh (q4/k4 the same
  *                  packed codes, q4_sf/k4_sf [B,H,ceil(L/128),2,512] E4M3 scale tiles); fp4_scale is then the product
  *                  of the two tensor scales, applied to the scores of the FP4 tiles.  P.V keeps the MX formats.
+ *   range_flag     optional (pv_mode 1, MXFP4): one int32, 0 on entry, private to this call.  When given, the forward runs
+ *                  with the row reference fixed after the first key tile (block-scaled P carries its magnitude in
+ *                  the scale codes, so nothing has to be rescaled while scores stay within 2^64 of that reference);
+ *                  a score beyond that sets the word, and the exact kernel, launched behind the first one, then
+ *                  recomputes the output.  Results are the same either way.  NULL: the exact kernel only.
  *   status         one int32, must be 0 on entry; a kernel whose bounded waits expire stores a
  *                  non-zero code here (1 TMA, 2 MMA, 3 pipeline) and unwinds
  */
@@ -149,7 +154,7 @@ int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void*
                   const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
                   long long map_sb, long long map_sh, void* out, int out_dtype, void* lse, int B, int Hq, int Hkv,
                   int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int fp4_kind,
-                  float fp4_scale, int* status, void* stream);
+                  float fp4_scale, int* range_flag, int* status, void* stream);
 
 /* Merges a partial attention result into an accumulator: acc fp32 [rows, D] and lse_acc fp32 [rows] are
  * updated in place with part [rows, D] (part_dtype 0 f32, 1 f16, 2 bf16) and lse_part, where every lse is

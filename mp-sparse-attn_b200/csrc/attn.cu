@@ -67,6 +67,7 @@ constexpr uint32_t ATT_COL_SFP = 400, ATT_COL_SFV = 408;
 constexpr uint32_t ATT_COL_SFQN = 416, ATT_COL_SFKN = 424;        // NVFP4 scales: Q 8 columns, K 2 x 8
 constexpr uint32_t ATT_COL_P = 448;                              // quantised P: 2 buffers of 32 columns (128 keys x 1 byte)
 constexpr float ATT_RESCALE_LOG2 = 8.0f;
+constexpr float ATT_LAZY_HEADROOM = 64.0f;            // log2: P up to 2^64 relative to the fixed reference stays far from fp32 overflow
 
 constexpr int TILE_SKIP = 0, TILE_FP8 = 1, TILE_FP4 = 2;
 
@@ -95,6 +96,8 @@ struct AttnParams {
   const uint8_t* map; long long map_sb, map_sh; // [.., nq, nk], strides may be 0 (broadcast)
   void* out; int out_dtype;          // [B,Hq,S,D] contiguous; 0 f32, 1 f16, 2 bf16
   float* lse;                        // optional [B,Hq,S]: log2 of the softmax denominator (incl. the row reference)
+  int* range_flag;                   // LAZY kernels: set to 1 when a score leaves the fixed reference's headroom
+  const int* run_if;                 // when given: the kernel does nothing unless this word is non-zero
   int* status;
 };
 
@@ -276,13 +279,20 @@ __device__ __forceinline__ uint32_t softmax_block(const uint32_t* sc, float mref
 
 // NVF4: the FP4 tiles of Q.K^T are NVFP4 (16-element blocks, E4M3 scales, kind::mxf4nvf4) instead of MXFP4; their
 // scores are multiplied by the product of the two tensor scales before the softmax.
-template <int NWG, int NSPLIT, int PVQ, int NVF4>
+// LAZY (quantised P.V only): the row reference is fixed after the first key tile.  Block-scaled P carries its
+// magnitude in E8M0 scale codes, so P, O and the row sums may exceed 1 by up to 2^ATT_LAZY_HEADROOM without loss; then
+// no tile after the first needs the row maximum agreed between threads, the reference handed over between
+// warpgroups, a second look at S or a rescale of O, and S is released as soon as it has been read.  A score beyond
+// the headroom sets *range_flag; the launcher then re-runs the exact kernel, which is launched behind this one with
+// run_if = range_flag.
+template <int NWG, int NSPLIT, int PVQ, int NVF4, int LAZY>
 __global__ void __launch_bounds__(128 + 128 * NWG * NSPLIT, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant__ CUtensorMap tm_q4,
                 const __grid_constant__ CUtensorMap tm_k8, const __grid_constant__ CUtensorMap tm_k4,
                 const __grid_constant__ CUtensorMap tm_vt, const __grid_constant__ CUtensorMap tm_vt8,
                 const __grid_constant__ CUtensorMap tm_vt4, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
+  if (p.run_if && *(volatile const int*)p.run_if == 0) return;     // conditional re-run: nothing to do
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024 - (raw & 1023)) & 1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_OFF_BAR);
@@ -582,6 +592,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     [[maybe_unused]] const int trole = (wg == 0) ? 2 : 0;
     float* mhint = mrow + 2 * 128;
     float m_seen = -INFINITY;                       // row reference this thread's partial sum refers to
+    [[maybe_unused]] float m_fix = -INFINITY;       // LAZY: the row reference fixed by the first tile
+    [[maybe_unused]] bool have_ref = false;
     float l_run = 0.0f;                             // partial row sum over this thread's tiles / columns
     bool ok = true;
     int t = 0;                                      // index among the non-skipped tiles
@@ -610,7 +622,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       // precision of P for this tile: 0 fp16; 1 MXFP8 E5M2; 2 MXFP8 E4M3; 3 MXFP4
       const int pmode = (PVQ == 0) ? 0 : ((map_row[j] == TILE_FP8) ? (p.fp8_fmt == 0 ? 2 : 1) : 3);
       // reference to start with: this thread's own on one warpgroup, else the latest published hint
-      const float m0 = (t == 0) ? -INFINITY : ((NWG > 1) ? mhint[r_in] : m_seen);
+      const bool lazy_tile = PVQ && LAZY && t > 0;
+      if (lazy_tile && !have_ref) {                  // the first tile's owner has fixed the reference
+        if (NWG > 1) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&m_bar[q], 0, p.status, KS_TIMEOUT_PIPE));
+          if (!ok) break;
+        }
+        m_fix = mrow[r_in];
+        m_seen = m_fix;
+        have_ref = true;
+      }
+      const float m0 = (t == 0) ? -INFINITY : (lazy_tile ? m_fix : ((NWG > 1) ? mhint[r_in] : m_seen));
       const float mref0 = (m0 == -INFINITY) ? 0.0f : m0;
       // ---- the pass ----
       if (ALL_UP) {
@@ -646,6 +668,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       }
       float mx = mx0;
       if (tracer) TRACE(trole, t, 2);
+      if (lazy_tile) {
+        // nothing to agree on: P and the partial sum already refer to the fixed reference; S is free
+        tc_fence_before();
+        mbar_arrive(&s_free[bsel]);
+        if (mx0 > mref0 + ATT_LAZY_HEADROOM) *p.range_flag = 1;
+      } else {
       if (NSPLIT > 1) {
         // full-row maximum = max over the NSPLIT partial maxima of this row
         float* xm = xmax + ((wg * 2 + (lt & 1)) * ATT_MAX_SPLIT) * 128;
@@ -727,11 +755,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
           if (c + 1 < NCH) tmem_ld32p(slice_addr + (c + 1) * 32, sr);
         }
       }
+      if (PVQ && LAZY && t == 0) { m_fix = m_used; have_ref = true; }
+      }  // !lazy_tile
       l_run += lsum0 + lsum1;
       if (tracer) TRACE(trole, t, 4);
       if (PVQ) {
-        tc_fence_before();
-        mbar_arrive(&s_free[bsel]);                 // this thread will not read the S buffer again
+        if (!lazy_tile) {
+          tc_fence_before();
+          mbar_arrive(&s_free[bsel]);               // this thread will not read the S buffer again
+        }
         if (t >= 2) {                               // the P buffer and its scale tile: P.V of tile t-2 has read them
           ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[bsel], ((t - 2) >> 1) & 1, p.status, KS_TIMEOUT_MMA));
           if (!ok) break;
@@ -772,7 +804,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     float l_tot = l_run;
     float m_final = m_seen;                         // reference the partial sums end up referring to
     if (NWG * NSPLIT > 1 && ok) {
-      if (NWG > 1 && t > 0) {
+      if (PVQ && LAZY) {
+        if (t > 0 && !have_ref) {                   // this thread owned no tile: all sums refer to the first tile's reference
+          if (NWG > 1) ok = __all_sync(0xffffffffu, mbar_wait(&m_bar[q], 0, p.status, KS_TIMEOUT_PIPE));
+          if (ok) m_fix = mrow[r_in];
+        }
+        if (t > 0) m_final = m_fix;
+      } else if (NWG > 1 && t > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(&m_bar[((t - 1) & 1) * 4 + q], ((t - 1) >> 1) & 1, p.status, KS_TIMEOUT_PIPE));
         if (ok) {
           const float m_fin = mrow[((t - 1) & 1) * 128 + r_in];
@@ -977,7 +1015,7 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
                              const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
                              long long map_sb, long long map_sh, void* out, int out_dtype, void* lse, int B, int Hq,
                              int Hkv, int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int fp4_kind,
-                             float fp4_scale, int* status, void* stream) {
+                             float fp4_scale, int* range_flag, int* status, void* stream) {
   if (!q8 || !q8_sf || !q4 || !q4_sf || !k8 || !k8_sf || !k4 || !k4_sf || !map || !out || !status)
     return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: null pointer");
   if (pv_mode != 0 && pv_mode != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: pv_mode must be 0 (fp16 P.V) or 1 (quantised P.V)");
@@ -1024,6 +1062,7 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   p.fp4_scale = fp4_scale;
   p.map = (const uint8_t*)map; p.map_sb = map_sb; p.map_sh = map_sh;
   p.out = out; p.out_dtype = out_dtype; p.lse = (float*)lse; p.status = status;
+  p.range_flag = nullptr; p.run_if = nullptr;
   // Softmax organisation: warpgroups taking tiles in turn (1 or 2) x threads per query row inside a
   // warpgroup (1, 2 or 4).  MPSA_ATTN_WG / MPSA_ATTN_SPLIT override the default.
   // Defaults (measured on B200 at S=32768): fp16 P.V 2 warpgroups x 1, quantised P.V 2 x 2.
@@ -1040,12 +1079,13 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
     }
     cudaError_t e = cudaSuccess;
 #define MPSA_SET_SMEM(A, B) \
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM); \
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 0, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM); \
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 1, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
     MPSA_SET_SMEM(1, 1) MPSA_SET_SMEM(1, 2) MPSA_SET_SMEM(1, 4) MPSA_SET_SMEM(2, 1) MPSA_SET_SMEM(2, 2)
 #undef MPSA_SET_SMEM
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 1, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 2, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 1, 0, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 2, 1, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 2, 1, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
     if (e != cudaSuccess) {
       cfg_of[0] = 0;
       return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
@@ -1059,15 +1099,23 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   if (pv_mode == 1 && cfg % 10 == 4)
     return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: quantised P.V needs at most 2 softmax threads per query row");
   if (fp4_kind == 1) {               // NVFP4 score tiles: the default organisation of each P.V mode only
-    if (pv_mode == 0) attn_fwd_kernel<2, 1, 0, 1><<<grid, 384, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
-    else attn_fwd_kernel<2, 2, 1, 1><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
+    if (pv_mode == 0) attn_fwd_kernel<2, 1, 0, 1, 0><<<grid, 384, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
+    else attn_fwd_kernel<2, 2, 1, 1, 0><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
     return check_launch("attn_fwd");
   }
 #define MPSA_LAUNCH(A, B, T)                                                                              \
   do {                                                                                                    \
-    if (pv_mode == 0) attn_fwd_kernel<A, B, 0, 0><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p); \
-    else attn_fwd_kernel<A, B, 1, 0><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);         \
+    if (pv_mode == 0) attn_fwd_kernel<A, B, 0, 0, 0><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p); \
+    else attn_fwd_kernel<A, B, 1, 0, 0><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);         \
   } while (0)
+  if (pv_mode == 1 && range_flag && cfg == 22) {
+    // fixed-reference kernel first; the exact kernel behind it runs only if a score left the headroom
+    p.range_flag = range_flag;
+    attn_fwd_kernel<2, 2, 1, 0, 1><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
+    if (int rc = check_launch("attn_fwd")) return rc;
+    p.range_flag = nullptr;
+    p.run_if = range_flag;
+  }
   switch (cfg) {
     case 11: MPSA_LAUNCH(1, 1, 256); break;
     case 12: MPSA_LAUNCH(1, 2, 384); break;

@@ -365,7 +365,8 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
 def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, B: int, Hq: int,
                                 Hkv: int, S: int, Skv: int, D: int, *, causal: bool, band: int = 1,
                                 prec_map: Optional[torch.Tensor] = None, uniform: Optional[str] = None,
-                                out_dtype: torch.dtype = torch.bfloat16, check: bool = False, return_lse: bool = False):
+                                out_dtype: torch.dtype = torch.bfloat16, check: bool = False, return_lse: bool = False,
+                                lazy: bool = True):
     """The fused forward on operands that are already quantised (depth padded to 128) and a V^T from
     prepare_vt (fp16 P.V) or a QuantizedV from quantize_v_seq (quantised P.V).  Both formats of Q and K
     must be present unless `uniform` restricts the map to one."""
@@ -435,13 +436,16 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
     out = torch.empty((B, Hq, S, D), dtype=out_dtype, device=dev)
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev) if return_lse else None
     st = status_word(dev)
+    # quantised P.V: a per-call word lets the library run the fixed-reference kernel with the exact one as its
+    # conditional fallback (same results, see include/mpsa.h)
+    flag = torch.zeros(1, dtype=torch.int32, device=dev) if (requant and not nvf4 and lazy) else None
     with torch.cuda.device(dev):
         rc = _lib.load().mpsa_attn_fwd(
             q8.data_ptr(), q8s.data_ptr(), q4.data_ptr(), q4s.data_ptr(),
             k8.data_ptr(), k8s.data_ptr(), k4.data_ptr(), k4s.data_ptr(),
             *vptrs, prec_map.data_ptr(), msb, msh, out.data_ptr(), _OUT_DTYPE[out_dtype], _ptr(lse),
             B, Hq, Hkv, S, Skv, D, skv_pad, int(causal), _FP8_DESC[qq.fp8_elem], int(nvf4), fp4_scale,
-            st.data_ptr(), _stream())
+            _ptr(flag), st.data_ptr(), _stream())
     _lib.check(rc)
     if check:
         check_status(dev)

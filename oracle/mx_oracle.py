@@ -113,10 +113,12 @@ def unpack_e2m1(packed: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------
 # MX block quantizers  (ours/quant_mxint8.py)
 # --------------------------------------------------------------------------------------
-def _mx_prepare(x: torch.Tensor, s: float, emax: int, vec: int = 32):
+def _mx_prepare(x: torch.Tensor, s: float, emax: int, vec: int = 32, min_sh: Optional[float] = None):
     """Shared front end of the MX quantizers: fp32 multiply by the fp32 scalar ``s``,
     32-element groups along the last axis, shared exponent and E8M0 code.
     ours/quant_mxint8.py:295-309 (fp4) / :183-197 (fp8), scale code :347-351 / :215-219.
+    ``min_sh`` (not in the reference): lower clamp of the shared exponent, for operands such as softmax
+    probabilities whose blocks can be smaller than the smallest E8M0 scale.
     """
     d = x.shape[-1]
     assert d % vec == 0
@@ -124,6 +126,8 @@ def _mx_prepare(x: torch.Tensor, s: float, emax: int, vec: int = 32):
     g = xf.reshape(*x.shape[:-1], d // vec, vec)
     amax = g.abs().amax(dim=-1, keepdim=True)
     sh = torch.floor(torch.log2(amax)) - float(emax)
+    if min_sh is not None:
+        sh = torch.clamp(sh, min=min_sh)
     scale = torch.exp2(sh)
     y = g / scale
     e = torch.floor(torch.log2(scale)) + 127.0
@@ -154,7 +158,7 @@ def quant_mxfp4_side(x: torch.Tensor, s: float = 1.0) -> Tuple[torch.Tensor, tor
 
 
 def quant_mxfp8_side(x: torch.Tensor, s: float = 1.0, elem: str = "e5m2",
-                     zero_block_code: Optional[int] = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+                     zero_block_code: Optional[int] = 0, min_sh: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """One side of ``quant_mxfp8e5``: fp8 codes (as uint8) + E8M0 scales.
     ours/quant_mxint8.py:164-221: emax_elem = 7 (:191), clamp +-57344 (:203), cast to E5M2 (:205).
 
@@ -171,7 +175,7 @@ def quant_mxfp8_side(x: torch.Tensor, s: float = 1.0, elem: str = "e5m2",
         emax, lim, dt = 8, 448.0, torch.float8_e4m3fn
     else:
         raise ValueError(elem)
-    y, e8, amax = _mx_prepare(x, s, emax=emax)
+    y, e8, amax = _mx_prepare(x, s, emax=emax, min_sh=min_sh)
     yq = torch.clamp(y, -lim, lim).to(dt).view(torch.uint8)
     if zero_block_code is not None:
         yq = torch.where(amax == 0, torch.full_like(yq, zero_block_code), yq)
@@ -504,8 +508,9 @@ def _pv_requant(p: torch.Tensor, v: torch.Tensor, cell: torch.Tensor, tile: int,
     v4c, v4s = quant_v_seq(v, "fp4")
     V8 = dequant(v8c, v8s, f8).T
     V4 = dequant(v4c, v4s, "fp4").T
-    p8c, p8s = quant_mxfp8_side(p, 1.0, "e5m2" if f8 == "fp8e5" else "e4m3")
-    y, e8, amax = _mx_prepare(p, 1.0, emax=2)
+    # the kernel clamps P's shared exponent at -126 (probabilities below that carry no weight)
+    p8c, p8s = quant_mxfp8_side(p, 1.0, "e5m2" if f8 == "fp8e5" else "e4m3", min_sh=-126.0)
+    y, e8, amax = _mx_prepare(p, 1.0, emax=2, min_sh=-126.0)
     p4c = encode_e2m1_rne(torch.where(amax == 0, torch.zeros_like(y), y)).reshape(p.shape)
     P8, P4 = dequant(p8c, p8s, f8), dequant(p4c, e8, "fp4")
     is8 = cell == TILE_FP8

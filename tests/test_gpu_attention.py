@@ -192,3 +192,31 @@ def test_host_tensors_are_streamed():
     r = mxfp_attn_kernel(q, k, v, is_causal=True, block_scale_type="diag_requant", output_dtype=torch.bfloat16, out=buf)
     torch.cuda.synchronize()
     assert r is buf and torch.equal(buf, dev_out)
+
+
+def test_fixed_reference_kernel_and_its_fallback():
+    """Quantised P.V runs with the row reference fixed after the first key tile; the exact kernel is its conditional
+    fallback.  (1) On ordinary data both give the same output.  (2) When later keys push the scores more than 2^64
+    above the first tile's maximum, the fallback must take over: the result still matches the oracle."""
+    import mpsa
+    from mpsa import ops
+    q, k, v = O.make_qkv(9, 1, 4, 2, 1024, 128, outliers=3)
+
+    def run(q, k, v, lazy):
+        sq = ops.q_side_scale(128)
+        qq, kq = mpsa.quantize_mx(q.cuda(), sq), mpsa.quantize_mx(k.cuda(), 1.0)
+        vq = mpsa.quantize_v_seq(v.cuda())
+        return ops.attention_forward_quantized(qq, kq, vq, 1, 4, 2, 1024, 1024, 128, causal=True, out_dtype=torch.float32,
+                                               check=True, lazy=lazy).cpu()
+
+    a, b = run(q, k, v, True), run(q, k, v, False)
+    assert torch.allclose(a, b, rtol=1e-5, atol=1e-6), (a - b).abs().max()
+    _check(a, O.attention_mxfp(q, k, v, causal=True, pv_mode="requant"), "fixed reference")
+    k2 = k.clone().float()
+    k2[:, :, 128:] *= 60.0                       # scores of every later tile dwarf the first tile's
+    k2 = k2.to(torch.bfloat16)
+    ref = O.attention_mxfp(q, k2, v, causal=True, pv_mode="requant")
+    out = run(q, k2, v, True)
+    assert torch.isfinite(out).all()
+    _check(out, ref, "fallback")
+    assert torch.allclose(out, run(q, k2, v, False), rtol=1e-5, atol=1e-6)
