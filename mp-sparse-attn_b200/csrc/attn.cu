@@ -223,6 +223,16 @@ __device__ __forceinline__ float block_max32(const uint32_t* sc) {
   return fmaxf(max3f(b0, b1, b2), b3);
 }
 
+// Packed fp32 pairs (one instruction for two lanes of arithmetic): (a, b) += (c, d) and (a, b) = (c, d) - (e, e).
+__device__ __forceinline__ void add2(float& a, float& b, float c, float d) {
+  asm("{\n\t.reg .b64 x, y;\n\tmov.b64 x, {%0, %1};\n\tmov.b64 y, {%2, %3};\n\tadd.rn.f32x2 x, x, y;\n\tmov.b64 {%0, %1}, x;\n\t}"
+      : "+f"(a), "+f"(b) : "f"(c), "f"(d));
+}
+__device__ __forceinline__ void sub2(float& a, float& b, float c, float d, float neg_e) {
+  asm("{\n\t.reg .b64 x, y;\n\tmov.b64 x, {%2, %3};\n\tmov.b64 y, {%4, %4};\n\tadd.rn.f32x2 x, x, y;\n\tmov.b64 {%0, %1}, x;\n\t}"
+      : "=f"(a), "=f"(b) : "f"(c), "f"(d), "f"(neg_e));
+}
+
 // One 32-key block of one query row: P = exp2(S - m) in the precision the P.V product uses.
 //   PMODE 0: fp16 pairs (16 words).  PMODE 1/2: MXFP8 E5M2/E4M3 (8 words), PMODE 3: MXFP4 (4 words), with the
 //   block's E8M0 scale code returned: shared exponent floor(log2(amax P)) - emax = floor(bmax - m) - emax,
@@ -232,12 +242,14 @@ template <int PMODE>
 __device__ __forceinline__ uint32_t softmax_block(const uint32_t* sc, float mref, float bmax, uint32_t* pk,
                                                   float& lsum0, float& lsum1) {
   if (PMODE == 0) {
+    const float nm = -mref;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float p0 = ex2(__uint_as_float(sc[2 * i]) - mref);
-      const float p1 = ex2(__uint_as_float(sc[2 * i + 1]) - mref);
-      lsum0 += p0;
-      lsum1 += p1;
+      float x0, x1;
+      sub2(x0, x1, __uint_as_float(sc[2 * i]), __uint_as_float(sc[2 * i + 1]), nm);
+      const float p0 = ex2(x0);
+      const float p1 = ex2(x1);
+      add2(lsum0, lsum1, p0, p1);
       pk[i] = pack_f16x2(p0, p1);
     }
     return 0;
@@ -254,12 +266,14 @@ __device__ __forceinline__ uint32_t softmax_block(const uint32_t* sc, float mref
     const float cb = mref + (float)sh;            // exact: mref is integral in this mode
     float y[32];
     float a0 = 0.0f, a1 = 0.0f;
+    const float ncb = -cb;
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
-      y[i] = ex2(__uint_as_float(sc[i]) - cb);
-      y[i + 1] = ex2(__uint_as_float(sc[i + 1]) - cb);
-      a0 += y[i];
-      a1 += y[i + 1];
+      float x0, x1;
+      sub2(x0, x1, __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]), ncb);
+      y[i] = ex2(x0);
+      y[i + 1] = ex2(x1);
+      add2(a0, a1, y[i], y[i + 1]);
     }
     const float two_sh = __uint_as_float((uint32_t)(sh + 127) << 23);
     lsum0 = fmaf(a0, two_sh, lsum0);
