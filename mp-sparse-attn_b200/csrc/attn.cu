@@ -20,7 +20,9 @@
 //               accumulates each tile in fp16 first).  pv_mode 1: P is re-quantised to the tile's
 //               format (MXFP8 or MXFP4, one E8M0 scale per 32 keys, written by the softmax threads)
 //               and multiplied with V quantised along the sequence, as block-scaled MMAs with P in
-//               TMEM; the row reference is kept integral so that the codes do not depend on it.
+//               TMEM (its own columns, so that Q.K^T of tile t+2 can be issued before P.V of tile t); the
+//               row reference is kept integral so that the codes do not depend on it.  By default the
+//               reference is fixed after the first key tile (template parameter LAZY, see the kernel).
 // Roles: warp 0 TMA producer, warp 1 MMA issuer (warps 2-3 idle), warps 4.. softmax/correction/epilogue.  S is
 // double-buffered in TMEM so that Q.K^T of tile t+1 overlaps the softmax of tile t.  NWG softmax
 // warpgroups take the key tiles in turn (warpgroup w owns tiles t = w mod NWG), so that the
