@@ -141,7 +141,7 @@ int mpsa_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv
  *   fp4_kind       0: the FP4 operands of Q.K^T are MXFP4 (above).  1: NVFP4 from mpsa_quant_nvfp4_bh (q4/k4 the same
  *                  packed codes, q4_sf/k4_sf [B,H,ceil(L/128),2,512] E4M3 scale tiles); fp4_scale is then the product
  *                  of the two tensor scales, applied to the scores of the FP4 tiles.  P.V keeps the MX formats.
- *   range_flag     optional (pv_mode 1, MXFP4): one int32, 0 on entry, private to this call.  When given, the forward runs
+ *   range_flag     optional (pv_mode 1): one int32, 0 on entry, private to this call.  When given, the forward runs
  *                  with the row reference fixed after the first key tile (block-scaled P carries its magnitude in
  *                  the scale codes, so nothing has to be rescaled while scores stay within 2^64 of that reference);
  *                  a score beyond that sets the word, and the exact kernel, launched behind the first one, then

@@ -688,7 +688,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         // nothing to agree on: P and the partial sum already refer to the fixed reference; S is free
         tc_fence_before();
         mbar_arrive(&s_free[bsel]);
-        if (mx0 > mref0 + ATT_LAZY_HEADROOM) *p.range_flag = 1;
+        if (m_glob < p.S && mx0 > mref0 + ATT_LAZY_HEADROOM) *p.range_flag = 1;   // rows of the ragged tail hold no data
       } else {
       if (NSPLIT > 1) {
         // full-row maximum = max over the NSPLIT partial maxima of this row
@@ -1102,6 +1102,7 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 1, 0, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 2, 1, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 2, 1, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 2, 1, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
     if (e != cudaSuccess) {
       cfg_of[0] = 0;
       return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
@@ -1115,8 +1116,18 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   if (pv_mode == 1 && cfg % 10 == 4)
     return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: quantised P.V needs at most 2 softmax threads per query row");
   if (fp4_kind == 1) {               // NVFP4 score tiles: the default organisation of each P.V mode only
-    if (pv_mode == 0) attn_fwd_kernel<2, 1, 0, 1, 0><<<grid, 384, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
-    else attn_fwd_kernel<2, 2, 1, 1, 0><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
+    if (pv_mode == 0) {
+      attn_fwd_kernel<2, 1, 0, 1, 0><<<grid, 384, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
+    } else {
+      if (range_flag) {              // fixed-reference kernel first, the exact one as its conditional fallback
+        p.range_flag = range_flag;
+        attn_fwd_kernel<2, 2, 1, 1, 1><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
+        if (int rc = check_launch("attn_fwd")) return rc;
+        p.range_flag = nullptr;
+        p.run_if = range_flag;
+      }
+      attn_fwd_kernel<2, 2, 1, 1, 0><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
+    }
     return check_launch("attn_fwd");
   }
 #define MPSA_LAUNCH(A, B, T)                                                                              \

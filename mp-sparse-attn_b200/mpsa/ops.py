@@ -17,6 +17,7 @@ _OUT_DTYPE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.float
 _FP8_QUANT = {"e5m2": 1, "e4m3": 2}
 _FP8_DESC = {"e5m2": 1, "e4m3": 0}
 _status = {}
+_last_range_flag = None
 
 
 def _stream():
@@ -438,7 +439,9 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
     st = status_word(dev)
     # quantised P.V: a per-call word lets the library run the fixed-reference kernel with the exact one as its
     # conditional fallback (same results, see include/mpsa.h)
-    flag = torch.zeros(1, dtype=torch.int32, device=dev) if (requant and not nvf4 and lazy) else None
+    flag = torch.zeros(1, dtype=torch.int32, device=dev) if (requant and lazy) else None
+    global _last_range_flag
+    _last_range_flag = flag                       # kept for inspection: non-zero after the call = the exact kernel took over
     with torch.cuda.device(dev):
         rc = _lib.load().mpsa_attn_fwd(
             q8.data_ptr(), q8s.data_ptr(), q4.data_ptr(), q4s.data_ptr(),

@@ -220,3 +220,14 @@ def test_fixed_reference_kernel_and_its_fallback():
     assert torch.isfinite(out).all()
     _check(out, ref, "fallback")
     assert torch.allclose(out, run(q, k2, v, False), rtol=1e-5, atol=1e-6)
+
+
+def test_fixed_reference_is_not_abandoned_on_ragged_shapes():
+    """The padding rows of a ragged last query tile hold no data: they must not trigger the exact-kernel fallback."""
+    import mpsa
+    from mpsa import ops
+    for S, causal in ((1560, False), (300, True)):
+        q, k, v = O.make_qkv(10, 1, 2, 2, S, 128)
+        out = mpsa.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal=causal, pv_mode="requant", out_dtype=torch.float32, check=True)
+        assert int(ops._last_range_flag.item()) == 0
+        _check(out.cpu(), O.attention_mxfp(q, k, v, causal=causal, pv_mode="requant"), ("ragged", S))
