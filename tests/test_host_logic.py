@@ -24,3 +24,40 @@ def test_host_chunks_cut_first_and_last_group_finer():
     assert [c[3] for c in chunks[:3]] == [1, 1, 2] and [c[3] for c in chunks[-3:]] == [2, 1, 1]
     assert all(c[3] == 4 for c in chunks[3:-3])
     assert _host_chunks(1, 1, 4) == [(0, 0, 0, 4)]          # a single group is not cut
+
+
+def test_oracle_router_statistic_equals_a_naive_loop():
+    """The vectorised router statistic of the oracle against a tile-by-tile restatement of its definition
+    (mean over the query rows of the row maximum over the visible keys; rows without a visible key count 0)."""
+    import torch
+    from oracle import mx_oracle as O
+    for (S, Skv, causal, D) in [(300, 300, True, 64), (256, 640, True, 128), (200, 330, False, 128)]:
+        q, _, _ = O.make_qkv(21, 1, 2, 2, S, D)
+        _, k, _ = O.make_qkv(22, 1, 1, 1, Skv, D, outliers=2)
+        got = O.router_statistic_map(q, k, causal=causal)
+        qc, qs = O.quant_mxfp4_side(q, O.q_side_scale(D))
+        kc, ks = O.quant_mxfp4_side(k, 1.0)
+        qd, kd = O.dequant(qc, qs, "fp4").float(), O.dequant(kc, ks, "fp4").float()
+        off = Skv - S
+        for h in range(2):
+            s = qd[0, h] @ kd[0, 0].T
+            for i in range(-(-S // 128)):
+                for j in range(-(-Skv // 128)):
+                    rows = range(i * 128, min(S, i * 128 + 128))
+                    tot = 0.0
+                    for r in rows:
+                        cols = [c for c in range(j * 128, min(Skv, j * 128 + 128)) if (not causal) or c <= r + off]
+                        if cols:
+                            tot += float(s[r, cols].max())
+                    exp = tot / len(rows)
+                    assert abs(float(got[0, h, i, j]) - exp) <= 1e-4 * max(1.0, abs(exp)), (S, Skv, causal, h, i, j)
+
+
+def test_oracle_online_map_rules():
+    import torch
+    from oracle import mx_oracle as O
+    stat = torch.tensor([[[[4.0, 0, 0, 0], [4.0, 5.0, 0, 0], [4.0, 3.0, 9.0, 0], [4.0, 4.4, 1.0, 2.0]]]])
+    m = O.precision_map_online(stat, 512, 512, causal=True, band=1, tau=1.1)
+    assert m[0, 0].tolist() == [[1, 0, 0, 0], [2, 1, 0, 0], [2, 2, 1, 0], [2, 1, 2, 1]]
+    m = O.precision_map_online(stat, 512, 512, causal=True, band=1, tau=1.1, skip_thresh=0.5)
+    assert m[0, 0].tolist() == [[1, 0, 0, 0], [2, 1, 0, 0], [2, 2, 1, 0], [2, 1, 0, 1]]      # the first tile and the band are never dropped
