@@ -146,6 +146,9 @@ int mpsa_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv
  *                  the scale codes, so nothing has to be rescaled while scores stay within 2^64 of that reference);
  *                  a score beyond that sets the word, and the exact kernel, launched behind the first one, then
  *                  recomputes the output.  Results are the same either way.  NULL: the exact kernel only.
+ *   acc_in, lse_in optional, together: an earlier partial result (fp32 [B,Hq,S,D], log2 denominators [B,Hq,S]) over OTHER keys;
+ *                  out (fp32) and lse then receive the merged result (buffers distinct from the inputs), which saves
+ *                  the separate mpsa_attn_merge pass
  *   status         one int32, must be 0 on entry; a kernel whose bounded waits expire stores a
  *                  non-zero code here (1 TMA, 2 MMA, 3 pipeline) and unwinds
  */
@@ -154,7 +157,8 @@ int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void*
                   const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
                   long long map_sb, long long map_sh, void* out, int out_dtype, void* lse, int B, int Hq, int Hkv,
                   int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int fp4_kind,
-                  float fp4_scale, int* range_flag, int* status, void* stream);
+                  float fp4_scale, int* range_flag,
+                  const void* acc_in, const void* lse_in, int* status, void* stream);
 
 /* Merges a partial attention result into an accumulator: acc fp32 [rows, D] and lse_acc fp32 [rows] are
  * updated in place with part [rows, D] (part_dtype 0 f32, 1 f16, 2 bf16) and lse_part, where every lse is

@@ -98,6 +98,8 @@ struct AttnParams {
   const uint8_t* map; long long map_sb, map_sh; // [.., nq, nk], strides may be 0 (broadcast)
   void* out; int out_dtype;          // [B,Hq,S,D] contiguous; 0 f32, 1 f16, 2 bf16
   float* lse;                        // optional [B,Hq,S]: log2 of the softmax denominator (incl. the row reference)
+  const float* acc_in;               // optional [B,Hq,S,D] fp32 + lse_in [B,Hq,S]: an earlier partial result over OTHER keys;
+  const float* lse_in;               // the kernel then writes the merged result (out must be fp32, lse is required)
   int* range_flag;                   // LAZY kernels: set to 1 when a score leaves the fixed reference's headroom
   const int* run_if;                 // when given: the kernel does nothing unless this word is non-zero
   int* status;
@@ -851,10 +853,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       tc_fence_after();
     }
     if (ok) {
-      const float inv_l = (t > 0 && l_tot > 0.0f) ? 1.0f / l_tot : 0.0f;
+      float inv_l = (t > 0 && l_tot > 0.0f) ? 1.0f / l_tot : 0.0f;
       const long long o_off = ((long long)(b * p.Hq + h) * p.S + m_glob) * p.D;
+      float lse_row = (t > 0 && l_tot > 0.0f) ? m_final + log2f(l_tot) : -INFINITY;
+      float w_prev = 0.0f;                          // weight of the earlier partial result (merge mode)
+      if (p.acc_in && m_glob < p.S) {
+        // two normalised partial results over disjoint key sets combine with weights 2^(lse_i - lse),
+        // lse = log2(2^lse_a + 2^lse_b); every thread of a row computes the same numbers
+        const float la = p.lse_in[(long long)(b * p.Hq + h) * p.S + m_glob];
+        const float lm = fmaxf(la, lse_row);
+        if (lm != -INFINITY) {
+          const float ea = exp2f(la - lm), eb = exp2f(lse_row - lm);
+          const float inv = 1.0f / (ea + eb);
+          w_prev = ea * inv;
+          inv_l *= eb * inv;
+          lse_row = lm + log2f(ea + eb);
+        }
+      }
       if (p.lse && part == 0 && m_glob < p.S)       // log2(sum_k exp2(S_k)): lets partial results be merged
-        p.lse[(long long)(b * p.Hq + h) * p.S + m_glob] = (t > 0 && l_tot > 0.0f) ? m_final + log2f(l_tot) : -INFINITY;
+        p.lse[(long long)(b * p.Hq + h) * p.S + m_glob] = lse_row;
       for (int c = part; c < p.D / 32; c += NWG * NSPLIT) {
         uint32_t o[32];
         if (t > 0) {
@@ -867,10 +884,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         if (m_glob < p.S) {
           if (p.out_dtype == 0) {
             float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o_off + c * 32);
+            if (p.acc_in) {
+              const float4* src = reinterpret_cast<const float4*>(p.acc_in + o_off + c * 32);
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              dst[i] = make_float4(__uint_as_float(o[4 * i]) * inv_l, __uint_as_float(o[4 * i + 1]) * inv_l,
-                                   __uint_as_float(o[4 * i + 2]) * inv_l, __uint_as_float(o[4 * i + 3]) * inv_l);
+              for (int i = 0; i < 8; ++i) {
+                const float4 a = src[i];
+                dst[i] = make_float4(fmaf(a.x, w_prev, __uint_as_float(o[4 * i]) * inv_l), fmaf(a.y, w_prev, __uint_as_float(o[4 * i + 1]) * inv_l),
+                                     fmaf(a.z, w_prev, __uint_as_float(o[4 * i + 2]) * inv_l), fmaf(a.w, w_prev, __uint_as_float(o[4 * i + 3]) * inv_l));
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                dst[i] = make_float4(__uint_as_float(o[4 * i]) * inv_l, __uint_as_float(o[4 * i + 1]) * inv_l,
+                                     __uint_as_float(o[4 * i + 2]) * inv_l, __uint_as_float(o[4 * i + 3]) * inv_l);
+            }
           } else {
             uint32_t w[16];
 #pragma unroll
@@ -1031,7 +1058,8 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
                              const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
                              long long map_sb, long long map_sh, void* out, int out_dtype, void* lse, int B, int Hq,
                              int Hkv, int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int fp4_kind,
-                             float fp4_scale, int* range_flag, int* status, void* stream) {
+                             float fp4_scale, int* range_flag, const void* acc_in, const void* lse_in, int* status,
+                             void* stream) {
   if (!q8 || !q8_sf || !q4 || !q4_sf || !k8 || !k8_sf || !k4 || !k4_sf || !map || !out || !status)
     return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: null pointer");
   if (pv_mode != 0 && pv_mode != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: pv_mode must be 0 (fp16 P.V) or 1 (quantised P.V)");
@@ -1043,6 +1071,9 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   if (out_dtype < 0 || out_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: out_dtype must be 0 (f32), 1 (f16) or 2 (bf16)");
   if (fp8_fmt != 0 && fp8_fmt != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: fp8_fmt must be 0 (E4M3) or 1 (E5M2)");
   if (fp4_kind != 0 && fp4_kind != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: fp4_kind must be 0 (MXFP4) or 1 (NVFP4)");
+  if ((acc_in != nullptr) != (lse_in != nullptr)) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: acc_in and lse_in go together");
+  if (acc_in && (out_dtype != 0 || !lse || acc_in == out || lse_in == lse || ((uintptr_t)acc_in % 16)))
+    return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: merging needs fp32 out, lse, 16-byte aligned acc_in, and outputs distinct from the inputs");
   if (fp4_kind == 1 && !(fp4_scale > 0.0f)) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: NVFP4 needs a positive fp4_scale");
   if (causal && Skv < S) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: causal needs Skv >= S");
   if (Skv_pad < Skv || Skv_pad % 128) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: Skv_pad must be Skv rounded up to 128");
@@ -1079,6 +1110,7 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   p.map = (const uint8_t*)map; p.map_sb = map_sb; p.map_sh = map_sh;
   p.out = out; p.out_dtype = out_dtype; p.lse = (float*)lse; p.status = status;
   p.range_flag = nullptr; p.run_if = nullptr;
+  p.acc_in = (const float*)acc_in; p.lse_in = (const float*)lse_in;
   // Softmax organisation: warpgroups taking tiles in turn (1 or 2) x threads per query row inside a
   // warpgroup (1, 2 or 4).  MPSA_ATTN_WG / MPSA_ATTN_SPLIT override the default.
   // Defaults (measured on B200 at S=32768): fp16 P.V 2 warpgroups x 1, quantised P.V 2 x 2.

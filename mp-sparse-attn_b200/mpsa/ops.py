@@ -367,7 +367,7 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
                                 Hkv: int, S: int, Skv: int, D: int, *, causal: bool, band: int = 1,
                                 prec_map: Optional[torch.Tensor] = None, uniform: Optional[str] = None,
                                 out_dtype: torch.dtype = torch.bfloat16, check: bool = False, return_lse: bool = False,
-                                lazy: bool = True):
+                                lazy: bool = True, merge_with=None):
     """The fused forward on operands that are already quantised (depth padded to 128) and a V^T from
     prepare_vt (fp16 P.V) or a QuantizedV from quantize_v_seq (quantised P.V).  Both formats of Q and K
     must be present unless `uniform` restricts the map to one."""
@@ -434,6 +434,14 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
         raise ValueError("MXFP8 operands missing but the precision map may select FP8 tiles")
     if (qq.fp4 is None or kq.fp4 is None) and uniform != "fp8":
         raise ValueError("MXFP4 operands missing but the precision map may select FP4 tiles")
+    acc_in = lse_in = None
+    if merge_with is not None:
+        # (acc, lse) of an earlier partial result over other keys: the kernel's epilogue merges instead of a second pass
+        acc_in, lse_in = merge_with
+        if acc_in.dtype != torch.float32 or tuple(acc_in.shape) != (B, Hq, S, D) or not acc_in.is_contiguous() or \
+                lse_in.dtype != torch.float32 or tuple(lse_in.shape) != (B, Hq, S) or not lse_in.is_contiguous():
+            raise ValueError("merge_with = (fp32 [B,Hq,S,D], fp32 [B,Hq,S]), both contiguous")
+        out_dtype, return_lse = torch.float32, True
     out = torch.empty((B, Hq, S, D), dtype=out_dtype, device=dev)
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev) if return_lse else None
     st = status_word(dev)
@@ -448,7 +456,7 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
             k8.data_ptr(), k8s.data_ptr(), k4.data_ptr(), k4s.data_ptr(),
             *vptrs, prec_map.data_ptr(), msb, msh, out.data_ptr(), _OUT_DTYPE[out_dtype], _ptr(lse),
             B, Hq, Hkv, S, Skv, D, skv_pad, int(causal), _FP8_DESC[qq.fp8_elem], int(nvf4), fp4_scale,
-            _ptr(flag), st.data_ptr(), _stream())
+            _ptr(flag), _ptr(acc_in), _ptr(lse_in), st.data_ptr(), _stream())
     _lib.check(rc)
     if check:
         check_status(dev)

@@ -142,17 +142,21 @@ class CudaRingBackend:
                                  views[2].view(B, Hkv, D, pad // 2), views[3].view(B, Hkv, pad // 128, 512), self.fp8_elem)
         return kq, vq
 
-    def partial(self, qq, local_kv, payload, kind):
-        """Attention of one query block against one key block -> (normalised output, log2 denominator)."""
+    def partial(self, qq, local_kv, payload, kind, merge_with=None):
+        """Attention of one query block against one key block -> (normalised output, log2 denominator); with
+        merge_with = (acc, lse) the result is already merged with that earlier partial result."""
         rows = self.rows
         if kind == DIAG:
             kq, vq = local_kv
             return self.ops.attention_forward_quantized(qq, kq, vq, self.B, self.Hq, self.Hkv, rows, rows, self.D,
-                                                        causal=True, out_dtype=torch.float32, return_lse=True)
+                                                        causal=True, out_dtype=torch.float32, return_lse=True,
+                                                        merge_with=merge_with)
         kq, vq = self._unpack(payload)
         return self.ops.attention_forward_quantized(qq, kq, vq, self.B, self.Hq, self.Hkv, rows, rows, self.D,
                                                     causal=False, uniform="fp4", out_dtype=torch.float32,
-                                                    return_lse=True)
+                                                    return_lse=True, merge_with=merge_with)
+
+    fused_merge = True                             # partial() can merge in its epilogue
 
     def new_accumulator(self):
         acc = torch.zeros((self.B, self.Hq, self.rows, self.D), dtype=torch.float32, device=self.device)
@@ -209,8 +213,12 @@ def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
             works = _exchange(dist, group, cur, nxt, sched.send_to, sched.recv_from)
         blocks = backend.split_payload(cur, nb)
         for qi, ki, kind in sched.pairs_at(step):
-            o, lse = backend.partial(qqs[qi], local[ki] if step == 0 else None, blocks[ki], kind)
-            backend.merge(accs[qi][0], accs[qi][1], o, lse)
+            if getattr(backend, "fused_merge", False):
+                # the forward's epilogue merges with what has been accumulated so far (fresh output buffers each time)
+                accs[qi] = backend.partial(qqs[qi], local[ki] if step == 0 else None, blocks[ki], kind, merge_with=accs[qi])
+            else:
+                o, lse = backend.partial(qqs[qi], local[ki] if step == 0 else None, blocks[ki], kind)
+                backend.merge(accs[qi][0], accs[qi][1], o, lse)
         if works is not None:
             for w in works:
                 w.wait()

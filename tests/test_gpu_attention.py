@@ -231,3 +231,34 @@ def test_fixed_reference_is_not_abandoned_on_ragged_shapes():
         out = mpsa.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal=causal, pv_mode="requant", out_dtype=torch.float32, check=True)
         assert int(ops._last_range_flag.item()) == 0
         _check(out.cpu(), O.attention_mxfp(q, k, v, causal=causal, pv_mode="requant"), ("ragged", S))
+
+
+@pytest.mark.parametrize("pv_mode", ["fp16", "requant"])
+def test_merge_in_the_epilogue(pv_mode):
+    """A forward over the second half of the keys, given the partial result over the first half, writes the merged
+    result itself: it must equal the separate merge pass, and the attention over all keys up to quantisation of
+    V in halves (V's block scales do not depend on the split: its blocks are 32 keys long)."""
+    import mpsa
+    from mpsa import ops
+    B, Hq, Hkv, S, D = 1, 4, 2, 512, 128
+    q, k, v = O.make_qkv(12, B, Hq, Hkv, S, D, outliers=2)
+    qq = mpsa.quantize_mx(q.cuda(), ops.q_side_scale(D))
+    halves = []
+    for sl in (slice(0, S // 2), slice(S // 2, S)):
+        vh = v[:, :, sl].contiguous().cuda()
+        halves.append((mpsa.quantize_mx(k[:, :, sl].contiguous().cuda(), 1.0),
+                       mpsa.quantize_v_seq(vh) if pv_mode == "requant" else ops.prepare_vt(vh)))
+    kw = dict(causal=False, uniform="fp4", out_dtype=torch.float32, check=True)
+    a0, l0 = ops.attention_forward_quantized(qq, *halves[0], B, Hq, Hkv, S, S // 2, D, return_lse=True, **kw)
+    a1, l1 = ops.attention_forward_quantized(qq, *halves[1], B, Hq, Hkv, S, S // 2, D, return_lse=True, **kw)
+    fused, lf = ops.attention_forward_quantized(qq, *halves[1], B, Hq, Hkv, S, S // 2, D, merge_with=(a0, l0), **kw)
+    acc, lacc = a0.clone(), l0.clone()
+    mpsa.attention_merge(acc, lacc, a1, l1)
+    assert torch.allclose(fused, acc, rtol=1e-5, atol=1e-6), (fused - acc).abs().max()
+    assert torch.allclose(lf, lacc, rtol=1e-6, atol=1e-5)
+    ref = O.attention_mxfp(q, k, v, causal=False, uniform="fp4", pv_mode=pv_mode)
+    _check(fused.cpu(), ref, ("merged", pv_mode))
+    # an empty earlier result (lse = -inf) leaves the plain forward
+    z, lz = torch.zeros_like(a0), torch.full_like(l0, float("-inf"))
+    alone, _ = ops.attention_forward_quantized(qq, *halves[1], B, Hq, Hkv, S, S // 2, D, merge_with=(z, lz), **kw)
+    assert torch.allclose(alone, a1, rtol=1e-6, atol=1e-7)
