@@ -308,13 +308,13 @@ def run_ring(args):
         torch.cuda.synchronize()
 
     for _ in range(W):
-        ring_attention(q, k, v, causal=True, layout=args.layout)
+        ring_attention(q, k, v, causal=True, layout=args.layout, exchange=args.exchange)
     mpsa.check_status(dev)
     sync_all()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(K):
-        ring_attention(q, k, v, causal=True, layout=args.layout)
+        ring_attention(q, k, v, causal=True, layout=args.layout, exchange=args.exchange)
     e1.record()
     sync_all()
     t = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -328,7 +328,7 @@ def run_ring(args):
             "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 3),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "mxfp8/mxfp4 (fp32 accumulate)",
             "data": "synthetic", "config": {"workload": f"cfg5 causal B=1 Hq=32 Hkv=8 D=128 S={S} sequence-sharded, "
-                                                        f"{args.layout} ownership, MXFP4 K/V ring over NCCL",
+                                                        f"{args.layout} ownership, MXFP4 K/V " + ("ring (send/recv)" if args.exchange == "ring" else "all-gather") + " over NCCL",
                                             "work_units_per_rank": sched.work_units()}}))
     dist.destroy_process_group()
 
@@ -458,6 +458,8 @@ def main():
                          "sequence-sharded over the GPUs (strong scaling); gemm: the standalone block-scaled GEMM (1 GPU)")
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of --workload gemm")
     ap.add_argument("--layout", default="zigzag", choices=["contiguous", "zigzag"])
+    ap.add_argument("--exchange", default="ring", choices=["ring", "gather"],
+                    help="ring workload: K/V blocks by send/recv round the ring, or one all-gather")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

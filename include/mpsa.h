@@ -134,7 +134,10 @@ int mpsa_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv
  *   *_sf           tiled scales [B,H,ceil(L/128),512]
  *   pv_mode 0      P and V in fp16 (the reference's P.V precision): vt from mpsa_prepare_vt
  *   pv_mode 1      P re-quantised to the tile's format, V from mpsa_quant_v_seq (vt8, v8_sf, vt4, v4_sf)
+ *   Skv_pad        keys per row of the V^T buffers (the value given to mpsa_prepare_vt / mpsa_quant_v_seq): any multiple
+ *                  of 128 that is at least Skv
  *   map            uint8 [.., ceil(S/128), ceil(Skv/128)] with batch / head strides map_sb / map_sh (0 = shared)
+ *                  (0 skip, 1 MXFP8, 2 FP4; a CTA walks only from the first to the last non-skipped tile of its row)
  *   out            [B,Hq,S,D] contiguous
  *   lse            optional fp32 [B,Hq,S]: log2 of each row's softmax denominator (for merging partial results)
  *   fp8_fmt        descriptor format of the fp8 codes: 0 E4M3, 1 E5M2

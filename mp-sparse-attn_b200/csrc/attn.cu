@@ -94,6 +94,7 @@ struct AttnParams {
   const uint8_t* k8_sf; const uint8_t* k4_sf;   // [B,Hkv,nk,512]
   const uint8_t* v8_sf; const uint8_t* v4_sf;   // [B,Hkv,nk,512] (pv_mode 1)
   int pv_mode;                       // 0: P and V in fp16; 1: P and V in the tile's MX format
+  int v_tiles;                       // 128-key scale tiles per head in v8_sf / v4_sf (= Skv_pad / 128)
   float fp4_scale;                   // NVFP4 score tiles: product of the tensor scales of Q and K
   const uint8_t* map; long long map_sb, map_sh; // [.., nq, nk], strides may be 0 (broadcast)
   void* out; int out_dtype;          // [B,Hq,S,D] contiguous; 0 f32, 1 f16, 2 bf16
@@ -340,8 +341,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   const uint8_t* map_glob = p.map + (long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk;
   // every role walks this row once per tile; keep it in shared memory when it fits
   const uint8_t* map_row = (nk <= ATT_MAP_SMEM) ? (smem + ATT_OFF_MAP) : map_glob;
-  if (nk <= ATT_MAP_SMEM)
-    for (int i = threadIdx.x; i < nk; i += blockDim.x) smem[ATT_OFF_MAP + i] = map_glob[i];
+  // [first, last + 1) non-skipped tile of the row: the roles walk only that range, so the tiles above a causal
+  // diagonal, or the unused end of a longer key buffer, cost nothing
+  int* vis = reinterpret_cast<int*>(tmem_slot + 1);
+  if (threadIdx.x == 0) { vis[0] = nk; vis[1] = 0; }
+  __syncthreads();
+  for (int i0 = 0; i0 < nk; i0 += blockDim.x) {
+    const int i = i0 + threadIdx.x;
+    const uint8_t c = i < nk ? map_glob[i] : (uint8_t)TILE_SKIP;
+    if (i < nk && nk <= ATT_MAP_SMEM) smem[ATT_OFF_MAP + i] = c;
+    const int lo = __reduce_min_sync(0xffffffffu, c != TILE_SKIP ? i : nk);
+    const int hi = __reduce_max_sync(0xffffffffu, c != TILE_SKIP ? i + 1 : 0);
+    if ((threadIdx.x & 31) == 0 && hi > 0) { atomicMin(&vis[0], lo); atomicMax(&vis[1], hi); }
+  }
   if (threadIdx.x < 128) reinterpret_cast<float*>(smem + ATT_OFF_MROW)[2 * 128 + threadIdx.x] = -INFINITY;   // reference hint
   const int off = p.Skv - p.S;                      // queries are aligned to the end of the keys
 
@@ -360,6 +372,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  const int j_lo = vis[0], j_hi = vis[1];           // j_lo >= j_hi: the row has no tile to visit
 
   uint8_t* sQ8 = smem + ATT_OFF_Q8;
   uint8_t* sQ4 = smem + ATT_OFF_Q4;
@@ -385,13 +398,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
 
       const int k_row0 = (b * p.Hkv + hk) * p.Skv;
       const long long ksf0 = (long long)(b * p.Hkv + hk) * nk * 512;
+      const long long vsf0 = (long long)(b * p.Hkv + hk) * p.v_tiles * 512;
       const int v_row = (b * p.Hkv + hk) * p.D;
       bool ok = true;
       int tk = 0, tv = 0;                          // tiles issued on the K and V rings
-      int jk = 0, jv = 0;                          // next key-tile index to examine for each ring
+      int jk = j_lo, jv = j_lo;                    // next key-tile index to examine for each ring
       auto issue_k = [&]() {                       // returns false when no tile is left
-        while (jk < nk && map_row[jk] == TILE_SKIP) ++jk;
-        if (jk >= nk) return false;
+        while (jk < j_hi && map_row[jk] == TILE_SKIP) ++jk;
+        if (jk >= j_hi) return false;
         const int s = tk % ATT_KSTAGES;
         if (tk >= ATT_KSTAGES) ok = mbar_wait(&k_empty[s], ((tk / ATT_KSTAGES) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
         if (!ok) return false;
@@ -404,8 +418,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         return true;
       };
       auto issue_v = [&]() {
-        while (jv < nk && map_row[jv] == TILE_SKIP) ++jv;
-        if (jv >= nk) return false;
+        while (jv < j_hi && map_row[jv] == TILE_SKIP) ++jv;
+        if (jv >= j_hi) return false;
         const int s = tv % ATT_VSTAGES;
         if (tv >= ATT_VSTAGES) ok = mbar_wait(&v_empty[s], ((tv / ATT_VSTAGES) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
         if (!ok) return false;
@@ -418,7 +432,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
           const bool f8 = map_row[jv] == TILE_FP8;
           mbar_arrive_expect_tx(&v_full[s], (f8 ? v_half_bytes : v_half_bytes / 2) + 512);
           tma_load_2d(sV + s * ATT_V_BYTES, f8 ? &tm_vt8 : &tm_vt4, &v_full[s], f8 ? jv * ATT_BN : jv * (ATT_BN / 2), v_row);
-          bulk_load(sPSF + (2 + s) * 512, (f8 ? p.v8_sf : p.v4_sf) + ksf0 + (long long)jv * 512, 512, &v_full[s]);
+          bulk_load(sPSF + (2 + s) * 512, (f8 ? p.v8_sf : p.v4_sf) + vsf0 + (long long)jv * 512, 512, &v_full[s]);
         }
         ++tv; ++jv;
         return true;
@@ -480,12 +494,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
           tc_cp_32x128b_warpx4(tmem + ATT_COL_SFQ4, sdesc_sf_tile(smem_u32(sSF + 512)));
         }
       }
-      int jq = 0;                                  // scan position in the map row
+      int jq = j_lo;                               // scan position in the map row
       int tq = 0, tp = 0;                          // tiles issued: Q.K^T and P.V
       int jn = -1;                                 // key-tile index of the next Q.K^T to issue (-1: none)
       auto find_next = [&]() {
-        while (jq < nk && map_row[jq] == TILE_SKIP) ++jq;
-        jn = (jq < nk) ? jq++ : -1;
+        while (jq < j_hi && map_row[jq] == TILE_SKIP) ++jq;
+        jn = (jq < j_hi) ? jq++ : -1;
       };
       auto wait_k = [&]() {                        // K tile of Q.K^T number tq has landed
         ok = mbar_wait(&k_full[tq % ATT_KSTAGES], (tq / ATT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
@@ -615,7 +629,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     float l_run = 0.0f;                             // partial row sum over this thread's tiles / columns
     bool ok = true;
     int t = 0;                                      // index among the non-skipped tiles
-    for (int j = 0; j < nk && ok; ++j) {
+    for (int j = j_lo; j < j_hi && ok; ++j) {
       if (map_row[j] == TILE_SKIP) continue;
       if (t % NWG != wg) { ++t; continue; }
       const int bsel = t & 1, lt = t / NWG;         // S buffer; count of tiles this warpgroup has done
@@ -1076,7 +1090,7 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
     return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: merging needs fp32 out, lse, 16-byte aligned acc_in, and outputs distinct from the inputs");
   if (fp4_kind == 1 && !(fp4_scale > 0.0f)) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: NVFP4 needs a positive fp4_scale");
   if (causal && Skv < S) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: causal needs Skv >= S");
-  if (Skv_pad < Skv || Skv_pad % 128) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: Skv_pad must be Skv rounded up to 128");
+  if (Skv_pad < Skv || Skv_pad % 128) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: Skv_pad must be a multiple of 128, at least Skv");
   const void* ptrs[] = {q8, q8_sf, q4, q4_sf, k8, k8_sf, k4, k4_sf, vt, vt8, v8_sf, vt4, v4_sf, out};
   for (const void* ptr : ptrs)
     if ((uintptr_t)ptr % 16) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: every tensor base must be 16-byte aligned");
@@ -1105,7 +1119,7 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S = S; p.Skv = Skv; p.D = D; p.causal = causal; p.fp8_fmt = fp8_fmt;
   p.q8_sf = (const uint8_t*)q8_sf; p.q4_sf = (const uint8_t*)q4_sf;
   p.k8_sf = (const uint8_t*)k8_sf; p.k4_sf = (const uint8_t*)k4_sf;
-  p.v8_sf = (const uint8_t*)v8_sf; p.v4_sf = (const uint8_t*)v4_sf; p.pv_mode = pv_mode;
+  p.v8_sf = (const uint8_t*)v8_sf; p.v4_sf = (const uint8_t*)v4_sf; p.pv_mode = pv_mode; p.v_tiles = Skv_pad / 128;
   p.fp4_scale = fp4_scale;
   p.map = (const uint8_t*)map; p.map_sb = map_sb; p.map_sh = map_sh;
   p.out = out; p.out_dtype = out_dtype; p.lse = (float*)lse; p.status = status;

@@ -544,7 +544,7 @@ extern "C" int mpsa_quant_v_seq(const void* v, int in_dtype, int B, int H, int S
                                 void* v4_sf, void* stream) {
   if (!v || B <= 0 || H <= 0 || Skv <= 0) return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: null input or non-positive shape");
   if (D != 64 && D != 128) return set_error(MPSA_ERR_UNSUPPORTED, "quant_v_seq: head_dim must be 64 or 128");
-  if (Skv_pad < Skv || Skv_pad % 128) return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: Skv_pad must be Skv rounded up to 128");
+  if (Skv_pad < Skv || Skv_pad % 128) return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: Skv_pad must be a multiple of 128, at least Skv");
   if (in_dtype < 0 || in_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: bad in_dtype");
   if (fp8_fmt != FMT_FP8_E5M2 && fp8_fmt != FMT_FP8_E4M3) return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: fp8_fmt must be 1 (E5M2) or 2 (E4M3)");
   if ((vt8 && !v8_sf) || (vt4 && !v4_sf) || (!vt8 && !vt4)) return set_error(MPSA_ERR_BAD_ARG, "quant_v_seq: codes and scales go together");

@@ -5,6 +5,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional
 
+import os
+
 import torch
 
 from . import _lib
@@ -208,13 +210,23 @@ def quantize_qk(x: torch.Tensor, scale: float = 1.0, *, fp8_elem="e5m2", fp4_kin
     return out
 
 
-def prepare_vt(v: torch.Tensor) -> torch.Tensor:
-    """V [B,H,Skv,D] -> fp16 V^T [B,H,D,Skv_pad] (Skv_pad = Skv rounded up to 128, zero filled)."""
+V_PITCH_EXTRA = int(os.environ.get("MPSA_V_PITCH_EXTRA", "128"))
+
+
+def v_pitch(Skv: int) -> int:
+    """Keys per row of a V^T buffer: Skv rounded up to 128, plus one more tile when that is a multiple of 2048.
+    The rows of a V^T tile are one pitch apart; pitches that are large powers of two measured slower."""
+    pad = -(-Skv // 128) * 128
+    return pad + V_PITCH_EXTRA if pad % 2048 == 0 else pad
+
+
+def prepare_vt(v: torch.Tensor, pad: Optional[int] = None) -> torch.Tensor:
+    """V [B,H,Skv,D] -> fp16 V^T [B,H,D,Skv_pad] (Skv_pad = v_pitch(Skv) unless given, zero filled)."""
     _require_cuda(v)
     if v.stride(-1) != 1:
         v = v.contiguous()
     B, H, Skv, D = v.shape
-    pad = -(-Skv // 128) * 128
+    pad = v_pitch(Skv) if pad is None else pad
     vt = torch.empty((B, H, D, pad), dtype=torch.float16, device=v.device)
     with torch.cuda.device(v.device):
         rc = _lib.load().mpsa_prepare_vt(v.data_ptr(), _IN_DTYPE[v.dtype], vt.data_ptr(), B, H, Skv, D, pad,
@@ -233,13 +245,13 @@ class QuantizedV:
     fp8_elem: str = "e5m2"
 
 
-def quantize_v_seq(v: torch.Tensor, fp8_elem: str = "e5m2") -> QuantizedV:
+def quantize_v_seq(v: torch.Tensor, fp8_elem: str = "e5m2", pad: Optional[int] = None) -> QuantizedV:
     """V [B,H,Skv,D] -> MXFP8 and MXFP4 V^T with 32-key blocks along the sequence (one launch)."""
     _require_cuda(v)
     if v.stride(-1) != 1:
         v = v.contiguous()
     B, H, Skv, D = v.shape
-    pad = -(-Skv // 128) * 128
+    pad = v_pitch(Skv) if pad is None else pad
     u8 = dict(dtype=torch.uint8, device=v.device)
     out = QuantizedV(torch.empty((B, H, D, pad), **u8), torch.empty((B, H, pad // 128, 512), **u8),
                      torch.empty((B, H, D, pad // 2), **u8), torch.empty((B, H, pad // 128, 512), **u8), fp8_elem)
@@ -418,17 +430,19 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
     for t, n in ((q8s, B * Hq * nq), (q4s, B * Hq * nq * m4), (k8s, B * Hkv * nk), (k4s, B * Hkv * nk * m4)):
         if t.numel() != n * 512 or not t.is_contiguous():
             raise ValueError("scale tiles have the wrong size")
-    skv_pad = nk * 128
+    skv_pad = (vt.vt8 if requant else vt).shape[-1]      # keys per V^T row: any multiple of 128 that holds Skv
+    if skv_pad % 128 or skv_pad < nk * 128:
+        raise ValueError("V^T rows must hold a multiple of 128 keys, at least Skv")
     if requant:
         if tuple(vt.vt8.shape) != (B, Hkv, D, skv_pad) or tuple(vt.vt4.shape) != (B, Hkv, D, skv_pad // 2) or \
-                vt.v8_sf.numel() != B * Hkv * nk * 512 or vt.v4_sf.numel() != B * Hkv * nk * 512:
+                vt.v8_sf.numel() != B * Hkv * (skv_pad // 128) * 512 or vt.v4_sf.numel() != B * Hkv * (skv_pad // 128) * 512:
             raise ValueError("quantised V has the wrong shape")
         if vt.fp8_elem != qq.fp8_elem:
             raise ValueError("Q/K and V use different fp8 element formats")
         vptrs = (None, vt.vt8.data_ptr(), vt.v8_sf.data_ptr(), vt.vt4.data_ptr(), vt.v4_sf.data_ptr(), 1)
     else:
         if tuple(vt.shape) != (B, Hkv, D, skv_pad) or vt.dtype != torch.float16 or not vt.is_contiguous():
-            raise ValueError("vt must be contiguous fp16 [B, Hkv, D, Skv rounded up to 128]")
+            raise ValueError("vt must be contiguous fp16 [B, Hkv, D, keys per row]")
         vptrs = (vt.data_ptr(), None, None, None, None, 0)
     if (qq.fp8 is None or kq.fp8 is None) and uniform != "fp4":
         raise ValueError("MXFP8 operands missing but the precision map may select FP8 tiles")

@@ -17,7 +17,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, layout, S, ret):
+def _worker(rank, world, port, layout, exchange, S, ret):
     for p in (ROOT, os.path.join(ROOT, "mp-sparse-attn_b200")):
         if p not in sys.path:
             sys.path.insert(0, p)
@@ -37,7 +37,7 @@ def _worker(rank, world, port, layout, S, ret):
         sched = RingSchedule(world, rank, layout, True)
         rows = S // sched.n_blocks
         take = lambda t: torch.cat([t[:, :, b * rows:(b + 1) * rows] for b in sched.my_blocks], dim=2).contiguous()
-        out = ring_attention(take(q), take(k), take(v), causal=True, layout=layout, out_dtype=torch.float32)
+        out = ring_attention(take(q), take(k), take(v), causal=True, layout=layout, out_dtype=torch.float32, exchange=exchange)
         mpsa.check_status()
         ref = take(full)
         ret[rank] = float((out - ref).norm() / ref.norm())
@@ -45,12 +45,13 @@ def _worker(rank, world, port, layout, S, ret):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["ring", "gather"])
 @pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
-def test_ring_equals_single_gpu(layout):
+def test_ring_equals_single_gpu(layout, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     world = 2
     ret = mp.get_context("spawn").Manager().dict()
-    mp.spawn(_worker, args=(world, _free_port(), layout, 2048, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), layout, exchange, 2048, ret), nprocs=world, join=True)
     assert len(ret) == world and max(ret.values()) < 1e-4, dict(ret)

@@ -70,6 +70,20 @@ class RefBackend:
         l = p.sum(-1, keepdim=True)
         return (p @ v) / l, (m + torch.log2(l)).squeeze(-1)
 
+    def assemble(self, gathered, order):
+        return torch.stack([gathered[i] for i in order])
+
+    def partial_prefix(self, qq, gkv, n_key_blocks):
+        B, H = qq.shape[:2]
+        half = gkv.shape[1] // 2
+        k = torch.cat([gkv[g, :half].view(B, H, self.rows, self.D) for g in range(n_key_blocks)], dim=2)
+        v = torch.cat([gkv[g, half:].view(B, H, self.rows, self.D) for g in range(n_key_blocks)], dim=2)
+        s = qq @ k.transpose(-1, -2)
+        m = s.amax(-1, keepdim=True)
+        p = torch.exp2(s - m)
+        l = p.sum(-1, keepdim=True)
+        return (p @ v) / l, (m + torch.log2(l)).squeeze(-1)
+
     def new_accumulator(self):
         return None, None
 
@@ -100,7 +114,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, layout, causal, q, k, v, ref, ret):
+def _worker(rank, world, port, layout, causal, exchange, q, k, v, ref, ret):
     sys.path.insert(0, os.path.join(os.path.dirname(HERE), "mp-sparse-attn_b200"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -110,16 +124,18 @@ def _worker(rank, world, port, layout, causal, q, k, v, ref, ret):
         rows = S // sched.n_blocks
         take = lambda t: torch.cat([t[:, :, b * rows:(b + 1) * rows] for b in sched.my_blocks], dim=2)
         out = ring_attention(take(q), take(k), take(v), causal=causal, layout=layout,
-                             backend=MergingRefBackend(rows, q.shape[-1], q.shape[0], q.shape[1]), out_dtype=torch.float32)
+                             backend=MergingRefBackend(rows, q.shape[-1], q.shape[0], q.shape[1]), out_dtype=torch.float32,
+                             exchange=exchange)
         err = float((out - take(ref)).abs().max())
         ret[rank] = err
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["ring", "gather"])
 @pytest.mark.parametrize("world,layout,causal", [(2, "contiguous", True), (2, "zigzag", True), (4, "zigzag", True),
                                                  (3, "contiguous", False)])
-def test_ring_matches_single_process_attention(world, layout, causal):
+def test_ring_matches_single_process_attention(world, layout, causal, exchange):
     g = torch.Generator().manual_seed(3)
     B, H, D = 1, 2, 16
     S = 24 * world
@@ -129,5 +145,5 @@ def test_ring_matches_single_process_attention(world, layout, causal):
         s = s.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool), 1), float("-inf"))
     ref = torch.softmax(s, -1) @ v
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(world, _free_port(), layout, causal, q, k, v, ref, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), layout, causal, exchange, q, k, v, ref, ret), nprocs=world, join=True)
     assert len(ret) == world and max(ret.values()) < 1e-5, dict(ret)
