@@ -278,7 +278,8 @@ def run_ours(args):
 
 def run_ring(args):
     """Long-context causal attention, B=1 Hq=32 Hkv=8 D=128 S=131072, sequence-sharded over the GPUs: every
-    rank quantises its slice once and the MXFP4 K/V blocks travel round an NCCL ring (strong scaling)."""
+    rank quantises its slice once and the MXFP4 K/V blocks are exchanged over NCCL, by one all-gather (default) or
+    by send/recv round a ring (strong scaling)."""
     import torch.distributed as dist
     import mpsa
     from mpsa.ring import RingSchedule, ring_attention
@@ -458,7 +459,7 @@ def main():
                          "sequence-sharded over the GPUs (strong scaling); gemm: the standalone block-scaled GEMM (1 GPU)")
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of --workload gemm")
     ap.add_argument("--layout", default="zigzag", choices=["contiguous", "zigzag"])
-    ap.add_argument("--exchange", default="ring", choices=["ring", "gather"],
+    ap.add_argument("--exchange", default="gather", choices=["ring", "gather"],
                     help="ring workload: K/V blocks by send/recv round the ring, or one all-gather")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -5,8 +5,6 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional
 
-import os
-
 import torch
 
 from . import _lib
@@ -210,14 +208,10 @@ def quantize_qk(x: torch.Tensor, scale: float = 1.0, *, fp8_elem="e5m2", fp4_kin
     return out
 
 
-V_PITCH_EXTRA = int(os.environ.get("MPSA_V_PITCH_EXTRA", "128"))
-
-
 def v_pitch(Skv: int) -> int:
-    """Keys per row of a V^T buffer: Skv rounded up to 128, plus one more tile when that is a multiple of 2048.
-    The rows of a V^T tile are one pitch apart; pitches that are large powers of two measured slower."""
-    pad = -(-Skv // 128) * 128
-    return pad + V_PITCH_EXTRA if pad % 2048 == 0 else pad
+    """Default number of keys per row of a V^T buffer: Skv rounded up to 128.  The kernels take the pitch as an
+    argument (any multiple of 128 that holds Skv), so a caller may lay several blocks side by side in one buffer."""
+    return -(-Skv // 128) * 128
 
 
 def prepare_vt(v: torch.Tensor, pad: Optional[int] = None) -> torch.Tensor:
