@@ -33,7 +33,8 @@ import torch  # noqa: E402
 
 HQ, HKV, D = 32, 8, 128
 OUTLIERS = 5
-LAUNCHES_PER_STEP = 7      # quant Q, quant K, quant V, router statistic (+ its finish kernel), precision map, fused forward
+LAUNCHES_PER_STEP = 8      # quant Q, quant K, quant V, router statistic + its finish kernel, precision map, fused forward
+                           # + the exact kernel behind it as conditional fallback (its CTAs return at once)
 TAU = 1.1                  # online router: a tile is promoted to MXFP8 iff its statistic >= TAU x the first key tile's
 # DRAM bytes (read + written) of one launch of the fused forward at S=8192 from an ncu capture
 # (profiles/attn_fwd_requant_cfg3_S8192.md); every term of it grows linearly with S

@@ -48,6 +48,21 @@ int mpsa_quant_mx(const void* x, int in_dtype, int B, int H, int L, int D, long 
                   void* fp8_scales_rm, void* fp4_scales_rm, void* fp4_codes_packed, void* fp8_scales_tiled,
                   void* fp4_scales_tiled, void* stream);
 
+/* "Smooth K": the reference subtracts the mean over the sequence from K before quantising it
+ * (ours/mxfp_attn_kernel.py:33-34: km = k.mean(dim=-2, keepdim=True); k = k - km).  mpsa_col_mean leaves that mean,
+ * fp32 [B,H,D] holding values rounded to the input dtype (fp32 sums in a fixed order, divided by L), and
+ * mpsa_quant_mx_centered is mpsa_quant_mx with `center` subtracted from every row first, the difference rounded to
+ * the input dtype as the elementwise torch op does, so K is read once instead of three times.
+ *   scratch  fp32, at least mpsa_col_mean_scratch_floats(B,H,L,D) elements; center 16-byte aligned. */
+long long mpsa_col_mean_scratch_floats(int B, int H, int L, int D);
+int mpsa_col_mean(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b, long long xs_h,
+                  long long xs_l, void* mean, void* scratch, long long scratch_floats, void* stream);
+int mpsa_quant_mx_centered(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b, long long xs_h,
+                           long long xs_l, float s, const void* center, int fp8_fmt, void* fp8_codes, long long o8_b,
+                           long long o8_h, long long o8_l, void* fp4_codes_unpacked, long long o4_b, long long o4_h,
+                           long long o4_l, void* fp8_scales_rm, void* fp4_scales_rm, void* fp4_codes_packed,
+                           void* fp8_scales_tiled, void* fp4_scales_tiled, void* stream);
+
 /* Per-32 int8 quantizer, one side per call.  Replaces quant_fpxint8 (ours/quant_mxint8.py:21-114).
  *   codes int8 with byte strides o_*; scales fp32 [B,H,L,D/32]. */
 int mpsa_quant_int8(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b, long long xs_h,

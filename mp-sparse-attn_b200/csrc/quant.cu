@@ -27,6 +27,7 @@ struct QuantParams {
   int B, H, L, D;
   long long xs_b, xs_h, xs_l;  // input strides in elements (inner stride 1)
   float s;                     // fp32 scalar multiplied into x before quantisation
+  const float* center;         // optional [B,H,D]: subtracted from every row first (result rounded to the input dtype)
   int fp8_fmt;                 // FMT_FP8_E5M2 or FMT_FP8_E4M3
   // reference-format outputs (strided like the input tensor's logical shape)
   uint8_t* fp8_codes;  long long o8_b, o8_h, o8_l;
@@ -74,6 +75,12 @@ __device__ __forceinline__ void load16<float>(const float* p, float (&v)[16]) {
     v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = a.z; v[4 * i + 3] = a.w;
   }
 }
+
+// x rounded to the storage type T (what an elementwise torch op on a T tensor returns)
+template <typename T> __device__ __forceinline__ float round_as(float x);
+template <> __device__ __forceinline__ float round_as<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+template <> __device__ __forceinline__ float round_as<__half>(float x) { return __half2float(__float2half_rn(x)); }
+template <> __device__ __forceinline__ float round_as<float>(float x) { return x; }
 
 constexpr int kQuantThreads = 256;
 constexpr int kRunsPerThread = 4;   // 256 threads * 4 runs * 16 elements = 128 x 128 tile (int8 / NVFP4 kernels)
@@ -138,6 +145,18 @@ __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantPara
     live[i] = (r < p.L) && (c < p.D);
     if (live[i]) {
       load16<T>(xb + (long long)r * p.xs_l + c, v[i]);
+      if (p.center) {
+        // "smooth K": k - mean over the sequence (ours/mxfp_attn_kernel.py:33-34), an elementwise op in the input dtype
+        const float4* cen = reinterpret_cast<const float4*>(p.center + ((long long)b * p.H + h) * p.D + c);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 m = __ldg(cen + j);
+          v[i][4 * j] = round_as<T>(v[i][4 * j] - m.x);
+          v[i][4 * j + 1] = round_as<T>(v[i][4 * j + 1] - m.y);
+          v[i][4 * j + 2] = round_as<T>(v[i][4 * j + 2] - m.z);
+          v[i][4 * j + 3] = round_as<T>(v[i][4 * j + 3] - m.w);
+        }
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < 16; ++j) v[i][j] = 0.0f;
@@ -477,14 +496,64 @@ __global__ void __launch_bounds__(kQuantThreads) nvfp4_quant_kernel(const QuantN
 
 }  // namespace mpsa
 
+namespace mpsa {
+// ---- mean over the sequence per (batch, head, depth index): the vector "smooth K" subtracts ------------------
+// Two launches, fixed summation order: partial column sums of kMeanRows rows per CTA, then their sum / L rounded to
+// the input dtype (torch's mean of a 16-bit tensor accumulates in fp32 and returns the input dtype).
+constexpr int kMeanRows = 512;
+template <typename T>
+__global__ void __launch_bounds__(128) col_sum_kernel(const T* x, float* part, int H, int L, int D, long long xs_b,
+                                                      long long xs_h, long long xs_l, int nchunk) {
+  __shared__ float acc_s[16][128];
+  const int chunk = blockIdx.x, col0 = blockIdx.y * 128, bh = blockIdx.z;
+  const int b = bh / H, h = bh % H;
+  const int c16 = threadIdx.x & 7, rg = threadIdx.x >> 3;      // 8 threads x 16 columns per row, 16 rows per pass
+  const int c = col0 + c16 * 16;
+  const T* xb = x + (long long)b * xs_b + (long long)h * xs_h;
+  float acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+  const int r_end = min(L, (chunk + 1) * kMeanRows);
+  if (c < D) {
+    for (int r = chunk * kMeanRows + rg; r < r_end; r += 16) {
+      float v[16];
+      load16<T>(xb + (long long)r * xs_l + c, v);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc_s[rg][c16 * 16 + j] = acc[j];
+  __syncthreads();
+  const int col = col0 + threadIdx.x;
+  if (col < D) {
+    float t = 0.0f;
+#pragma unroll
+    for (int g = 0; g < 16; ++g) t += acc_s[g][threadIdx.x];
+    part[((long long)bh * nchunk + chunk) * D + col] = t;
+  }
+}
+
+template <typename T>
+__global__ void col_mean_finish_kernel(const float* part, float* mean, int L, int D, int nchunk) {
+  const int bh = blockIdx.x;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float t = 0.0f;
+    for (int ch = 0; ch < nchunk; ++ch) t += part[((long long)bh * nchunk + ch) * D + d];
+    mean[(long long)bh * D + d] = round_as<T>(__fdiv_rn(t, (float)L));
+  }
+}
+}  // namespace mpsa
+
 using namespace mpsa;
 
-extern "C" int mpsa_quant_mx(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b,
-                             long long xs_h, long long xs_l, float s, int fp8_fmt, void* fp8_codes,
-                             long long o8_b, long long o8_h, long long o8_l, void* fp4_codes_unpacked,
-                             long long o4_b, long long o4_h, long long o4_l, void* fp8_scales_rm,
-                             void* fp4_scales_rm, void* fp4_codes_packed, void* fp8_scales_tiled,
-                             void* fp4_scales_tiled, void* stream) {
+static int quant_mx_launch(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b,
+                           long long xs_h, long long xs_l, float s, const void* center, int fp8_fmt, void* fp8_codes,
+                           long long o8_b, long long o8_h, long long o8_l, void* fp4_codes_unpacked,
+                           long long o4_b, long long o4_h, long long o4_l, void* fp8_scales_rm,
+                           void* fp4_scales_rm, void* fp4_codes_packed, void* fp8_scales_tiled,
+                           void* fp4_scales_tiled, void* stream) {
+  if (center && ((uintptr_t)center % 16)) return set_error(MPSA_ERR_BAD_ARG, "quant_mx: center must be 16-byte aligned");
   if (!x || B <= 0 || H <= 0 || L <= 0 || D <= 0) return set_error(MPSA_ERR_BAD_ARG, "quant_mx: null input or non-positive shape");
   if (D % 32 != 0) return set_error(MPSA_ERR_UNSUPPORTED, "quant_mx: head_dim must be a multiple of 32");
   if (in_dtype < 0 || in_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "quant_mx: in_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
@@ -500,7 +569,7 @@ extern "C" int mpsa_quant_mx(const void* x, int in_dtype, int B, int H, int L, i
     return set_error(MPSA_ERR_BAD_ARG, "quant_mx: output pointers and strides must be 16-byte aligned");
   QuantParams p;
   p.x = x; p.in_dtype = in_dtype; p.B = B; p.H = H; p.L = L; p.D = D;
-  p.xs_b = xs_b; p.xs_h = xs_h; p.xs_l = xs_l; p.s = s; p.fp8_fmt = fp8_fmt;
+  p.xs_b = xs_b; p.xs_h = xs_h; p.xs_l = xs_l; p.s = s; p.fp8_fmt = fp8_fmt; p.center = (const float*)center;
   p.fp8_codes = (uint8_t*)fp8_codes; p.o8_b = o8_b; p.o8_h = o8_h; p.o8_l = o8_l;
   p.fp4_codes_unpacked = (uint8_t*)fp4_codes_unpacked; p.o4_b = o4_b; p.o4_h = o4_h; p.o4_l = o4_l;
   p.fp8_scales_rm = (uint8_t*)fp8_scales_rm; p.fp4_scales_rm = (uint8_t*)fp4_scales_rm;
@@ -513,6 +582,61 @@ extern "C" int mpsa_quant_mx(const void* x, int in_dtype, int B, int H, int L, i
   else if (in_dtype == 1) quant_mx_kernel<__half><<<grid, kMxThreads, 0, st>>>(p);
   else quant_mx_kernel<float><<<grid, kMxThreads, 0, st>>>(p);
   return check_launch("quant_mx");
+}
+
+extern "C" int mpsa_quant_mx(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b,
+                             long long xs_h, long long xs_l, float s, int fp8_fmt, void* fp8_codes,
+                             long long o8_b, long long o8_h, long long o8_l, void* fp4_codes_unpacked,
+                             long long o4_b, long long o4_h, long long o4_l, void* fp8_scales_rm,
+                             void* fp4_scales_rm, void* fp4_codes_packed, void* fp8_scales_tiled,
+                             void* fp4_scales_tiled, void* stream) {
+  return quant_mx_launch(x, in_dtype, B, H, L, D, xs_b, xs_h, xs_l, s, nullptr, fp8_fmt, fp8_codes, o8_b, o8_h, o8_l,
+                         fp4_codes_unpacked, o4_b, o4_h, o4_l, fp8_scales_rm, fp4_scales_rm, fp4_codes_packed,
+                         fp8_scales_tiled, fp4_scales_tiled, stream);
+}
+
+extern "C" int mpsa_quant_mx_centered(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b,
+                                      long long xs_h, long long xs_l, float s, const void* center, int fp8_fmt,
+                                      void* fp8_codes, long long o8_b, long long o8_h, long long o8_l,
+                                      void* fp4_codes_unpacked, long long o4_b, long long o4_h, long long o4_l,
+                                      void* fp8_scales_rm, void* fp4_scales_rm, void* fp4_codes_packed,
+                                      void* fp8_scales_tiled, void* fp4_scales_tiled, void* stream) {
+  if (!center) return set_error(MPSA_ERR_BAD_ARG, "quant_mx_centered: center is null");
+  return quant_mx_launch(x, in_dtype, B, H, L, D, xs_b, xs_h, xs_l, s, center, fp8_fmt, fp8_codes, o8_b, o8_h, o8_l,
+                         fp4_codes_unpacked, o4_b, o4_h, o4_l, fp8_scales_rm, fp4_scales_rm, fp4_codes_packed,
+                         fp8_scales_tiled, fp4_scales_tiled, stream);
+}
+
+extern "C" long long mpsa_col_mean_scratch_floats(int B, int H, int L, int D) {
+  return (long long)B * H * ((L + kMeanRows - 1) / kMeanRows) * D;
+}
+
+extern "C" int mpsa_col_mean(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b, long long xs_h,
+                             long long xs_l, void* mean, void* scratch, long long scratch_floats, void* stream) {
+  if (!x || !mean || !scratch || B <= 0 || H <= 0 || L <= 0 || D <= 0) return set_error(MPSA_ERR_BAD_ARG, "col_mean: null pointer or non-positive shape");
+  if (D % 16 != 0) return set_error(MPSA_ERR_UNSUPPORTED, "col_mean: depth must be a multiple of 16");
+  if (in_dtype < 0 || in_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "col_mean: in_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
+  const int esz = in_dtype == 2 ? 4 : 2;
+  if (((uintptr_t)x % 16) || ((xs_b * esz) % 16) || ((xs_h * esz) % 16) || ((xs_l * esz) % 16))
+    return set_error(MPSA_ERR_BAD_ARG, "col_mean: input base and strides must be 16-byte aligned");
+  if (scratch_floats < mpsa_col_mean_scratch_floats(B, H, L, D)) return set_error(MPSA_ERR_BAD_ARG, "col_mean: scratch too small");
+  const int nchunk = (L + kMeanRows - 1) / kMeanRows;
+  dim3 grid(nchunk, (D + 127) / 128, B * H);
+  if (grid.y > 65535 || grid.z > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "col_mean: B*H and D/128 must be below 65536");
+  cudaStream_t st = (cudaStream_t)stream;
+  float* part = (float*)scratch;
+  float* m = (float*)mean;
+  if (in_dtype == 0) {
+    col_sum_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, part, H, L, D, xs_b, xs_h, xs_l, nchunk);
+    col_mean_finish_kernel<__nv_bfloat16><<<B * H, 128, 0, st>>>(part, m, L, D, nchunk);
+  } else if (in_dtype == 1) {
+    col_sum_kernel<__half><<<grid, 128, 0, st>>>((const __half*)x, part, H, L, D, xs_b, xs_h, xs_l, nchunk);
+    col_mean_finish_kernel<__half><<<B * H, 128, 0, st>>>(part, m, L, D, nchunk);
+  } else {
+    col_sum_kernel<float><<<grid, 128, 0, st>>>((const float*)x, part, H, L, D, xs_b, xs_h, xs_l, nchunk);
+    col_mean_finish_kernel<float><<<B * H, 128, 0, st>>>(part, m, L, D, nchunk);
+  }
+  return check_launch("col_mean");
 }
 
 extern "C" int mpsa_quant_int8(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b,

@@ -92,12 +92,31 @@ def _bhld(x: torch.Tensor, tensor_layout: str):
     return x, (B, H, L, D), (sb, sh, sl)
 
 
+def column_mean(x: torch.Tensor, tensor_layout: str = "HND") -> torch.Tensor:
+    """Mean over the sequence, fp32 [B,H,D] holding values rounded to x's dtype: the vector "smooth K" subtracts
+    (ours/mxfp_attn_kernel.py:33-34)."""
+    _require_cuda(x)
+    if x.dtype not in _IN_DTYPE:
+        raise ValueError(f"unsupported input dtype {x.dtype}")
+    x, (B, H, L, D), (sb, sh, sl) = _bhld(x, tensor_layout)
+    lib = _lib.load()
+    n = lib.mpsa_col_mean_scratch_floats(B, H, L, D)
+    mean = torch.empty((B, H, D), dtype=torch.float32, device=x.device)
+    scratch = torch.empty(n, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.mpsa_col_mean(x.data_ptr(), _IN_DTYPE[x.dtype], B, H, L, D, sb, sh, sl, mean.data_ptr(), scratch.data_ptr(),
+                               n, _stream())
+    _lib.check(rc)
+    return mean
+
+
 def quantize_mx(x: torch.Tensor, scale: float = 1.0, *, want_fp8=True, want_fp4=True, reference_format=False,
-                kernel_format=True, fp8_elem="e5m2", tensor_layout="HND") -> QuantizedOperand:
+                kernel_format=True, fp8_elem="e5m2", tensor_layout="HND", center=None) -> QuantizedOperand:
     """Quantise one operand along its last axis in 32-element MX blocks (one kernel launch).
 
     reference_format: emit what ours/quant_mxint8.py returns (fp4 one code per byte, row-major
-    scales, shaped like the input).  kernel_format: emit packed fp4 and 128x4 scale tiles."""
+    scales, shaped like the input).  kernel_format: emit packed fp4 and 128x4 scale tiles.
+    center: optional fp32 [B,H,D] from column_mean, subtracted from every row before quantising."""
     _require_cuda(x)
     if x.dtype not in _IN_DTYPE:
         raise ValueError(f"unsupported input dtype {x.dtype}")
@@ -128,11 +147,18 @@ def quantize_mx(x: torch.Tensor, scale: float = 1.0, *, want_fp8=True, want_fp4=
         if kernel_format:
             out.fp4 = torch.empty((B, H, L, D // 2), **u8)
             out.fp4_sf = torch.empty((B, H, nl, nd, 512), **u8)
-    with torch.cuda.device(dev):
-        rc = _lib.load().mpsa_quant_mx(
-            x.data_ptr(), _IN_DTYPE[x.dtype], B, H, L, D, sb, sh, sl, float(scale), _FP8_QUANT[fp8_elem],
-            _ptr(out.fp8), *o8, _ptr(out.fp4_unpacked), *o4, _ptr(out.fp8_scales), _ptr(out.fp4_scales),
+    outs = (_ptr(out.fp8), *o8, _ptr(out.fp4_unpacked), *o4, _ptr(out.fp8_scales), _ptr(out.fp4_scales),
             _ptr(out.fp4), _ptr(out.fp8_sf), _ptr(out.fp4_sf), _stream())
+    with torch.cuda.device(dev):
+        if center is None:
+            rc = _lib.load().mpsa_quant_mx(x.data_ptr(), _IN_DTYPE[x.dtype], B, H, L, D, sb, sh, sl, float(scale),
+                                           _FP8_QUANT[fp8_elem], *outs)
+        else:
+            if center.dtype != torch.float32 or tuple(center.shape) != (B, H, D) or not center.is_contiguous() or \
+                    center.device != dev:
+                raise ValueError("center must be a contiguous fp32 [B, H, D] tensor on x's device")
+            rc = _lib.load().mpsa_quant_mx_centered(x.data_ptr(), _IN_DTYPE[x.dtype], B, H, L, D, sb, sh, sl, float(scale),
+                                                    center.data_ptr(), _FP8_QUANT[fp8_elem], *outs)
     _lib.check(rc)
     return out
 
@@ -195,13 +221,20 @@ def quantize_nvfp4_bh(x: torch.Tensor, scale: float = 1.0):
     return codes, scales, ts
 
 
-def quantize_qk(x: torch.Tensor, scale: float = 1.0, *, fp8_elem="e5m2", fp4_kind="mxfp4") -> QuantizedOperand:
+def quantize_qk(x: torch.Tensor, scale: float = 1.0, *, fp8_elem="e5m2", fp4_kind="mxfp4", smooth=False) -> QuantizedOperand:
     """Q or K (depth already padded to 128) in both precisions of the fused forward: MXFP8 and either MXFP4
-    (one pass for both) or NVFP4 (a second quantizer)."""
-    if fp4_kind == "mxfp4":
-        return quantize_mx(x, scale, fp8_elem=fp8_elem)
-    if fp4_kind != "nvfp4":
+    (one pass for both) or NVFP4 (a second quantizer).  smooth: subtract the mean over the sequence first
+    (the reference's smooth_k), inside the MX quantizer."""
+    if fp4_kind not in ("mxfp4", "nvfp4"):
         raise ValueError(f"unknown fp4_kind {fp4_kind!r}")
+    center = None
+    if smooth:
+        center = column_mean(x)
+        if fp4_kind == "nvfp4":                    # the NVFP4 quantizer has no centred form: it gets the difference
+            x = (x.float() - center.unsqueeze(2)).to(x.dtype)
+            center = None
+    if fp4_kind == "mxfp4":
+        return quantize_mx(x, scale, fp8_elem=fp8_elem, center=center)
     out = quantize_mx(x, scale, want_fp4=False, fp8_elem=fp8_elem)
     out.fp4, out.fp4_sf, out.fp4_ts = quantize_nvfp4_bh(x, scale)
     out.fp4_kind = "nvfp4"
@@ -320,9 +353,11 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
                       sm_scale: Optional[float] = None, fp8_elem: str = "e5m2",
                       out_dtype: torch.dtype = torch.bfloat16, pv_mode: str = "fp16", check: bool = False,
                       router: str = "band", tau: float = 1.0, fp4_kind: str = "mxfp4",
-                      skip_thresh: Optional[float] = None, return_sparsity: bool = False):
+                      skip_thresh: Optional[float] = None, return_sparsity: bool = False, smooth_k: bool = False):
     """Quantise Q/K (both MXFP8 and MXFP4 in one pass each), prepare V, build the precision map and
     run the fused forward.  q [B,Hq,S,D], k/v [B,Hkv,Skv,D]; D in {64, 128}.
+    smooth_k: subtract K's mean over the sequence inside the K quantizer (softmax is unchanged by it: every score
+    of a row moves by the same amount).
 
     router "band": the static diagonal-band map.  router "online": one extra MXFP4 pass over the score tiles
     (router_statistic) promotes to MXFP8 every tile whose statistic reaches `tau` times that of the row's
@@ -340,7 +375,7 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
         raise ValueError("headdim should be in [64, 128].")
     sq = q_side_scale(D, sm_scale)
     qq = quantize_qk(_pad_depth_128(q), sq, fp8_elem=fp8_elem, fp4_kind=fp4_kind)
-    kq = quantize_qk(_pad_depth_128(k), 1.0, fp8_elem=fp8_elem, fp4_kind=fp4_kind)
+    kq = quantize_qk(_pad_depth_128(k), 1.0, fp8_elem=fp8_elem, fp4_kind=fp4_kind, smooth=smooth_k)
     if pv_mode == "fp16":
         vt = prepare_vt(v)
     elif pv_mode == "requant":

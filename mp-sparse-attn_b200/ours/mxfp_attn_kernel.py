@@ -34,8 +34,8 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
         raise ValueError(f"Unknown tensor layout: {tensor_layout}")
     if q.dtype == torch.float32:
         q, k = q.to(torch.float16), k.to(torch.float16)      # ours/mxfp_attn_kernel.py:28-29
-    if smooth_k:
-        k = k - k.mean(dim=-2, keepdim=True)                 # :33-34
+    if smooth_k and host:
+        k = k - k.mean(dim=-2, keepdim=True)                 # :33-34; device tensors: inside the K quantizer, below
     assert q.shape[-1] in [64, 128], "headdim should be in [64, 128]."
     if block_scale_type == "mxfp4":
         uniform = "fp4"
@@ -54,7 +54,7 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
     else:
         if out is not None:
             raise ValueError("out= is for host tensors only")
-        o = _ops.attention_forward(q, k, v, return_sparsity=bool(return_sparsity and online), **kw)
+        o = _ops.attention_forward(q, k, v, return_sparsity=bool(return_sparsity and online), smooth_k=bool(smooth_k), **kw)
         if return_sparsity and online:
             o, sparsity = o
             return (o.transpose(1, 2) if tensor_layout == "NHD" else o), sparsity

@@ -9,7 +9,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _declared():
     text = open(os.path.join(ROOT, "include", "mpsa.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\bint\s+(mpsa_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(?:int|long long)\s+(mpsa_\w+)\s*\(", text)))
 
 
 def test_library_exports_every_declared_symbol():

@@ -262,3 +262,18 @@ def test_merge_in_the_epilogue(pv_mode):
     z, lz = torch.zeros_like(a0), torch.full_like(l0, float("-inf"))
     alone, _ = ops.attention_forward_quantized(qq, *halves[1], B, Hq, Hkv, S, S // 2, D, merge_with=(z, lz), **kw)
     assert torch.allclose(alone, a1, rtol=1e-6, atol=1e-7)
+
+
+def test_smooth_k_through_the_reference_entry_point():
+    """mxfp_attn_kernel(..., smooth_k=True) on device tensors centres K inside the quantizer; the result must match the
+    oracle run on K minus the same mean (a shift of K along the sequence moves every score of a row equally)."""
+    import mpsa
+    from ours.mxfp_attn_kernel import mxfp_attn_kernel
+    q, k, v = O.make_qkv(13, 1, 4, 2, 384, 128, outliers=2)
+    k = (k.float() + 1.5).to(torch.bfloat16)                    # a mean worth removing
+    o = mxfp_attn_kernel(q.cuda(), k.cuda(), v.cuda(), is_causal=True, smooth_k=True, block_scale_type="diag",
+                         output_dtype=torch.float32)
+    mpsa.check_status()
+    mean = mpsa.column_mean(k.cuda()).cpu()
+    kc = (k.float() - mean.unsqueeze(2)).to(torch.bfloat16)
+    _check(o.cpu(), O.attention_mxfp(q, kc, v, causal=True), "smooth_k")

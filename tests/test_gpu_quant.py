@@ -132,3 +132,29 @@ def test_nvfp4_quantizer_matches_oracle(rows, cols, dtype):
         ref = O.gemm_block_scaled(oc, osc, yc, ysc, "nvfp4", "nvfp4", 16, ots, yts)
         m = O.parity_metrics(out.cpu(), ref)
         assert m["cos"] >= 0.9999 and m["rel_l2"] <= 1e-2, m
+
+
+@pytest.mark.parametrize("shape,dtype", [((1, 2, 1300, 128), torch.bfloat16), ((2, 1, 700, 64), torch.float16),
+                                         ((1, 1, 513, 128), torch.float32)])
+def test_smooth_k_inside_the_quantizer(shape, dtype):
+    """The reference's smooth_k is k - k.mean(dim=-2, keepdim=True) ahead of the quantizer
+    (ours/mxfp_attn_kernel.py:33-34).  (1) column_mean is the fp32 mean rounded to the input dtype: within one unit in
+    the last place of the float64 mean.  (2) Given that mean, the centred quantizer is bit-exact against the oracle
+    quantizing the difference that torch's elementwise subtraction leaves (rounded to the input dtype)."""
+    import mpsa
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(shape, generator=g) + 0.7 * torch.randn(shape[0], shape[1], 1, shape[3], generator=g)).to(dtype)
+    mean = mpsa.column_mean(x.cuda()).cpu()
+    assert mean.dtype == torch.float32 and tuple(mean.shape) == (shape[0], shape[1], shape[3])
+    assert torch.equal(mean.to(dtype).float(), mean)                       # representable in the input dtype
+    ref = x.double().mean(dim=-2)
+    ulp = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -22}[dtype]
+    assert ((mean.double() - ref).abs() <= ulp * ref.abs() + 1e-6).all()
+    xc = (x.float() - mean.unsqueeze(2)).to(dtype)                         # what `k - km` holds, given this km
+    r = mpsa.quantize_mx(x.cuda(), 1.0, reference_format=True, kernel_format=True, center=mean.cuda())
+    c4, s4 = O.quant_mxfp4_side(xc, 1.0)
+    c8, s8 = O.quant_mxfp8_side(xc, 1.0)
+    assert torch.equal(r.fp4_unpacked.cpu(), c4) and torch.equal(r.fp4_scales.cpu(), s4)
+    assert torch.equal(r.fp8.cpu(), c8) and torch.equal(r.fp8_scales.cpu(), s8)
+    assert torch.equal(r.fp4.cpu(), O.pack_e2m1(c4))
+    assert torch.equal(r.fp4_sf.cpu().reshape(O.swizzle_scales(s4).shape), O.swizzle_scales(s4))
