@@ -536,13 +536,16 @@ class _HostPipeline:
 
     def __init__(self, dev, grp, S, Skv, D, dtype, slots=2):
         self.h2d, self.d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        # chunks alternate between two compute streams: the short kernels that open a chunk (quantizers, router) run
+        # in the tail of the previous chunk's forward instead of behind it
+        self.compute = [torch.cuda.Stream(dev), torch.cuda.Stream(dev)]
         self.q = [torch.empty((1, grp, S, D), dtype=dtype, device=dev) for _ in range(slots)]
         self.kv = [(torch.empty((1, 1, Skv, D), dtype=dtype, device=dev), torch.empty((1, 1, Skv, D), dtype=dtype, device=dev))
                    for _ in range(slots)]
         self.q_loaded = [torch.cuda.Event() for _ in range(slots)]     # the slot's queries have arrived
         self.q_consumed = [torch.cuda.Event() for _ in range(slots)]   # the forward that read them is done
         self.kv_loaded = [torch.cuda.Event() for _ in range(slots)]
-        self.kv_consumed = [torch.cuda.Event() for _ in range(slots)]
+        self.kv_consumed = [[] for _ in range(slots)]                   # one event per piece that read the slot
 
 
 _host_pipes = {}
@@ -572,8 +575,8 @@ def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                            device=None, out_dtype: torch.dtype = torch.bfloat16, **kw) -> torch.Tensor:
     """The fused forward for operands that live in (pinned) HOST memory: q [B,Hq,S,D], k/v [B,Hkv,S,D] CPU tensors,
     result a pinned CPU tensor [B,Hq,S,D].  The work is cut into (batch, KV group) chunks - independent units of
-    the path - and pipelined over three streams: while chunk i is computed, the inputs of chunk i+1 cross PCIe
-    and the output of chunk i-1 goes back, so that a call costs about max(copy, compute) rather than their sum.
+    the path - and pipelined over copy and compute streams: while chunk i is computed, the inputs of chunk i+1 cross
+    PCIe and the output of chunk i-1 goes back, so that a call costs about max(copy, compute) rather than their sum.
     Keyword arguments are those of attention_forward."""
     if q.is_cuda or k.is_cuda or v.is_cuda:
         raise ValueError("attention_forward_host expects CPU tensors; use attention_forward for device tensors")
@@ -599,6 +602,10 @@ def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     start.record(main)
     pipe.h2d.wait_event(start)                    # the caller's earlier work on these buffers comes first
     pipe.d2h.wait_event(start)
+    for cs in pipe.compute:
+        cs.wait_event(start)
+    for used in pipe.kv_consumed:
+        used.clear()
     keep = []
     chunks = _host_chunks(B, Hkv, grp)
     n_kv = -1                                      # KV groups uploaded so far - 1
@@ -612,8 +619,9 @@ def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
         dk, dv = pipe.kv[ks]
         with torch.cuda.stream(pipe.h2d):
             if new_kv:
-                if n_kv >= len(pipe.kv):
-                    pipe.h2d.wait_event(pipe.kv_consumed[ks])
+                for e in pipe.kv_consumed[ks]:     # every piece of the group that held this slot has read K and V
+                    pipe.h2d.wait_event(e)
+                pipe.kv_consumed[ks].clear()
                 dk.copy_(k[b:b + 1, g:g + 1], non_blocking=True)
                 dv.copy_(v[b:b + 1, g:g + 1], non_blocking=True)
                 pipe.kv_loaded[ks].record(pipe.h2d)
@@ -621,14 +629,15 @@ def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                 pipe.h2d.wait_event(pipe.q_consumed[qs])
             dq.copy_(q[b:b + 1, g * grp + h0:g * grp + h0 + nh], non_blocking=True)
             pipe.q_loaded[qs].record(pipe.h2d)
-        main.wait_event(pipe.kv_loaded[ks])
-        main.wait_event(pipe.q_loaded[qs])
-        o = attention_forward(dq, dk, dv, causal=causal, out_dtype=out_dtype, **kw)
-        pipe.q_consumed[qs].record(main)
-        if n + 1 == len(chunks) or chunks[n + 1][2] == 0:
-            pipe.kv_consumed[ks].record(main)      # the group's last piece has read K and V
+        cs = pipe.compute[n % len(pipe.compute)]
+        cs.wait_event(pipe.kv_loaded[ks])
+        cs.wait_event(pipe.q_loaded[qs])
+        with torch.cuda.stream(cs):
+            o = attention_forward(dq, dk, dv, causal=causal, out_dtype=out_dtype, **kw)
+        pipe.q_consumed[qs].record(cs)
         done = torch.cuda.Event()
-        done.record(main)
+        done.record(cs)
+        pipe.kv_consumed[ks].append(done)
         with torch.cuda.stream(pipe.d2h):
             pipe.d2h.wait_event(done)
             out[b:b + 1, g * grp + h0:g * grp + h0 + nh].copy_(o, non_blocking=True)
