@@ -63,6 +63,19 @@ int mpsa_quant_mx_centered(const void* x, int in_dtype, int B, int H, int L, int
                            long long o4_l, void* fp8_scales_rm, void* fp4_scales_rm, void* fp4_codes_packed,
                            void* fp8_scales_tiled, void* fp4_scales_tiled, void* stream);
 
+/* Rotary embedding fused into the MX quantizer (the step in front of the path: Q and K come out of the QKV projection,
+ * are rotated and then quantised by quant_mxfp4 / quant_mxfp8e5, ours/mxfp_attn_kernel.py:41-55; fusing the rotation
+ * removes one read and one write of the 16-bit tensor).  Rotate-half convention, as evaluate/llama applies it through
+ * transformers: with x1 / x2 the two halves of a row, y1 = x1 cos - x2 sin, y2 = x2 cos + x1 sin; fp32 products and sum,
+ * the result rounded to the input dtype (the tensor an unfused pipeline stores), then mpsa_quant_mx's arithmetic.
+ *   cos, sin  fp32 [.., L, D/2], 16-byte aligned, shared by the heads; rope_sb = batch stride in floats (0: shared)
+ *   D         64 or 128; the other arguments as mpsa_quant_mx. */
+int mpsa_rope_quant_mx(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b, long long xs_h,
+                       long long xs_l, const void* cos, const void* sin, long long rope_sb, float s, int fp8_fmt,
+                       void* fp8_codes, long long o8_b, long long o8_h, long long o8_l, void* fp4_codes_unpacked,
+                       long long o4_b, long long o4_h, long long o4_l, void* fp8_scales_rm, void* fp4_scales_rm,
+                       void* fp4_codes_packed, void* fp8_scales_tiled, void* fp4_scales_tiled, void* stream);
+
 /* Per-32 int8 quantizer, one side per call.  Replaces quant_fpxint8 (ours/quant_mxint8.py:21-114).
  *   codes int8 with byte strides o_*; scales fp32 [B,H,L,D/32]. */
 int mpsa_quant_int8(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b, long long xs_h,

@@ -28,6 +28,9 @@ struct QuantParams {
   long long xs_b, xs_h, xs_l;  // input strides in elements (inner stride 1)
   float s;                     // fp32 scalar multiplied into x before quantisation
   const float* center;         // optional [B,H,D]: subtracted from every row first (result rounded to the input dtype)
+  const float* rope_cos;       // ROPE kernels: cos / sin of the rotation angles, fp32 [.., L, D/2], batch stride rope_sb
+  const float* rope_sin;       // (0 = shared by the batch), shared by the heads
+  long long rope_sb;
   int fp8_fmt;                 // FMT_FP8_E5M2 or FMT_FP8_E4M3
   // reference-format outputs (strided like the input tensor's logical shape)
   uint8_t* fp8_codes;  long long o8_b, o8_h, o8_l;
@@ -117,7 +120,11 @@ __device__ __forceinline__ uint32_t cvt_fp8x4_regs(float y0, float y1, float y2,
   return r;
 }
 
-template <typename T>
+// ROPE: the rotary embedding is applied on the way in (rotate-half convention: y1 = x1 cos - x2 sin, y2 = x2 cos + x1 sin
+// with x1 / x2 the two halves of a row; fp32 products and sum, the result rounded to the input dtype, i.e. the tensor an
+// unfused pipeline would have stored).  A thread then holds a 16-element run of the first half and its partner run of
+// the second half of the same row; D <= 128.
+template <typename T, bool ROPE>
 __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantParams p) {
   __shared__ __align__(16) uint8_t sf8[512];
   __shared__ __align__(16) uint8_t sf4[512];
@@ -138,11 +145,23 @@ __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantPara
   const T* xb = reinterpret_cast<const T*>(p.x) + (long long)b * p.xs_b + (long long)h * p.xs_h;
   float v[kMxRuns][16];
   bool live[kMxRuns];
+  int rls[kMxRuns], cols[kMxRuns];              // row inside the tile and first column of each run
 #pragma unroll
   for (int i = 0; i < kMxRuns; ++i) {
-    const int g = tid + i * kMxThreads;         // run index inside the tile
-    const int r = row0 + (g >> 3), c = col0 + (g & 7) * 16;
-    live[i] = (r < p.L) && (c < p.D);
+    if (ROPE) {
+      const int cpr = p.D >> 5;                 // 16-element runs per half row
+      rls[i] = tid / cpr;
+      cols[i] = (tid % cpr) * 16 + i * (p.D >> 1);
+    } else {
+      const int g = tid + i * kMxThreads;       // run index inside the tile
+      rls[i] = g >> 3;
+      cols[i] = col0 + (g & 7) * 16;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kMxRuns; ++i) {
+    const int r = row0 + rls[i], c = cols[i];
+    live[i] = (rls[i] < 128) && (r < p.L) && (c < p.D);
     if (live[i]) {
       load16<T>(xb + (long long)r * p.xs_l + c, v[i]);
       if (p.center) {
@@ -162,13 +181,29 @@ __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantPara
       for (int j = 0; j < 16; ++j) v[i][j] = 0.0f;
     }
   }
+  if (ROPE && live[0]) {
+    const long long ang = (long long)b * p.rope_sb + (long long)(row0 + rls[0]) * (p.D >> 1) + cols[0];
+    const float4* cs4 = reinterpret_cast<const float4*>(p.rope_cos + ang);
+    const float4* sn4 = reinterpret_cast<const float4*>(p.rope_sin + ang);
+#pragma unroll
+    for (int j4 = 0; j4 < 4; ++j4) {
+      const float4 c4 = __ldg(cs4 + j4), s4 = __ldg(sn4 + j4);
+      const float co[4] = {c4.x, c4.y, c4.z, c4.w}, si[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int j = 4 * j4 + jj;
+        const float x1 = v[0][j], x2 = v[1][j];
+        v[0][j] = round_as<T>(__fsub_rn(__fmul_rn(x1, co[jj]), __fmul_rn(x2, si[jj])));
+        v[1][j] = round_as<T>(__fadd_rn(__fmul_rn(x2, co[jj]), __fmul_rn(x1, si[jj])));
+      }
+    }
+  }
   const int nblk = p.D >> 5;
   const bool scaled = (p.s != 1.0f);
 #pragma unroll
   for (int i = 0; i < kMxRuns; ++i) {
-    const int g = tid + i * kMxThreads;
-    const int rl = g >> 3;                  // row inside the tile
-    const int r = row0 + rl, c = col0 + (g & 7) * 16;
+    const int rl = rls[i];                  // row inside the tile
+    const int r = row0 + rl, c = cols[i];
     float amax = 0.0f;
     if (scaled) {
 #pragma unroll
@@ -548,12 +583,19 @@ __global__ void col_mean_finish_kernel(const float* part, float* mean, int L, in
 using namespace mpsa;
 
 static int quant_mx_launch(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b,
-                           long long xs_h, long long xs_l, float s, const void* center, int fp8_fmt, void* fp8_codes,
+                           long long xs_h, long long xs_l, float s, const void* center, const void* rope_cos,
+                           const void* rope_sin, long long rope_sb, int fp8_fmt, void* fp8_codes,
                            long long o8_b, long long o8_h, long long o8_l, void* fp4_codes_unpacked,
                            long long o4_b, long long o4_h, long long o4_l, void* fp8_scales_rm,
                            void* fp4_scales_rm, void* fp4_codes_packed, void* fp8_scales_tiled,
                            void* fp4_scales_tiled, void* stream) {
   if (center && ((uintptr_t)center % 16)) return set_error(MPSA_ERR_BAD_ARG, "quant_mx: center must be 16-byte aligned");
+  if (rope_cos) {
+    if (!rope_sin || center) return set_error(MPSA_ERR_BAD_ARG, "rope_quant_mx: cos and sin go together, and not with a center");
+    if (D != 64 && D != 128) return set_error(MPSA_ERR_UNSUPPORTED, "rope_quant_mx: head_dim must be 64 or 128");
+    if (((uintptr_t)rope_cos % 16) || ((uintptr_t)rope_sin % 16) || (rope_sb % 4))
+      return set_error(MPSA_ERR_BAD_ARG, "rope_quant_mx: cos / sin must be 16-byte aligned");
+  }
   if (!x || B <= 0 || H <= 0 || L <= 0 || D <= 0) return set_error(MPSA_ERR_BAD_ARG, "quant_mx: null input or non-positive shape");
   if (D % 32 != 0) return set_error(MPSA_ERR_UNSUPPORTED, "quant_mx: head_dim must be a multiple of 32");
   if (in_dtype < 0 || in_dtype > 2) return set_error(MPSA_ERR_BAD_ARG, "quant_mx: in_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
@@ -570,6 +612,7 @@ static int quant_mx_launch(const void* x, int in_dtype, int B, int H, int L, int
   QuantParams p;
   p.x = x; p.in_dtype = in_dtype; p.B = B; p.H = H; p.L = L; p.D = D;
   p.xs_b = xs_b; p.xs_h = xs_h; p.xs_l = xs_l; p.s = s; p.fp8_fmt = fp8_fmt; p.center = (const float*)center;
+  p.rope_cos = (const float*)rope_cos; p.rope_sin = (const float*)rope_sin; p.rope_sb = rope_sb;
   p.fp8_codes = (uint8_t*)fp8_codes; p.o8_b = o8_b; p.o8_h = o8_h; p.o8_l = o8_l;
   p.fp4_codes_unpacked = (uint8_t*)fp4_codes_unpacked; p.o4_b = o4_b; p.o4_h = o4_h; p.o4_l = o4_l;
   p.fp8_scales_rm = (uint8_t*)fp8_scales_rm; p.fp4_scales_rm = (uint8_t*)fp4_scales_rm;
@@ -578,9 +621,15 @@ static int quant_mx_launch(const void* x, int in_dtype, int B, int H, int L, int
   dim3 grid((L + 127) / 128, (D + 127) / 128, B * H);
   if (grid.y > 65535 || grid.z > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "quant_mx: B*H and D/128 must be below 65536");
   cudaStream_t st = (cudaStream_t)stream;
-  if (in_dtype == 0) quant_mx_kernel<__nv_bfloat16><<<grid, kMxThreads, 0, st>>>(p);
-  else if (in_dtype == 1) quant_mx_kernel<__half><<<grid, kMxThreads, 0, st>>>(p);
-  else quant_mx_kernel<float><<<grid, kMxThreads, 0, st>>>(p);
+  if (p.rope_cos) {
+    if (in_dtype == 0) quant_mx_kernel<__nv_bfloat16, true><<<grid, kMxThreads, 0, st>>>(p);
+    else if (in_dtype == 1) quant_mx_kernel<__half, true><<<grid, kMxThreads, 0, st>>>(p);
+    else quant_mx_kernel<float, true><<<grid, kMxThreads, 0, st>>>(p);
+  } else {
+    if (in_dtype == 0) quant_mx_kernel<__nv_bfloat16, false><<<grid, kMxThreads, 0, st>>>(p);
+    else if (in_dtype == 1) quant_mx_kernel<__half, false><<<grid, kMxThreads, 0, st>>>(p);
+    else quant_mx_kernel<float, false><<<grid, kMxThreads, 0, st>>>(p);
+  }
   return check_launch("quant_mx");
 }
 
@@ -590,7 +639,7 @@ extern "C" int mpsa_quant_mx(const void* x, int in_dtype, int B, int H, int L, i
                              long long o4_b, long long o4_h, long long o4_l, void* fp8_scales_rm,
                              void* fp4_scales_rm, void* fp4_codes_packed, void* fp8_scales_tiled,
                              void* fp4_scales_tiled, void* stream) {
-  return quant_mx_launch(x, in_dtype, B, H, L, D, xs_b, xs_h, xs_l, s, nullptr, fp8_fmt, fp8_codes, o8_b, o8_h, o8_l,
+  return quant_mx_launch(x, in_dtype, B, H, L, D, xs_b, xs_h, xs_l, s, nullptr, nullptr, nullptr, 0, fp8_fmt, fp8_codes, o8_b, o8_h, o8_l,
                          fp4_codes_unpacked, o4_b, o4_h, o4_l, fp8_scales_rm, fp4_scales_rm, fp4_codes_packed,
                          fp8_scales_tiled, fp4_scales_tiled, stream);
 }
@@ -602,8 +651,20 @@ extern "C" int mpsa_quant_mx_centered(const void* x, int in_dtype, int B, int H,
                                       void* fp8_scales_rm, void* fp4_scales_rm, void* fp4_codes_packed,
                                       void* fp8_scales_tiled, void* fp4_scales_tiled, void* stream) {
   if (!center) return set_error(MPSA_ERR_BAD_ARG, "quant_mx_centered: center is null");
-  return quant_mx_launch(x, in_dtype, B, H, L, D, xs_b, xs_h, xs_l, s, center, fp8_fmt, fp8_codes, o8_b, o8_h, o8_l,
+  return quant_mx_launch(x, in_dtype, B, H, L, D, xs_b, xs_h, xs_l, s, center, nullptr, nullptr, 0, fp8_fmt, fp8_codes, o8_b, o8_h, o8_l,
                          fp4_codes_unpacked, o4_b, o4_h, o4_l, fp8_scales_rm, fp4_scales_rm, fp4_codes_packed,
+                         fp8_scales_tiled, fp4_scales_tiled, stream);
+}
+
+extern "C" int mpsa_rope_quant_mx(const void* x, int in_dtype, int B, int H, int L, int D, long long xs_b,
+                                  long long xs_h, long long xs_l, const void* cos, const void* sin, long long rope_sb,
+                                  float s, int fp8_fmt, void* fp8_codes, long long o8_b, long long o8_h, long long o8_l,
+                                  void* fp4_codes_unpacked, long long o4_b, long long o4_h, long long o4_l,
+                                  void* fp8_scales_rm, void* fp4_scales_rm, void* fp4_codes_packed,
+                                  void* fp8_scales_tiled, void* fp4_scales_tiled, void* stream) {
+  if (!cos || !sin) return set_error(MPSA_ERR_BAD_ARG, "rope_quant_mx: cos or sin is null");
+  return quant_mx_launch(x, in_dtype, B, H, L, D, xs_b, xs_h, xs_l, s, nullptr, cos, sin, rope_sb, fp8_fmt, fp8_codes, o8_b,
+                         o8_h, o8_l, fp4_codes_unpacked, o4_b, o4_h, o4_l, fp8_scales_rm, fp4_scales_rm, fp4_codes_packed,
                          fp8_scales_tiled, fp4_scales_tiled, stream);
 }
 

@@ -22,6 +22,9 @@ _SIGNATURES = {
     "mpsa_quant_mx_centered": ([c_void_p, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_float, c_void_p, c_int,
                                 c_void_p, c_ll, c_ll, c_ll, c_void_p, c_ll, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p], c_int),
+    "mpsa_rope_quant_mx": ([c_void_p, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_void_p, c_void_p, c_ll, c_float,
+                            c_int, c_void_p, c_ll, c_ll, c_ll, c_void_p, c_ll, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_void_p], c_int),
     "mpsa_col_mean_scratch_floats": ([c_int, c_int, c_int, c_int], c_ll),
     "mpsa_col_mean": ([c_void_p, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_void_p, c_void_p, c_ll,
                        c_void_p], c_int),

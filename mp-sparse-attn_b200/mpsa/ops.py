@@ -111,12 +111,14 @@ def column_mean(x: torch.Tensor, tensor_layout: str = "HND") -> torch.Tensor:
 
 
 def quantize_mx(x: torch.Tensor, scale: float = 1.0, *, want_fp8=True, want_fp4=True, reference_format=False,
-                kernel_format=True, fp8_elem="e5m2", tensor_layout="HND", center=None) -> QuantizedOperand:
+                kernel_format=True, fp8_elem="e5m2", tensor_layout="HND", center=None, rope=None) -> QuantizedOperand:
     """Quantise one operand along its last axis in 32-element MX blocks (one kernel launch).
 
     reference_format: emit what ours/quant_mxint8.py returns (fp4 one code per byte, row-major
     scales, shaped like the input).  kernel_format: emit packed fp4 and 128x4 scale tiles.
-    center: optional fp32 [B,H,D] from column_mean, subtracted from every row before quantising."""
+    center: optional fp32 [B,H,D] from column_mean, subtracted from every row before quantising.
+    rope: optional (cos, sin), fp32 [L, D/2] or [B, L, D/2]: the rotary embedding (rotate-half convention) is applied to
+    every row first, in the same pass (D 64 or 128)."""
     _require_cuda(x)
     if x.dtype not in _IN_DTYPE:
         raise ValueError(f"unsupported input dtype {x.dtype}")
@@ -150,7 +152,18 @@ def quantize_mx(x: torch.Tensor, scale: float = 1.0, *, want_fp8=True, want_fp4=
     outs = (_ptr(out.fp8), *o8, _ptr(out.fp4_unpacked), *o4, _ptr(out.fp8_scales), _ptr(out.fp4_scales),
             _ptr(out.fp4), _ptr(out.fp8_sf), _ptr(out.fp4_sf), _stream())
     with torch.cuda.device(dev):
-        if center is None:
+        if rope is not None:
+            cos, sin = rope
+            if center is not None:
+                raise ValueError("rope and center do not combine: the mean would have to be that of the rotated tensor")
+            if cos.shape != sin.shape or cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.device != dev or \
+                    sin.device != dev or tuple(cos.shape[-2:]) != (L, D // 2) or cos.dim() not in (2, 3) or \
+                    (cos.dim() == 3 and cos.shape[0] != B) or not cos.is_contiguous() or not sin.is_contiguous():
+                raise ValueError("rope = (cos, sin): contiguous fp32 [L, D/2] or [B, L, D/2] on x's device")
+            rc = _lib.load().mpsa_rope_quant_mx(x.data_ptr(), _IN_DTYPE[x.dtype], B, H, L, D, sb, sh, sl, cos.data_ptr(),
+                                                sin.data_ptr(), L * (D // 2) if cos.dim() == 3 else 0, float(scale),
+                                                _FP8_QUANT[fp8_elem], *outs)
+        elif center is None:
             rc = _lib.load().mpsa_quant_mx(x.data_ptr(), _IN_DTYPE[x.dtype], B, H, L, D, sb, sh, sl, float(scale),
                                            _FP8_QUANT[fp8_elem], *outs)
         else:
@@ -221,20 +234,23 @@ def quantize_nvfp4_bh(x: torch.Tensor, scale: float = 1.0):
     return codes, scales, ts
 
 
-def quantize_qk(x: torch.Tensor, scale: float = 1.0, *, fp8_elem="e5m2", fp4_kind="mxfp4", smooth=False) -> QuantizedOperand:
+def quantize_qk(x: torch.Tensor, scale: float = 1.0, *, fp8_elem="e5m2", fp4_kind="mxfp4", smooth=False,
+                rope=None) -> QuantizedOperand:
     """Q or K (depth already padded to 128) in both precisions of the fused forward: MXFP8 and either MXFP4
     (one pass for both) or NVFP4 (a second quantizer).  smooth: subtract the mean over the sequence first
     (the reference's smooth_k), inside the MX quantizer."""
     if fp4_kind not in ("mxfp4", "nvfp4"):
         raise ValueError(f"unknown fp4_kind {fp4_kind!r}")
     center = None
+    if rope is not None and (smooth or fp4_kind != "mxfp4"):
+        raise ValueError("the fused rotary embedding goes with MXFP4/MXFP8 operands and without smooth_k")
     if smooth:
         center = column_mean(x)
         if fp4_kind == "nvfp4":                    # the NVFP4 quantizer has no centred form: it gets the difference
             x = (x.float() - center.unsqueeze(2)).to(x.dtype)
             center = None
     if fp4_kind == "mxfp4":
-        return quantize_mx(x, scale, fp8_elem=fp8_elem, center=center)
+        return quantize_mx(x, scale, fp8_elem=fp8_elem, center=center, rope=rope)
     out = quantize_mx(x, scale, want_fp4=False, fp8_elem=fp8_elem)
     out.fp4, out.fp4_sf, out.fp4_ts = quantize_nvfp4_bh(x, scale)
     out.fp4_kind = "nvfp4"
@@ -353,11 +369,14 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
                       sm_scale: Optional[float] = None, fp8_elem: str = "e5m2",
                       out_dtype: torch.dtype = torch.bfloat16, pv_mode: str = "fp16", check: bool = False,
                       router: str = "band", tau: float = 1.0, fp4_kind: str = "mxfp4",
-                      skip_thresh: Optional[float] = None, return_sparsity: bool = False, smooth_k: bool = False):
+                      skip_thresh: Optional[float] = None, return_sparsity: bool = False, smooth_k: bool = False,
+                      rope=None):
     """Quantise Q/K (both MXFP8 and MXFP4 in one pass each), prepare V, build the precision map and
     run the fused forward.  q [B,Hq,S,D], k/v [B,Hkv,Skv,D]; D in {64, 128}.
     smooth_k: subtract K's mean over the sequence inside the K quantizer (softmax is unchanged by it: every score
     of a row moves by the same amount).
+    rope: (cos, sin) fp32 [Skv, D/2] (or [B, Skv, D/2]): q and k arrive WITHOUT their rotary embedding and the
+    quantizers apply it (queries take the last S positions); D = 128.
 
     router "band": the static diagonal-band map.  router "online": one extra MXFP4 pass over the score tiles
     (router_statistic) promotes to MXFP8 every tile whose statistic reaches `tau` times that of the row's
@@ -374,8 +393,13 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
     if D not in (64, 128):
         raise ValueError("headdim should be in [64, 128].")
     sq = q_side_scale(D, sm_scale)
-    qq = quantize_qk(_pad_depth_128(q), sq, fp8_elem=fp8_elem, fp4_kind=fp4_kind)
-    kq = quantize_qk(_pad_depth_128(k), 1.0, fp8_elem=fp8_elem, fp4_kind=fp4_kind, smooth=smooth_k)
+    rope_q = None
+    if rope is not None:
+        if D != 128:
+            raise ValueError("the fused rotary embedding needs head_dim 128")
+        rope_q = tuple(t[..., Skv - S:, :].contiguous() for t in rope)
+    qq = quantize_qk(_pad_depth_128(q), sq, fp8_elem=fp8_elem, fp4_kind=fp4_kind, rope=rope_q)
+    kq = quantize_qk(_pad_depth_128(k), 1.0, fp8_elem=fp8_elem, fp4_kind=fp4_kind, smooth=smooth_k, rope=rope)
     if pv_mode == "fp16":
         vt = prepare_vt(v)
     elif pv_mode == "requant":

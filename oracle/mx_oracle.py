@@ -182,6 +182,27 @@ def quant_mxfp8_side(x: torch.Tensor, s: float = 1.0, elem: str = "e5m2",
     return yq.reshape(x.shape), e8
 
 
+def rope_rotate_half(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding in the rotate-half convention (what transformers applies to Q and K before the attention
+    call the reference patches, evaluate/llama/modify_sparse_attn.py): with x1 / x2 the halves of the last axis,
+    y1 = x1 cos - x2 sin, y2 = x2 cos + x1 sin.  x [B,H,L,D]; cos / sin fp32 [L,D/2] or [B,L,D/2].  fp32 products and
+    sum (no fused multiply-add), result in x's dtype.  No reference counterpart with this rounding: unpinned."""
+    half = x.shape[-1] // 2
+    x1, x2 = x[..., :half].float(), x[..., half:].float()
+    if cos.dim() == 3:
+        cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
+    y1 = x1 * cos - x2 * sin
+    y2 = x2 * cos + x1 * sin
+    return torch.cat([y1, y2], dim=-1).to(x.dtype)
+
+
+def rope_angles(L: int, D: int, base: float = 10000.0, offset: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos / sin fp32 [L, D/2] of position * base^(-2i/D), positions offset .. offset+L-1."""
+    inv = base ** (-torch.arange(0, D, 2, dtype=torch.float32) / D)
+    ang = torch.arange(offset, offset + L, dtype=torch.float32)[:, None] * inv[None, :]
+    return torch.cos(ang), torch.sin(ang)
+
+
 def q_side_scale(head_dim: int, sm_scale: Optional[float] = None) -> float:
     """Softmax scale folded into Q by every quantizer: sm_scale * log2(e), passed to the
     kernel as an fp32 scalar.  ours/quant_mxint8.py:479-480, :494."""

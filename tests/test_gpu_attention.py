@@ -277,3 +277,14 @@ def test_smooth_k_through_the_reference_entry_point():
     mean = mpsa.column_mean(k.cuda()).cpu()
     kc = (k.float() - mean.unsqueeze(2)).to(torch.bfloat16)
     _check(o.cpu(), O.attention_mxfp(q, kc, v, causal=True), "smooth_k")
+
+
+def test_rotary_embedding_fused_into_the_quantizers():
+    """attention_forward(..., rope=(cos, sin)) on un-rotated q and k equals the oracle on the rotated tensors."""
+    import mpsa
+    q, k, v = O.make_qkv(14, 1, 4, 2, 384, 128)
+    cos, sin = O.rope_angles(384, 128)
+    out = mpsa.attention_forward(q.cuda(), k.cuda(), v.cuda(), causal=True, out_dtype=torch.float32, check=True,
+                                 rope=(cos.cuda(), sin.cuda()))
+    ref = O.attention_mxfp(O.rope_rotate_half(q, cos, sin), O.rope_rotate_half(k, cos, sin), v, causal=True)
+    _check(out.cpu(), ref, "rope")

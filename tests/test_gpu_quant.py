@@ -158,3 +158,30 @@ def test_smooth_k_inside_the_quantizer(shape, dtype):
     assert torch.equal(r.fp8.cpu(), c8) and torch.equal(r.fp8_scales.cpu(), s8)
     assert torch.equal(r.fp4.cpu(), O.pack_e2m1(c4))
     assert torch.equal(r.fp4_sf.cpu().reshape(O.swizzle_scales(s4).shape), O.swizzle_scales(s4))
+
+
+@pytest.mark.parametrize("shape,dtype,batched", [((1, 2, 300, 128), torch.bfloat16, False), ((2, 2, 130, 64), torch.float16, True),
+                                                 ((1, 1, 128, 128), torch.float32, False)])
+def test_rotary_embedding_inside_the_quantizer(shape, dtype, batched):
+    """quantize_mx(x, rope=(cos, sin)) is bit-exact against the oracle quantizing the rotated tensor (rotate-half
+    convention, fp32 arithmetic without fused multiply-add, result rounded to the input dtype)."""
+    import mpsa
+    B, H, L, D = shape
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(shape, generator=g).to(dtype)
+    x[0, 0, 5, :32] = 0
+    if batched:                                  # per-batch positions
+        cs = [O.rope_angles(L, D, offset=17 * b) for b in range(B)]
+        cos, sin = torch.stack([c for c, _ in cs]), torch.stack([s_ for _, s_ in cs])
+    else:
+        cos, sin = O.rope_angles(L, D)
+    s = O.q_side_scale(D)
+    xr = O.rope_rotate_half(x, cos, sin)
+    r = mpsa.quantize_mx(x.cuda(), s, reference_format=True, kernel_format=True, rope=(cos.cuda(), sin.cuda()))
+    c4, s4 = O.quant_mxfp4_side(xr, s)
+    c8, s8 = O.quant_mxfp8_side(xr, s)
+    assert torch.equal(r.fp4_unpacked.cpu(), c4) and torch.equal(r.fp4_scales.cpu(), s4)
+    assert torch.equal(r.fp8.cpu(), c8) and torch.equal(r.fp8_scales.cpu(), s8)
+    assert torch.equal(r.fp4.cpu(), O.pack_e2m1(c4))
+    assert torch.equal(r.fp4_sf.cpu().reshape(O.swizzle_scales(s4).shape), O.swizzle_scales(s4))
+    assert torch.equal(r.fp8_sf.cpu().reshape(O.swizzle_scales(s8).shape), O.swizzle_scales(s8))
