@@ -288,3 +288,23 @@ def test_rotary_embedding_fused_into_the_quantizers():
                                  rope=(cos.cuda(), sin.cuda()))
     ref = O.attention_mxfp(O.rope_rotate_half(q, cos, sin), O.rope_rotate_half(k, cos, sin), v, causal=True)
     _check(out.cpu(), ref, "rope")
+
+
+def test_persisted_kv_block_feeds_the_forward(tmp_path):
+    """K and V quantised once, packed into the persisted byte form on the device, written to a file, read back and
+    unpacked as views: the forward gives bit-identical output to the one on the live operands."""
+    import mpsa
+    from mpsa import kvstore, ops
+    B, Hq, Hkv, S, D = 1, 4, 2, 640, 128
+    q, k, v = O.make_qkv(15, B, Hq, Hkv, S, D, outliers=2)
+    qq = mpsa.quantize_mx(q.cuda(), ops.q_side_scale(D))
+    kq, vq = mpsa.quantize_mx(k.cuda(), 1.0), mpsa.quantize_v_seq(v.cuda())
+    kw = dict(causal=True, out_dtype=torch.float32, check=True)
+    direct = ops.attention_forward_quantized(qq, kq, vq, B, Hq, Hkv, S, S, D, **kw)
+    path = str(tmp_path / "kv.mpsakv")
+    n = kvstore.save_kv(path, kq, vq)
+    assert n == kvstore.packed_size(kq, vq)
+    k2, v2, h = kvstore.load_kv(path, device="cuda")
+    assert (h["S"], h["Hkv"], h["pitch"]) == (S, Hkv, 640) and torch.equal(k2.fp4, kq.fp4) and torch.equal(v2.v4_sf, vq.v4_sf)
+    again = ops.attention_forward_quantized(qq, k2, v2, B, Hq, Hkv, S, S, D, **kw)
+    assert torch.equal(direct, again)
