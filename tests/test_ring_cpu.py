@@ -147,3 +147,47 @@ def test_ring_matches_single_process_attention(world, layout, causal, exchange):
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), layout, causal, exchange, q, k, v, ref, ret), nprocs=world, join=True)
     assert len(ret) == world and max(ret.values()) < 1e-5, dict(ret)
+
+
+def test_assemble_lays_the_gathered_blocks_out_in_sequence_order():
+    """exchange="gather": the per-block payloads (arrival order) become one K operand and one V^T operand whose rows
+    run over the whole sequence; checked byte for byte on the host with the CUDA backend's own code (it only moves
+    bytes; the kernels are not involved)."""
+    from mpsa import ops, ring
+
+    class Ops:
+        v_pitch = staticmethod(ops.v_pitch)
+        TILE_FP4 = ops.TILE_FP4
+
+        class QuantizedOperand:
+            def __init__(self, **kw):
+                self.__dict__.update(kw)
+
+        class QuantizedV:
+            def __init__(self, vt8, v8_sf, vt4, v4_sf, fp8_elem):
+                self.vt8, self.v8_sf, self.vt4, self.v4_sf = vt8, v8_sf, vt4, v4_sf
+
+    B, Hkv, D, rows, G = 1, 2, 128, 256, 4
+    be = ring.CudaRingBackend.__new__(ring.CudaRingBackend)
+    be.ops, be.B, be.Hkv, be.D, be.rows, be.device, be.fp8_elem, be._zeros = Ops, B, Hkv, D, rows, "cpu", "e5m2", {}
+    be.nt, be.pad = rows // 128, ops.v_pitch(rows)
+    nt, pad = be.nt, be.pad
+    be.sizes = (B * Hkv * rows * 64, B * Hkv * nt * 512, B * Hkv * D * pad // 2, B * Hkv * (pad // 128) * 512)
+    g = torch.Generator().manual_seed(7)
+    gathered = torch.randint(0, 256, (G, sum(be.sizes)), dtype=torch.uint8, generator=g)
+    order = [2, 0, 3, 1]                           # order[g] = arrival row of sequence block g
+    kq, vq, n = be.assemble(gathered, order)
+    assert n == G and kq.fp4.shape == (B, Hkv, G * rows, 64) and vq.vt4.shape[-1] * 2 >= G * rows
+    for blk in range(G):
+        row, o = gathered[order[blk]], 0
+        k4 = row[o:o + be.sizes[0]].view(B, Hkv, rows, 64); o += be.sizes[0]
+        k4s = row[o:o + be.sizes[1]].view(B, Hkv, nt, 1, 512); o += be.sizes[1]
+        v4 = row[o:o + be.sizes[2]].view(B, Hkv, D, pad // 2); o += be.sizes[2]
+        v4s = row[o:o + be.sizes[3]].view(B, Hkv, pad // 128, 512)
+        assert torch.equal(kq.fp4[:, :, blk * rows:(blk + 1) * rows], k4)
+        assert torch.equal(kq.fp4_sf[:, :, blk * nt:(blk + 1) * nt], k4s)
+        assert torch.equal(vq.vt4[..., blk * rows // 2:(blk + 1) * rows // 2], v4[..., :rows // 2])
+        assert torch.equal(vq.v4_sf[:, :, blk * nt:(blk + 1) * nt], v4s[:, :, :nt])
+    with pytest.raises(ValueError):
+        be.rows = 200
+        be.assemble(gathered, order)
