@@ -14,6 +14,10 @@ the slowest rank's time.
 
 `--impl reference` times the CPU restatement of the reference's algorithm (the oracle) on the host
 cores, on a bounded sample of the same workload.
+
+Other workloads (their own JSON line, not the headline): `--workload ring [--layout zigzag|contiguous]
+[--exchange gather|ring]` - one causal sequence of 131072 tokens sharded over the ranks (strong scaling);
+`--workload gemm [--size 8192]` - the stand-alone block-scaled GEMM in MXFP8, MXFP4 and NVFP4.
 """
 import argparse
 import json
