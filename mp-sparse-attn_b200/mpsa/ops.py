@@ -364,19 +364,41 @@ def _pad_depth_128(x: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.pad(x, (0, 128 - D))
 
 
+def prepare_kv(k: torch.Tensor, v: torch.Tensor, *, pv_mode: str = "fp16", fp8_elem: str = "e5m2", fp4_kind: str = "mxfp4",
+               smooth_k: bool = False, rope=None):
+    """The key/value side of attention_forward on its own: K quantised in both precisions (depth padded to 128) and V
+    prepared for the chosen P.V mode.  The pair can be kept - in memory, or through mpsa.kvstore - and given to
+    attention_forward(kv=...) any number of times, so K and V are read in 16 bits once."""
+    _require_cuda(k, v)
+    if k.shape[-1] not in (64, 128):
+        raise ValueError("headdim should be in [64, 128].")
+    if rope is not None and k.shape[-1] != 128:
+        raise ValueError("the fused rotary embedding needs head_dim 128")
+    kq = quantize_qk(_pad_depth_128(k), 1.0, fp8_elem=fp8_elem, fp4_kind=fp4_kind, smooth=smooth_k, rope=rope)
+    if pv_mode == "fp16":
+        vt = prepare_vt(v)
+    elif pv_mode == "requant":
+        vt = quantize_v_seq(v, fp8_elem)
+    else:
+        raise ValueError(f"unknown pv_mode {pv_mode!r}")
+    return kq, vt
+
+
 def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, band: int = 1,
                       prec_map: Optional[torch.Tensor] = None, uniform: Optional[str] = None,
                       sm_scale: Optional[float] = None, fp8_elem: str = "e5m2",
                       out_dtype: torch.dtype = torch.bfloat16, pv_mode: str = "fp16", check: bool = False,
                       router: str = "band", tau: float = 1.0, fp4_kind: str = "mxfp4",
                       skip_thresh: Optional[float] = None, return_sparsity: bool = False, smooth_k: bool = False,
-                      rope=None):
+                      rope=None, kv=None):
     """Quantise Q/K (both MXFP8 and MXFP4 in one pass each), prepare V, build the precision map and
     run the fused forward.  q [B,Hq,S,D], k/v [B,Hkv,Skv,D]; D in {64, 128}.
     smooth_k: subtract K's mean over the sequence inside the K quantizer (softmax is unchanged by it: every score
     of a row moves by the same amount).
     rope: (cos, sin) fp32 [Skv, D/2] (or [B, Skv, D/2]): q and k arrive WITHOUT their rotary embedding and the
     quantizers apply it (queries take the last S positions); D = 128.
+    kv: the pair from prepare_kv (or mpsa.kvstore) in place of k and v, which may then be None; pv_mode follows the
+    kind of V given, and smooth_k / the K side of rope have been applied when the pair was made.
 
     router "band": the static diagonal-band map.  router "online": one extra MXFP4 pass over the score tiles
     (router_statistic) promotes to MXFP8 every tile whose statistic reaches `tau` times that of the row's
@@ -387,9 +409,19 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
     pv_mode "requant": P is re-quantised to the tile's MX format and V is quantised along the sequence.
     fp4_kind "nvfp4": the FP4 tiles of Q.K^T use NVFP4 operands (16-element blocks, E4M3 scales, one tensor scale per
     operand) instead of MXFP4; P.V keeps the MX formats."""
-    _require_cuda(q, k, v)
+    if kv is not None:
+        _require_cuda(q)
+        kq, vt = kv
+        codes = kq.fp8 if kq.fp8 is not None else kq.fp4
+        if codes is None or codes.dim() != 4 or codes.shape[0] != q.shape[0]:
+            raise ValueError("kv = (QuantizedOperand of K [B,Hkv,Skv,...], V^T or QuantizedV)")
+        Hkv, Skv = codes.shape[1], codes.shape[2]
+        if kq.fp4_kind != fp4_kind or kq.fp8_elem != fp8_elem:
+            raise ValueError("kv was prepared with another fp4_kind / fp8_elem than this call asks for")
+    else:
+        _require_cuda(q, k, v)
+        _, Hkv, Skv, _ = k.shape
     B, Hq, S, D = q.shape
-    _, Hkv, Skv, _ = k.shape
     if D not in (64, 128):
         raise ValueError("headdim should be in [64, 128].")
     sq = q_side_scale(D, sm_scale)
@@ -399,13 +431,8 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
             raise ValueError("the fused rotary embedding needs head_dim 128")
         rope_q = tuple(t[..., Skv - S:, :].contiguous() for t in rope)
     qq = quantize_qk(_pad_depth_128(q), sq, fp8_elem=fp8_elem, fp4_kind=fp4_kind, rope=rope_q)
-    kq = quantize_qk(_pad_depth_128(k), 1.0, fp8_elem=fp8_elem, fp4_kind=fp4_kind, smooth=smooth_k, rope=rope)
-    if pv_mode == "fp16":
-        vt = prepare_vt(v)
-    elif pv_mode == "requant":
-        vt = quantize_v_seq(v, fp8_elem)
-    else:
-        raise ValueError(f"unknown pv_mode {pv_mode!r}")
+    if kv is None:
+        kq, vt = prepare_kv(k, v, pv_mode=pv_mode, fp8_elem=fp8_elem, fp4_kind=fp4_kind, smooth_k=smooth_k, rope=rope)
     if router == "online":
         if fp4_kind != "mxfp4":
             raise ValueError("the online router reads MXFP4 operands")

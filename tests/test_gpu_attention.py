@@ -308,3 +308,19 @@ def test_persisted_kv_block_feeds_the_forward(tmp_path):
     assert (h["S"], h["Hkv"], h["pitch"]) == (S, Hkv, 640) and torch.equal(k2.fp4, kq.fp4) and torch.equal(v2.v4_sf, vq.v4_sf)
     again = ops.attention_forward_quantized(qq, k2, v2, B, Hq, Hkv, S, S, D, **kw)
     assert torch.equal(direct, again)
+
+
+@pytest.mark.parametrize("pv_mode", ["fp16", "requant"])
+def test_prepared_kv_is_reused(pv_mode):
+    """prepare_kv once, attention_forward(kv=...) for two different query blocks: same bits as the calls that
+    quantise K and V themselves (online router included)."""
+    import mpsa
+    q, k, v = O.make_qkv(16, 1, 4, 2, 512, 128, outliers=2)
+    qd, kd, vd = q.cuda(), k.cuda(), v.cuda()
+    kw = dict(causal=True, pv_mode=pv_mode, router="online", tau=1.1, out_dtype=torch.float32, check=True)
+    kv = mpsa.prepare_kv(kd, vd, pv_mode=pv_mode)
+    assert torch.equal(mpsa.attention_forward(qd, None, None, kv=kv, **kw), mpsa.attention_forward(qd, kd, vd, **kw))
+    q2 = qd[:, :, 256:].contiguous()               # the last 256 queries against all keys
+    assert torch.equal(mpsa.attention_forward(q2, None, None, kv=kv, **kw), mpsa.attention_forward(q2, kd, vd, **kw))
+    with pytest.raises(ValueError):
+        mpsa.attention_forward(qd, None, None, kv=kv, fp4_kind="nvfp4", **kw)
