@@ -61,3 +61,28 @@ def test_oracle_online_map_rules():
     assert m[0, 0].tolist() == [[1, 0, 0, 0], [2, 1, 0, 0], [2, 2, 1, 0], [2, 1, 2, 1]]
     m = O.precision_map_online(stat, 512, 512, causal=True, band=1, tau=1.1, skip_thresh=0.5)
     assert m[0, 0].tolist() == [[1, 0, 0, 0], [2, 1, 0, 0], [2, 2, 1, 0], [2, 1, 0, 1]]      # the first tile and the band are never dropped
+
+
+def test_oracle_rotary_embedding_is_the_rotate_half_rule():
+    """The oracle's restatement against the formula written the way transformers writes it:
+    x * cos + rotate_half(x) * sin with cos / sin repeated over the two halves."""
+    import torch
+    from oracle import mx_oracle as O
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(2, 3, 40, 64, generator=g).to(torch.bfloat16)
+    cos, sin = O.rope_angles(40, 64, offset=5)
+    assert cos.shape == (40, 32) and float(cos[0, 0]) == float(torch.cos(torch.tensor(5.0)))
+    cc, ss = torch.cat([cos, cos], -1), torch.cat([sin, sin], -1)
+    rot = torch.cat([-x[..., 32:].float(), x[..., :32].float()], -1)
+    ref = (x.float() * cc + rot * ss).to(torch.bfloat16)
+    assert torch.equal(O.rope_rotate_half(x, cos, sin), ref)
+    # per-batch angles
+    cb, sb = torch.stack([cos, cos.flip(0)]), torch.stack([sin, sin.flip(0)])
+    y = O.rope_rotate_half(x, cb, sb)
+    assert torch.equal(y[0], ref[0]) and not torch.equal(y[1], ref[1])
+    # a rotation keeps the norm of every (x1[i], x2[i]) pair
+    xf = torch.randn(1, 1, 40, 64, generator=g)
+    yf = O.rope_rotate_half(xf, cos, sin)
+    n0 = xf[..., :32] ** 2 + xf[..., 32:] ** 2
+    n1 = yf[..., :32] ** 2 + yf[..., 32:] ** 2
+    assert torch.allclose(n0, n1, rtol=1e-5, atol=1e-6)
