@@ -21,6 +21,7 @@ from . import ops
 PV_MODE = "requant"        # "fp16" for the reference's P.V precision
 ROUTER = "band"            # "online" adds the statistic pass
 TAU = 1.1
+SMOOTH_K = False           # True: subtract K's mean over the sequence inside the K quantizer (the default of the reference's mxfp_attn)
 
 
 def mpsa_attention_forward(module: torch.nn.Module, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
@@ -38,7 +39,7 @@ def mpsa_attention_forward(module: torch.nn.Module, query: torch.Tensor, key: to
                                       is_causal=is_causal, **kwargs)
     out = ops.attention_forward(query, key, value, causal=bool(is_causal), sm_scale=scaling, out_dtype=query.dtype
                                 if query.dtype != torch.float32 else torch.float32, pv_mode=PV_MODE,
-                                router=ROUTER, tau=TAU)
+                                router=ROUTER, tau=TAU, smooth_k=SMOOTH_K)
     return out.transpose(1, 2).contiguous(), None
 
 
