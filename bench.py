@@ -17,7 +17,9 @@ cores, on a bounded sample of the same workload.
 
 Other workloads (their own JSON line, not the headline): `--workload ring [--layout zigzag|contiguous]
 [--exchange gather|ring]` - one causal sequence of 131072 tokens sharded over the ranks (strong scaling);
-`--workload gemm [--size 8192]` - the stand-alone block-scaled GEMM in MXFP8, MXFP4 and NVFP4.
+`--workload gemm [--size 8192]` - the stand-alone block-scaled GEMM in MXFP8, MXFP4 and NVFP4;
+`--workload refcmp --reference-dir DIR` - the reference's own Triton kernels (imported unmodified from DIR, a
+checkout of the reference project) timed beside this library's on the same GPU and the same operands.
 """
 import argparse
 import json
@@ -452,6 +454,131 @@ def run_gemm(args):
                       "gpu_launches": 3 * K}))
 
 
+def run_refcmp(args):
+    """The reference's Triton kernels beside this library's, same process, same operands, CUDA events:
+    block_scaled_matmul "mxfp8" at M=N=K=--size (ours/block_scaled_matmul.py:271-296); the fused attention in its
+    "mxfp8" mode, non-causal, equal head counts, D=128 - the one shape family the reference kernel handles
+    (ours/mxfp_attn_kernel.py:19-74, :362-423) - kernel alone and whole wrapper; quant_mxfp4 / quant_mxfp8e5 on the
+    Llama-shaped Q and K (ours/quant_mxint8.py:453-512, :223-272).  The reference's MXFP4 attention mode packs the
+    wrong axis and reads out of bounds, and its "nvfp4" GEMM mode does not compile: neither is run."""
+    ref_dir = args.reference_dir or os.environ.get("MPSA_REFERENCE_DIR")
+    if not ref_dir or not os.path.isdir(os.path.join(ref_dir, "ours")):
+        raise SystemExit("--workload refcmp needs --reference-dir (or MPSA_REFERENCE_DIR): a checkout of the reference project")
+    import importlib
+    import torch._dynamo  # noqa: F401  (the reference's decorators pull it in; it must be imported before `ours` is swapped)
+    import mpsa
+    import ours.quant_mxint8 as our_quant
+    from ours.mxfp_attn_kernel import mxfp_attn_kernel as our_attn
+    # The reference's package is a directory `ours` without __init__.py and this library's mirror has the same name:
+    # import the reference modules with only the reference checkout on the path, then put everything back.
+    saved = {n: m for n, m in sys.modules.items() if n == "ours" or n.startswith("ours.")}
+    for n in saved:
+        del sys.modules[n]
+    saved_path = list(sys.path)
+    sys.path[:] = [ref_dir] + [p for p in saved_path if not os.path.isdir(os.path.join(p or ".", "ours"))]
+    try:
+        ref_quant = importlib.import_module("ours.quant_mxint8")
+        ref_attn = importlib.import_module("ours.mxfp_attn_kernel")
+        ref_gemm = importlib.import_module("ours.block_scaled_matmul")
+    finally:
+        sys.path[:] = saved_path
+        for n in [n for n in sys.modules if n == "ours" or n.startswith("ours.")]:
+            del sys.modules[n]
+        sys.modules.update(saved)
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    K, W = args.steps, max(args.warmup, 3)
+    sampler = ClockSampler(0)
+    sampler.start()
+
+    def timed(fn, steps=K):
+        for _ in range(W):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    res = {}
+    # ---- GEMM, mxfp8 ----
+    n = args.size
+    g = torch.Generator(device=dev).manual_seed(1)
+    a = torch.randn(n, n, generator=g, device=dev).to(torch.bfloat16)
+    b = torch.randn(n, n, generator=g, device=dev).to(torch.bfloat16)
+    qa, qb = mpsa.quantize_mx(a.view(1, 1, n, n), 1.0, want_fp4=False), mpsa.quantize_mx(b.view(1, 1, n, n), 1.0, want_fp4=False)
+    a8, b8 = qa.fp8.view(n, n).view(torch.float8_e5m2), qb.fp8.view(n, n).view(torch.float8_e5m2)
+    sa, sb = qa.fp8_sf.view(n // 128, n // 128, 32, 4, 4), qb.fp8_sf.view(n // 128, n // 128, 32, 4, 4)
+    cfg = {"BLOCK_SIZE_M": 128, "BLOCK_SIZE_N": 256, "BLOCK_SIZE_K": 128, "num_stages": 4, "ELEM_PER_BYTE_A": 1,
+           "ELEM_PER_BYTE_B": 1, "VEC_SIZE": 32}
+    c_ref = ref_gemm.block_scaled_matmul(a8, sa, b8, sb, torch.float16, n, n, n, cfg)
+    c_our = mpsa.gemm_block_scaled(a8, sa, b8, sb, torch.float16, n, n, n, "mxfp8")
+    flops = 2.0 * n ** 3
+    t_ref = timed(lambda: ref_gemm.block_scaled_matmul(a8, sa, b8, sb, torch.float16, n, n, n, cfg))
+    t_our = timed(lambda: mpsa.gemm_block_scaled(a8, sa, b8, sb, torch.float16, n, n, n, "mxfp8"))
+    d = (c_ref.float() - c_our.float())
+    res["gemm_mxfp8"] = {"shape": f"M=N=K={n}", "reference_ms": round(t_ref, 4), "ours_ms": round(t_our, 4),
+                         "reference_tflops": round(flops / t_ref / 1e9, 1), "ours_tflops": round(flops / t_our / 1e9, 1),
+                         "rel_l2_between": float(d.norm() / c_ref.float().norm())}
+    del a, b, qa, qb, a8, b8, sa, sb, c_ref, c_our, d
+    # ---- attention, mxfp8 mode, non-causal, equal head counts ----
+    for S in args.refcmp_seq:
+        H = 32
+        g = torch.Generator(device=dev).manual_seed(2)
+        q = torch.randn(1, H, S, D, generator=g, device=dev).to(torch.float16)
+        k = torch.randn(1, H, S, D, generator=g, device=dev).to(torch.float16)
+        v = torch.randn(1, H, S, D, generator=g, device=dev).to(torch.float16)
+        o_ref = ref_attn.mxfp_attn_kernel(q, k, v, is_causal=False, block_scale_type="mxfp8", skip_thresh=-1e9)
+        o_our = our_attn(q, k, v, is_causal=False, block_scale_type="mxfp8", output_dtype=torch.float16)
+        dd = o_ref.float() - o_our.float()
+        cos = float((o_ref.float().flatten() @ o_our.float().flatten()) / (o_ref.float().norm() * o_our.float().norm()))
+        steps = max(2, min(K, 10))
+        t_ref = timed(lambda: ref_attn.mxfp_attn_kernel(q, k, v, is_causal=False, block_scale_type="mxfp8", skip_thresh=-1e9), steps)
+        t_our = timed(lambda: our_attn(q, k, v, is_causal=False, block_scale_type="mxfp8", output_dtype=torch.float16), steps)
+        # the fused kernels alone, operands already quantised
+        a8r, sar, b8r, sbr = ref_quant.quant_mxfp8e5(q, k)
+        sar = sar.reshape(1, H, S // 128, 4, 32, 1, 4).permute(0, 1, 2, 5, 4, 3, 6).contiguous()
+        sbr = sbr.reshape(1, H, S // 128, 4, 32, 1, 4).permute(0, 1, 2, 5, 4, 3, 6).contiguous()
+        rcfg = {"BLOCK_SIZE_M": 128, "BLOCK_SIZE_N": 128, "BLOCK_SIZE_K": 128, "num_stages": 1, "ELEM_PER_BYTE_A": 1,
+                "ELEM_PER_BYTE_B": 1, "VEC_SIZE": 32}
+        tk_ref = timed(lambda: ref_attn.block_scaled_batched_attn(a8r, sar, b8r, sbr, v, torch.float16, 1, H, S, S, D, rcfg, skip_thresh=-1e9), steps)
+        del a8r, sar, b8r, sbr
+        qq = mpsa.quantize_mx(q, mpsa.ops.q_side_scale(D), want_fp4=False)
+        kq = mpsa.quantize_mx(k, 1.0, want_fp4=False)
+        vt = mpsa.prepare_vt(v)
+        tk_our = timed(lambda: mpsa.attention_forward_quantized(qq, kq, vt, 1, H, H, S, S, D, causal=False, uniform="fp8",
+                                                                out_dtype=torch.float16), steps)
+        fl = attn_flops(1, H, S, D, causal=False)
+        res[f"attn_mxfp8_S{S}"] = {
+            "shape": f"B=1 H={H} S={S} D={D} non-causal, fp16 P.V", "reference_ms": round(t_ref, 3), "ours_ms": round(t_our, 3),
+            "reference_kernel_ms": round(tk_ref, 3), "ours_kernel_ms": round(tk_our, 3),
+            "reference_kernel_tflops": round(fl / tk_ref / 1e9, 1), "ours_kernel_tflops": round(fl / tk_our / 1e9, 1),
+            "cos_between": cos, "rel_l2_between": float(dd.norm() / o_ref.float().norm())}
+        del q, k, v, o_ref, o_our, dd, qq, kq, vt
+    # ---- quantizers on the Llama-shaped operands ----
+    S = args.seq or 32768
+    g = torch.Generator(device=dev).manual_seed(2)
+    q = torch.randn(1, HQ, S, D, generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn(1, HKV, S, D, generator=g, device=dev).to(torch.bfloat16)
+    elems = (HQ + HKV) * S * D
+    for name in ("quant_mxfp4", "quant_mxfp8e5"):
+        rf, of = getattr(ref_quant, name), getattr(our_quant, name)
+        r, o = rf(q, k), of(q, k)
+        same = all(bool(torch.equal(x.view(torch.uint8), y.view(torch.uint8))) for x, y in zip(r, o))
+        t_ref, t_our = timed(lambda: rf(q, k)), timed(lambda: of(q, k))
+        by = elems * (2 + 1 + 1 / 32)              # 16-bit in, one byte per element out, one scale byte per 32
+        res[name] = {"shape": f"Q [1,{HQ},{S},{D}] + K [1,{HKV},{S},{D}] bf16, reference output format",
+                     "reference_ms": round(t_ref, 4), "ours_ms": round(t_our, 4), "reference_gbs": round(by / t_ref / 1e6, 1),
+                     "ours_gbs": round(by / t_our / 1e6, 1), "bit_identical": same}
+        del r, o
+    mpsa.check_status(dev)
+    print(json.dumps({"workload": "reference Triton kernels beside this library, one B200", "steps": K, "warmup": W,
+                      "results": res, "clocks": sampler.stop(), "peaks": measured_peaks()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -459,10 +586,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seq", type=int, default=None, help="sequence length (default 32768; 131072 for --workload ring)")
-    ap.add_argument("--workload", default="prefill", choices=["prefill", "ring", "gemm"],
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "ring", "gemm", "refcmp"],
                     help="prefill: the headline single-GPU workload replicated per GPU; ring: S=131072 causal, "
                          "sequence-sharded over the GPUs (strong scaling); gemm: the standalone block-scaled GEMM (1 GPU)")
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of --workload gemm")
+    ap.add_argument("--reference-dir", default=None, help="refcmp: checkout of the reference project (default $MPSA_REFERENCE_DIR)")
+    ap.add_argument("--refcmp-seq", type=int, nargs="+", default=[8192], help="refcmp: sequence lengths of the attention comparison")
     ap.add_argument("--layout", default="zigzag", choices=["contiguous", "zigzag"])
     ap.add_argument("--exchange", default="gather", choices=["ring", "gather"],
                     help="ring workload: K/V blocks by send/recv round the ring, or one all-gather")
@@ -476,6 +605,8 @@ def main():
         run_ring(args)
     elif args.workload == "gemm":
         run_gemm(args)
+    elif args.workload == "refcmp":
+        run_refcmp(args)
     else:
         run_ours(args)
 

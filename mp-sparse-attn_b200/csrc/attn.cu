@@ -40,6 +40,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cstdlib>
+#include <mutex>
 
 namespace mpsa {
 
@@ -72,19 +73,6 @@ constexpr float ATT_RESCALE_LOG2 = 8.0f;
 constexpr float ATT_LAZY_HEADROOM = 64.0f;            // log2: P up to 2^64 relative to the fixed reference stays far from fp32 overflow
 
 constexpr int TILE_SKIP = 0, TILE_FP8 = 1, TILE_FP4 = 2;
-
-// Optional timeline recording (development builds only, -DMPSA_TRACE): clock64 stamps of one CTA.
-#ifdef MPSA_TRACE
-__device__ long long* g_trace = nullptr;             // [3 roles][64 tiles][8 events]
-#define TRACE_INIT() long long* trace_ptr = (blockIdx.x == 8 && blockIdx.y == 0 && blockIdx.z == 0) ? g_trace : nullptr
-#define TRACE(role, tile, ev)                                                                         \
-  do {                                                                                                \
-    if (trace_ptr && (tile) < 64) trace_ptr[((role) * 64 + (tile)) * 8 + (ev)] = clock64();           \
-  } while (0)
-#else
-#define TRACE_INIT() do {} while (0)
-#define TRACE(role, tile, ev) do {} while (0)
-#endif
 
 struct AttnParams {
   int B, Hq, Hkv, S, Skv, D;        // D = value head dim (64 or 128); Q/K depth is padded to 128
@@ -332,7 +320,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   float* xsum = reinterpret_cast<float*>(smem + ATT_OFF_XSUM);
   float* mrow = reinterpret_cast<float*>(smem + ATT_OFF_MROW);
 
-  TRACE_INIT();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.S + ATT_BM - 1) / ATT_BM, nk = (p.Skv + ATT_BN - 1) / ATT_BN;
   const int qi = nq - 1 - (int)blockIdx.x;          // heavy (late) causal rows first
@@ -508,7 +495,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         const int s = tq % ATT_KSTAGES;
         const bool f8 = map_row[jn] == TILE_FP8;
         fmt_ring = (fmt_ring & ~(1u << (tq & 3))) | ((f8 ? 1u : 0u) << (tq & 3));
-        TRACE(1, tq, 0);
         tc_fence_after();
         const uint32_t sfk = tmem + ATT_COL_SFK + (tq & 1) * 4;
         if (NVF4 && !f8) {
@@ -533,7 +519,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         }
         tc_commit(&k_empty[s]);
         tc_commit(&s_full[tq & 1]);
-        TRACE(1, tq, 1);
         ++tq;
       };
       if (ok) {
@@ -559,10 +544,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         ok = mbar_wait(&v_full[s], (tp / ATT_VSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
         if (!PVQ && ok && jn >= 0) wait_k();
         if (!ok) break;
-        TRACE(1, tp, 2);
         ok = mbar_wait(&p_ready[bsel], (tp >> 1) & 1, p.status, KS_TIMEOUT_PIPE);
         if (!ok) break;
-        TRACE(1, tp, 3);
         tc_fence_after();
         const uint32_t ptm = PVQ ? tmem + ATT_COL_P + bsel * 32 : tmem + ATT_COL_S + bsel * 128;   // P, see the softmax role for its columns
         const uint32_t acc0 = tp > 0 ? 1u : 0u;
@@ -594,7 +577,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         }
         tc_commit(&v_empty[s]);
         tc_commit(&pv_done[bsel]);
-        TRACE(1, tp, 4);
         ++tp;
         if (!PVQ && jn >= 0) {
           issue_qk();
@@ -620,8 +602,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     const int r_in = q * 32 + lane;                 // row inside the tile == TMEM lane
     const int m_glob = qi * ATT_BM + r_in;
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-    const bool tracer = (q == 0 && g == 0 && lane == 0);
-    [[maybe_unused]] const int trole = (wg == 0) ? 2 : 0;
     float* mhint = mrow + 2 * 128;
     float m_seen = -INFINITY;                       // row reference this thread's partial sum refers to
     [[maybe_unused]] float m_fix = -INFINITY;       // LAZY: the row reference fixed by the first tile
@@ -633,10 +613,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       if (map_row[j] == TILE_SKIP) continue;
       if (t % NWG != wg) { ++t; continue; }
       const int bsel = t & 1, lt = t / NWG;         // S buffer; count of tiles this warpgroup has done
-      if (tracer) TRACE(trole, t, 0);
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[bsel], (t >> 1) & 1, p.status, KS_TIMEOUT_MMA));
       if (!ok) break;
-      if (tracer) TRACE(trole, t, 1);
       tc_fence_after();
       const uint32_t slice_addr = tmem + lane_base + ATT_COL_S + bsel * 128 + g * W;
       const int n0 = j * ATT_BN + g * W;            // first key of this thread's slice
@@ -699,7 +677,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         if (!ALL_UP && c + 1 < NCH) tmem_ld32p(slice_addr + (c + 1) * 32, sr);
       }
       float mx = mx0;
-      if (tracer) TRACE(trole, t, 2);
       if (lazy_tile) {
         // nothing to agree on: P and the partial sum already refer to the fixed reference; S is free
         tc_fence_before();
@@ -725,7 +702,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         if (!ok) break;
         m1 = mrow[((t - 1) & 1) * 128 + r_in];
       }
-      if (tracer) TRACE(trole, t, 3);
       // the reference moves only when the maximum grew by more than 2^8 (every thread of a row takes
       // the same decision: it sees the same maximum and the same previous reference)
       const bool grow = (t == 0) || (mx > m1 + ATT_RESCALE_LOG2);
@@ -790,7 +766,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       if (PVQ && LAZY && t == 0) { m_fix = m_used; have_ref = true; }
       }  // !lazy_tile
       l_run += lsum0 + lsum1;
-      if (tracer) TRACE(trole, t, 4);
       if (PVQ) {
         if (!lazy_tile) {
           tc_fence_before();
@@ -825,11 +800,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         else *dst = (uint8_t)psc;
         fence_proxy_async_smem();                   // make the tile visible to tcgen05.cp
       }
-      if (tracer) TRACE(trole, t, 5);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_ready[bsel]);
-      if (tracer) TRACE(trole, t, 6);
       ++t;
     }
     // ---- epilogue: bring every partial sum to the final reference, add them, O / l ----
@@ -1023,12 +996,6 @@ __global__ void route_band_kernel(uint8_t* map, int nq, int nk, int T, int causa
 
 using namespace mpsa;
 
-#ifdef MPSA_TRACE
-extern "C" int mpsa_debug_set_trace(void* buf) {
-  return cudaMemcpyToSymbol(g_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -3;
-}
-#endif
-
 extern "C" int mpsa_route_band(void* map, int nq, int nk, int tile, int causal, int band, int S, int Skv, void* stream) {
   if (!map || nq <= 0 || nk <= 0 || tile <= 0 || band < 0) return set_error(MPSA_ERR_BAD_ARG, "route_band: bad argument");
   if (nq > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "route_band: more than 65535 query tiles");
@@ -1066,6 +1033,24 @@ extern "C" int mpsa_prepare_vt(const void* v, int in_dtype, void* vt, int B, int
   else return set_error(MPSA_ERR_BAD_ARG, "prepare_vt: in_dtype must be 0 (bf16), 1 (fp16) or 2 (fp32)");
   return check_launch("prepare_vt");
 }
+
+namespace {
+struct AttnMaps { const CUtensorMap *q8, *q4, *k8, *k4, *vt, *vt8, *vt4; };
+
+// One launch of one organisation of the forward.  The opt-in for more than 48 KB of dynamic shared memory is a
+// per-device attribute of the kernel: it is set before every launch (a host-side table write), so that any device and
+// any thread may make the first call.
+template <int NWG, int NSPLIT, int PVQ, int NVF4, int LAZY>
+int launch_attn(dim3 grid, cudaStream_t st, const AttnMaps& m, const AttnParams& p) {
+  auto kern = attn_fwd_kernel<NWG, NSPLIT, PVQ, NVF4, (PVQ ? LAZY : 0)>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess) {
+    cudaGetLastError();
+    return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
+  }
+  kern<<<grid, 128 + 128 * NWG * NSPLIT, ATT_SMEM, st>>>(*m.q8, *m.q4, *m.k8, *m.k4, *m.vt, *m.vt8, *m.vt4, p);
+  return check_launch("attn_fwd");
+}
+}  // namespace
 
 extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
                              const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* vt8,
@@ -1126,10 +1111,11 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   p.range_flag = nullptr; p.run_if = nullptr;
   p.acc_in = (const float*)acc_in; p.lse_in = (const float*)lse_in;
   // Softmax organisation: warpgroups taking tiles in turn (1 or 2) x threads per query row inside a
-  // warpgroup (1, 2 or 4).  MPSA_ATTN_WG / MPSA_ATTN_SPLIT override the default.
-  // Defaults (measured on B200 at S=32768): fp16 P.V 2 warpgroups x 1, quantised P.V 2 x 2.
-  static int cfg_of[2] = {0, 0};
-  if (cfg_of[0] == 0) {
+  // warpgroup (1, 2 or 4).  MPSA_ATTN_WG / MPSA_ATTN_SPLIT override the defaults (read once per process):
+  // fp16 P.V 2 warpgroups x 1, quantised P.V 2 x 2.
+  static std::once_flag cfg_once;
+  static int cfg_of[2];
+  std::call_once(cfg_once, [] {
     const char* e1 = getenv("MPSA_ATTN_WG");
     const char* e2 = getenv("MPSA_ATTN_SPLIT");
     for (int m = 0; m < 2; ++m) {
@@ -1139,63 +1125,45 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
       if (nwg == 2 && ns == 4) ns = 2;
       cfg_of[m] = nwg * 10 + ns;
     }
-    cudaError_t e = cudaSuccess;
-#define MPSA_SET_SMEM(A, B) \
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 0, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM); \
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<A, B, 1, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
-    MPSA_SET_SMEM(1, 1) MPSA_SET_SMEM(1, 2) MPSA_SET_SMEM(1, 4) MPSA_SET_SMEM(2, 1) MPSA_SET_SMEM(2, 2)
-#undef MPSA_SET_SMEM
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 1, 0, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 2, 1, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 2, 1, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_fwd_kernel<2, 2, 1, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
-    if (e != cudaSuccess) {
-      cfg_of[0] = 0;
-      return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
-    }
-  }
+  });
   const int cfg = cfg_of[pv_mode];
   const int nq = (S + ATT_BM - 1) / ATT_BM;
   if (Hq > 65535 || B > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: Hq and B must be below 65536");
-  dim3 grid(nq, Hq, B);
+  const dim3 grid(nq, Hq, B);
   cudaStream_t st = (cudaStream_t)stream;
-  if (pv_mode == 1 && cfg % 10 == 4)
-    return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: quantised P.V needs at most 2 softmax threads per query row");
-  if (fp4_kind == 1) {               // NVFP4 score tiles: the default organisation of each P.V mode only
-    if (pv_mode == 0) {
-      attn_fwd_kernel<2, 1, 0, 1, 0><<<grid, 384, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
-    } else {
-      if (range_flag) {              // fixed-reference kernel first, the exact one as its conditional fallback
-        p.range_flag = range_flag;
-        attn_fwd_kernel<2, 2, 1, 1, 1><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
-        if (int rc = check_launch("attn_fwd")) return rc;
-        p.range_flag = nullptr;
-        p.run_if = range_flag;
-      }
-      attn_fwd_kernel<2, 2, 1, 1, 0><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
-    }
-    return check_launch("attn_fwd");
-  }
-#define MPSA_LAUNCH(A, B, T)                                                                              \
-  do {                                                                                                    \
-    if (pv_mode == 0) attn_fwd_kernel<A, B, 0, 0, 0><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p); \
-    else attn_fwd_kernel<A, B, 1, 0, 0><<<grid, T, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);         \
+  const AttnMaps maps{&tq8, &tq4, &tk8, &tk4, &tvt, &tvt8, &tvt4};
+  // quantised P.V with a range word: the fixed-reference kernel first, the exact kernel behind it runs only if a
+  // score left the headroom (its CTAs return at once otherwise)
+  const bool lazy_first = pv_mode == 1 && range_flag != nullptr;
+#define MPSA_GO(A, B, PV, NV)                                                              \
+  do {                                                                                     \
+    if (lazy_first) {                                                                      \
+      p.range_flag = range_flag;                                                           \
+      if (int rc = launch_attn<A, B, PV, NV, PV>(grid, st, maps, p)) return rc;            \
+      p.range_flag = nullptr;                                                              \
+      p.run_if = range_flag;                                                               \
+    }                                                                                      \
+    return launch_attn<A, B, PV, NV, 0>(grid, st, maps, p);                                \
   } while (0)
-  if (pv_mode == 1 && range_flag && cfg == 22) {
-    // fixed-reference kernel first; the exact kernel behind it runs only if a score left the headroom
-    p.range_flag = range_flag;
-    attn_fwd_kernel<2, 2, 1, 0, 1><<<grid, 640, ATT_SMEM, st>>>(tq8, tq4, tk8, tk4, tvt, tvt8, tvt4, p);
-    if (int rc = check_launch("attn_fwd")) return rc;
-    p.range_flag = nullptr;
-    p.run_if = range_flag;
+  if (fp4_kind == 1) {               // NVFP4 score tiles: the default organisation of each P.V mode only
+    if (pv_mode == 0) MPSA_GO(2, 1, 0, 1);
+    MPSA_GO(2, 2, 1, 1);
+  }
+  if (pv_mode == 0) {
+    switch (cfg) {
+      case 11: MPSA_GO(1, 1, 0, 0);
+      case 12: MPSA_GO(1, 2, 0, 0);
+      case 14: MPSA_GO(1, 4, 0, 0);
+      case 22: MPSA_GO(2, 2, 0, 0);
+      default: MPSA_GO(2, 1, 0, 0);
+    }
   }
   switch (cfg) {
-    case 11: MPSA_LAUNCH(1, 1, 256); break;
-    case 12: MPSA_LAUNCH(1, 2, 384); break;
-    case 14: MPSA_LAUNCH(1, 4, 640); break;
-    case 21: MPSA_LAUNCH(2, 1, 384); break;
-    default: MPSA_LAUNCH(2, 2, 640); break;
+    case 11: MPSA_GO(1, 1, 1, 0);
+    case 12: MPSA_GO(1, 2, 1, 0);
+    case 14: MPSA_GO(1, 4, 1, 0);
+    case 21: MPSA_GO(2, 1, 1, 0);
+    default: MPSA_GO(2, 2, 1, 0);
   }
-#undef MPSA_LAUNCH
-  return check_launch("attn_fwd");
+#undef MPSA_GO
 }

@@ -256,11 +256,10 @@ static int launch_gemm(const void* a, const void* a_scale, const void* b, const 
   p.M = M; p.N = N; p.K = K; p.mode = mode; p.a_fmt = a_fmt; p.b_fmt = b_fmt;
   p.sfa = (const uint8_t*)a_scale; p.sfb = (const uint8_t*)b_scale; p.nchunks = K / chunk;
   p.c = c; p.ldc = ldc; p.out_dtype = out_dtype; p.alpha = alpha; p.status = status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_block_scaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess)
-      return set_error(MPSA_ERR_LAUNCH, "gemm_block_scaled: cannot reserve %d bytes of shared memory", GEMM_SMEM);
-    attr_set = true;
+  // per-device attribute of the kernel: set before every launch, so that any device and any thread may call first
+  if (cudaFuncSetAttribute(gemm_block_scaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess) {
+    cudaGetLastError();
+    return set_error(MPSA_ERR_LAUNCH, "gemm_block_scaled: cannot reserve %d bytes of shared memory", GEMM_SMEM);
   }
   dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + GEMM_BN - 1) / GEMM_BN, batch);
   if (grid.y > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "gemm_block_scaled: N too large");

@@ -262,11 +262,10 @@ extern "C" int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S = S; p.Skv = Skv; p.causal = causal;
   p.nh = ((Hq / Hkv) % 2 == 0) ? 2 : 1;
   p.q4_sf = (const uint8_t*)q4_sf; p.k4_sf = (const uint8_t*)k4_sf; p.part = (float*)scratch; p.status = status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(route_stat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM) != cudaSuccess)
-      return set_error(MPSA_ERR_LAUNCH, "route_stat: cannot reserve shared memory");
-    attr_set = true;
+  // per-device attribute of the kernel: set before every launch, so that any device and any thread may call first
+  if (cudaFuncSetAttribute(route_stat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM) != cudaSuccess) {
+    cudaGetLastError();
+    return set_error(MPSA_ERR_LAUNCH, "route_stat: cannot reserve shared memory");
   }
   if (Hq > 65535 || B > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "route_stat: Hq and B must be below 65536");
   const int nq = (S + RT_BM - 1) / RT_BM, nk = (Skv + RT_BN - 1) / RT_BN;
