@@ -23,7 +23,8 @@
 //               TMEM (its own columns, so that Q.K^T of tile t+2 can be issued before P.V of tile t); the
 //               row reference is kept integral so that the codes do not depend on it.  By default the
 //               reference is fixed after the first key tile (template parameter LAZY, see the kernel).
-// Roles: warp 0 TMA producer, warp 1 MMA issuer (warps 2-3 idle), warps 4.. softmax/correction/epilogue.  S is
+// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2.. softmax/correction/epilogue (a warp reaches the TMEM lane
+// quarter warp % 4, so any four consecutive warps cover the 128 rows).  S is
 // double-buffered in TMEM so that Q.K^T of tile t+1 overlaps the softmax of tile t.  NWG softmax
 // warpgroups take the key tiles in turn (warpgroup w owns tiles t = w mod NWG), so that the
 // exponentials of one tile (MUFU) overlap the max / pack / TMEM traffic of the next; the running
@@ -56,14 +57,16 @@ constexpr int ATT_OFF_V = ATT_OFF_K + ATT_KSTAGES * ATT_K_BYTES;
 constexpr int ATT_OFF_SF = ATT_OFF_V + ATT_VSTAGES * ATT_V_BYTES;   // scale tiles: Q8 (512 B), Q4 (1024), K[stages] (1024 each;
                                                                     // an NVFP4 operand has two 128x4 tiles per 128 rows)
 constexpr int ATT_MAX_SPLIT = 4, ATT_MAX_WG = 2;
+constexpr int ATT_SERVICE_THREADS = 96;               // warp 0 TMA producer, warp 1 Q.K^T issuer, warp 2 P.V issuer
 constexpr int ATT_OFF_PSF = ATT_OFF_SF + (3 + 2 * ATT_KSTAGES) * 512;    // P scale tiles [2], V scale tiles [VSTAGES]
 constexpr int ATT_OFF_XMAX = ATT_OFF_PSF + (2 + ATT_VSTAGES) * 512;   // float [WG][2][SPLIT][128] partial row maxima
 constexpr int ATT_OFF_XSUM = ATT_OFF_XMAX + ATT_MAX_WG * 2 * ATT_MAX_SPLIT * 128 * 4;   // float [WG*SPLIT][128] partial sums
 constexpr int ATT_OFF_MROW = ATT_OFF_XSUM + ATT_MAX_WG * ATT_MAX_SPLIT * 128 * 4;       // float [3][128] running row max: per tile parity, and an unsynchronised hint
 constexpr int ATT_OFF_BAR = ATT_OFF_MROW + 3 * 128 * 4;
 constexpr int ATT_OFF_MAP = ATT_OFF_BAR + 512;                        // this CTA's row of the precision map
-constexpr int ATT_MAP_SMEM = 4096;                                    // rows longer than this stay in global memory
-constexpr int ATT_SMEM = ATT_OFF_MAP + ATT_MAP_SMEM + 1024;
+constexpr int ATT_MAP_SMEM = 8192;                                    // longest row: 8192 key tiles (1M keys)
+constexpr int ATT_OFF_VLIST = ATT_OFF_MAP + ATT_MAP_SMEM;             // uint16 per visited tile
+constexpr int ATT_SMEM = ATT_OFF_VLIST + 2 * ATT_MAP_SMEM + 1024;
 constexpr uint32_t ATT_TMEM_COLS = 512;
 constexpr uint32_t ATT_COL_S = 0, ATT_COL_O = 256, ATT_COL_SFQ8 = 384, ATT_COL_SFQ4 = 388, ATT_COL_SFK = 392;
 constexpr uint32_t ATT_COL_SFP = 400, ATT_COL_SFV = 408;
@@ -283,6 +286,52 @@ __device__ __forceinline__ uint32_t softmax_block(const uint32_t* sc, float mref
   }
 }
 
+// floor(d) - emax as an integer and as a float, without conversion instructions (which share the exponential's
+// pipe): d + 1.5 * 2^23 rounded DOWN holds floor(d) in its low mantissa bits (|d| < 2^22).
+__device__ __forceinline__ int block_shift(float d, int emax, float& sh_f) {
+  const float t = __fadd_rd(fmaxf(d, -1024.0f), 12582912.0f);
+  const int sh = max(__float_as_int(t) - 0x4b400000 - emax, -126);
+  sh_f = fmaxf(t - 12582912.0f - (float)emax, -126.0f);
+  return sh;
+}
+
+// One 32-key block of a query row for the quantised P.V, written word by word (eight MXFP4 or four MXFP8 codes at a
+// time) so that few values are live at once.  Same arithmetic as softmax_block<1..3>.
+template <int PMODE>
+__device__ __forceinline__ uint32_t softmax_block_q(const uint32_t* sc, float mref, float bmax, uint32_t* pk,
+                                                    float& lsum0, float& lsum1) {
+  constexpr int EMAX = (PMODE == 3) ? 2 : ((PMODE == 2) ? 8 : 7);
+  constexpr int NW = (PMODE == 3) ? 4 : 8;
+  if (bmax == -INFINITY) {                        // nothing visible in this block
+#pragma unroll
+    for (int i = 0; i < NW; ++i) pk[i] = 0;
+    return 0;
+  }
+  float sh_f;
+  const int sh = block_shift(bmax - mref, EMAX, sh_f);
+  const float ncb = -(mref + sh_f);               // exact: mref is integral in this mode
+  float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) {
+    constexpr int E = 32 / NW;                    // elements per word
+    float y[E];
+#pragma unroll
+    for (int i = 0; i < E; i += 2) {
+      float x0, x1;
+      sub2(x0, x1, __uint_as_float(sc[w * E + i]), __uint_as_float(sc[w * E + i + 1]), ncb);
+      y[i] = ex2(x0);
+      y[i + 1] = ex2(x1);
+      add2(a0, a1, y[i], y[i + 1]);
+    }
+    if (PMODE == 3) pk[w] = pack_e2m1x8(y[0], y[1], y[2], y[3], y[E > 4 ? 4 : 0], y[E > 4 ? 5 : 1], y[E > 4 ? 6 : 2], y[E > 4 ? 7 : 3]);
+    else pk[w] = pack_fp8x4<PMODE == 2>(y[0], y[1], y[2], y[3]);
+  }
+  const float two_sh = __uint_as_float((uint32_t)(sh + 127) << 23);
+  lsum0 = fmaf(a0, two_sh, lsum0);
+  lsum1 = fmaf(a1, two_sh, lsum1);
+  return (uint32_t)(sh + 127);
+}
+
 
 // NVF4: the FP4 tiles of Q.K^T are NVFP4 (16-element blocks, E4M3 scales, kind::mxf4nvf4) instead of MXFP4; their
 // scores are multiplied by the product of the two tensor scales before the softmax.
@@ -293,7 +342,7 @@ __device__ __forceinline__ uint32_t softmax_block(const uint32_t* sc, float mref
 // the headroom sets *range_flag; the launcher then re-runs the exact kernel, which is launched behind this one with
 // run_if = range_flag.
 template <int NWG, int NSPLIT, int PVQ, int NVF4, int LAZY>
-__global__ void __launch_bounds__(128 + 128 * NWG * NSPLIT, 1)
+__global__ void __launch_bounds__(ATT_SERVICE_THREADS + 128 * NWG * NSPLIT, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant__ CUtensorMap tm_q4,
                 const __grid_constant__ CUtensorMap tm_k8, const __grid_constant__ CUtensorMap tm_k4,
                 const __grid_constant__ CUtensorMap tm_vt, const __grid_constant__ CUtensorMap tm_vt8,
@@ -316,9 +365,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   uint64_t* l_bar = m_bar + 8;                     // [4] partial-sum exchange in the epilogue
   uint64_t* s_free = l_bar + 4;                    // 2: quantised P.V only - every softmax thread is done with the S buffer
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
+  int* n_visit = reinterpret_cast<int*>(tmem_slot + 1);
   float* xmax = reinterpret_cast<float*>(smem + ATT_OFF_XMAX);
   float* xsum = reinterpret_cast<float*>(smem + ATT_OFF_XSUM);
   float* mrow = reinterpret_cast<float*>(smem + ATT_OFF_MROW);
+  // the tiles this CTA visits, in order: key-tile index, bit 15 set on MXFP8 tiles.  Every role walks this list, so
+  // skipped cells of the map (above a causal diagonal, the unused end of a longer key buffer, dropped tiles) cost nothing.
+  const uint16_t* vlist = reinterpret_cast<const uint16_t*>(smem + ATT_OFF_VLIST);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.S + ATT_BM - 1) / ATT_BM, nk = (p.Skv + ATT_BN - 1) / ATT_BN;
@@ -326,21 +379,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
   const uint8_t* map_glob = p.map + (long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk;
-  // every role walks this row once per tile; keep it in shared memory when it fits
-  const uint8_t* map_row = (nk <= ATT_MAP_SMEM) ? (smem + ATT_OFF_MAP) : map_glob;
-  // [first, last + 1) non-skipped tile of the row: the roles walk only that range, so the tiles above a causal
-  // diagonal, or the unused end of a longer key buffer, cost nothing
-  int* vis = reinterpret_cast<int*>(tmem_slot + 1);
-  if (threadIdx.x == 0) { vis[0] = nk; vis[1] = 0; }
-  __syncthreads();
-  for (int i0 = 0; i0 < nk; i0 += blockDim.x) {
-    const int i = i0 + threadIdx.x;
-    const uint8_t c = i < nk ? map_glob[i] : (uint8_t)TILE_SKIP;
-    if (i < nk && nk <= ATT_MAP_SMEM) smem[ATT_OFF_MAP + i] = c;
-    const int lo = __reduce_min_sync(0xffffffffu, c != TILE_SKIP ? i : nk);
-    const int hi = __reduce_max_sync(0xffffffffu, c != TILE_SKIP ? i + 1 : 0);
-    if ((threadIdx.x & 31) == 0 && hi > 0) { atomicMin(&vis[0], lo); atomicMax(&vis[1], hi); }
-  }
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) smem[ATT_OFF_MAP + i] = map_glob[i];     // nk <= ATT_MAP_SMEM (host check)
   if (threadIdx.x < 128) reinterpret_cast<float*>(smem + ATT_OFF_MROW)[2 * 128 + threadIdx.x] = -INFINITY;   // reference hint
   const int off = p.Skv - p.S;                      // queries are aligned to the end of the keys
 
@@ -355,11 +394,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     fence_mbar_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, ATT_TMEM_COLS);
+  __syncthreads();
+  if (warp == 2) {
+    // ordered compaction of the map row, 32 cells at a time
+    uint16_t* vl = reinterpret_cast<uint16_t*>(smem + ATT_OFF_VLIST);
+    int base = 0;
+    for (int i0 = 0; i0 < nk; i0 += 32) {
+      const int i = i0 + lane;
+      const uint8_t c = i < nk ? smem[ATT_OFF_MAP + i] : (uint8_t)TILE_SKIP;
+      const uint32_t vis = __ballot_sync(0xffffffffu, c != TILE_SKIP);
+      if (c != TILE_SKIP) vl[base + __popc(vis & ((1u << lane) - 1u))] = (uint16_t)(i | (c == TILE_FP8 ? 0x8000 : 0));
+      base += __popc(vis);
+    }
+    if (lane == 0) *n_visit = base;
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const int j_lo = vis[0], j_hi = vis[1];           // j_lo >= j_hi: the row has no tile to visit
+  const int nv = *n_visit;                          // number of tiles to visit (0: the row has none)
 
   uint8_t* sQ8 = smem + ATT_OFF_Q8;
   uint8_t* sQ4 = smem + ATT_OFF_Q4;
@@ -368,15 +421,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   uint8_t* sSF = smem + ATT_OFF_SF;                 // [0] Q8, [1] Q4, [2+s] K stage s
   uint8_t* sPSF = smem + ATT_OFF_PSF;               // [0..1] P scale tiles per S buffer, [2+s] V stage s
   const int v_half_bytes = p.D * 128;               // one 64-key half of a V^T tile
+  constexpr int SF4 = NVF4 ? 1024 : 512;            // bytes of FP4 scales per 128 rows
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
+    // Consumption order of the issuing warps: K0, K1, (V0, K2), (V1, K3), ...; the rings are filled in that order.
     if (lane == 0) {
       tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_q4); tma_prefetch_desc(&tm_k8);
       tma_prefetch_desc(&tm_k4); tma_prefetch_desc(&tm_vt); tma_prefetch_desc(&tm_vt8); tma_prefetch_desc(&tm_vt4);
       const int q_row = (b * p.Hq + h) * p.S + qi * ATT_BM;
       const long long qsf = ((long long)(b * p.Hq + h) * nq + qi) * 512;
-      constexpr int SF4 = NVF4 ? 1024 : 512;       // bytes of FP4 scales per 128 rows
       mbar_arrive_expect_tx(q_full, ATT_Q8_BYTES + ATT_Q4_BYTES + 512 + SF4);
       tma_load_2d(sQ8, &tm_q8, q_full, 0, q_row);
       tma_load_2d(sQ4, &tm_q4, q_full, 0, q_row);
@@ -384,54 +438,53 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       bulk_load(sSF + 512, p.q4_sf + (NVF4 ? 2 * qsf : qsf), SF4, q_full);
 
       const int k_row0 = (b * p.Hkv + hk) * p.Skv;
-      const long long ksf0 = (long long)(b * p.Hkv + hk) * nk * 512;
+      const uint8_t* k8sf = p.k8_sf + (long long)(b * p.Hkv + hk) * nk * 512;
+      const uint8_t* k4sf = p.k4_sf + (long long)(b * p.Hkv + hk) * nk * SF4;
       const long long vsf0 = (long long)(b * p.Hkv + hk) * p.v_tiles * 512;
       const int v_row = (b * p.Hkv + hk) * p.D;
       bool ok = true;
-      int tk = 0, tv = 0;                          // tiles issued on the K and V rings
-      int jk = j_lo, jv = j_lo;                    // next key-tile index to examine for each ring
-      auto issue_k = [&]() {                       // returns false when no tile is left
-        while (jk < j_hi && map_row[jk] == TILE_SKIP) ++jk;
-        if (jk >= j_hi) return false;
-        const int s = tk % ATT_KSTAGES;
-        if (tk >= ATT_KSTAGES) ok = mbar_wait(&k_empty[s], ((tk / ATT_KSTAGES) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
-        if (!ok) return false;
-        const bool f8 = map_row[jk] == TILE_FP8;
-        mbar_arrive_expect_tx(&k_full[s], (f8 ? ATT_K_BYTES + 512 : ATT_K_BYTES / 2 + SF4));
-        tma_load_2d(sK + s * ATT_K_BYTES, f8 ? &tm_k8 : &tm_k4, &k_full[s], 0, k_row0 + jk * ATT_BN);
-        if (f8) bulk_load(sSF + (3 + 2 * s) * 512, p.k8_sf + ksf0 + (long long)jk * 512, 512, &k_full[s]);
-        else bulk_load(sSF + (3 + 2 * s) * 512, p.k4_sf + (ksf0 + (long long)jk * 512) * (SF4 / 512), SF4, &k_full[s]);
-        ++tk; ++jk;
-        return true;
+      int sk = 0, sv = 0;                          // ring slots, and the parity of the `empty` phase to wait for
+      uint32_t pk_par = 0, pv_par = 0;
+      auto issue_k = [&](int t) {
+        const uint32_t e = vlist[t];
+        const int j = e & 0x7fff;
+        const bool f8 = (e & 0x8000) != 0;
+        if (t >= ATT_KSTAGES) ok = mbar_wait(&k_empty[sk], pk_par, p.status, KS_TIMEOUT_PIPE);
+        if (!ok) return;
+        mbar_arrive_expect_tx(&k_full[sk], (f8 ? ATT_K_BYTES + 512 : ATT_K_BYTES / 2 + SF4));
+        tma_load_2d(sK + sk * ATT_K_BYTES, f8 ? &tm_k8 : &tm_k4, &k_full[sk], 0, k_row0 + j * ATT_BN);
+        if (f8) bulk_load(sSF + (3 + 2 * sk) * 512, k8sf + (long long)j * 512, 512, &k_full[sk]);
+        else bulk_load(sSF + (3 + 2 * sk) * 512, k4sf + (long long)j * SF4, SF4, &k_full[sk]);
+        if (++sk == ATT_KSTAGES) { sk = 0; if (t >= ATT_KSTAGES) pk_par ^= 1; }
       };
-      auto issue_v = [&]() {
-        while (jv < j_hi && map_row[jv] == TILE_SKIP) ++jv;
-        if (jv >= j_hi) return false;
-        const int s = tv % ATT_VSTAGES;
-        if (tv >= ATT_VSTAGES) ok = mbar_wait(&v_empty[s], ((tv / ATT_VSTAGES) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
-        if (!ok) return false;
+      auto issue_v = [&](int t) {
+        const uint32_t e = vlist[t];
+        const int j = e & 0x7fff;
+        if (t >= ATT_VSTAGES) ok = mbar_wait(&v_empty[sv], pv_par, p.status, KS_TIMEOUT_PIPE);
+        if (!ok) return;
         if (PVQ == 0) {
-          mbar_arrive_expect_tx(&v_full[s], 2 * v_half_bytes);
-          tma_load_2d(sV + s * ATT_V_BYTES, &tm_vt, &v_full[s], jv * ATT_BN, v_row);
-          tma_load_2d(sV + s * ATT_V_BYTES + v_half_bytes, &tm_vt, &v_full[s], jv * ATT_BN + 64, v_row);
+          mbar_arrive_expect_tx(&v_full[sv], 2 * v_half_bytes);
+          tma_load_2d(sV + sv * ATT_V_BYTES, &tm_vt, &v_full[sv], j * ATT_BN, v_row);
+          tma_load_2d(sV + sv * ATT_V_BYTES + v_half_bytes, &tm_vt, &v_full[sv], j * ATT_BN + 64, v_row);
         } else {
           // V^T tile in the tile's format: D rows of 128 (MXFP8) or 64 (MXFP4) bytes, and its scale tile
-          const bool f8 = map_row[jv] == TILE_FP8;
-          mbar_arrive_expect_tx(&v_full[s], (f8 ? v_half_bytes : v_half_bytes / 2) + 512);
-          tma_load_2d(sV + s * ATT_V_BYTES, f8 ? &tm_vt8 : &tm_vt4, &v_full[s], f8 ? jv * ATT_BN : jv * (ATT_BN / 2), v_row);
-          bulk_load(sPSF + (2 + s) * 512, (f8 ? p.v8_sf : p.v4_sf) + vsf0 + (long long)jv * 512, 512, &v_full[s]);
+          const bool f8 = (e & 0x8000) != 0;
+          mbar_arrive_expect_tx(&v_full[sv], (f8 ? v_half_bytes : v_half_bytes / 2) + 512);
+          tma_load_2d(sV + sv * ATT_V_BYTES, f8 ? &tm_vt8 : &tm_vt4, &v_full[sv], f8 ? j * ATT_BN : j * (ATT_BN / 2), v_row);
+          bulk_load(sPSF + (2 + sv) * 512, (f8 ? p.v8_sf : p.v4_sf) + vsf0 + (long long)j * 512, 512, &v_full[sv]);
         }
-        ++tv; ++jv;
-        return true;
+        if (++sv == ATT_VSTAGES) { sv = 0; if (t >= ATT_VSTAGES) pv_par ^= 1; }
       };
-      // consumption order of the MMA warp: K0, K1, V0, K2, V1, ...
-      bool more_k = issue_k();
-      while (ok && more_k) {
-        more_k = issue_k();
+      int tk = 0, tv = 0;                          // tiles issued on each ring
+      if (nv > 0) { issue_k(0); tk = 1; }
+      while (ok && tk < nv) {
+        issue_k(tk);
         if (!ok) break;
-        issue_v();
+        ++tk;
+        issue_v(tv);
+        if (ok) ++tv;
       }
-      while (ok && issue_v()) {}
+      while (ok && tv < nv) { issue_v(tv); if (ok) ++tv; }
       if (!ok) {
         // unwind: give copies in flight a chance to land before shared memory is released
         mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
@@ -442,34 +495,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
-    // Issue order: QK(0) QK(1) | PV(0) QK(2) | PV(1) QK(3) | ...  Everything that does not depend
-    // on the softmax of tile t (V and K arrival, descriptors) is settled before the wait for P(t),
-    // so that P.V(t) and Q.K^T(t+2) go out back to back once P(t) is there.
+    // ------------------------------ Q.K^T issuer ------------------------------
+    // S(t) goes to accumulator t & 1 as soon as its K tile has landed and the softmax threads have read S(t - 2).
+    // One thread issues; its loop holds nothing but the waits, one scale copy, the MMAs and two commits: the tensor
+    // pipe takes ~64 cycles per MXFP4 MMA and the loop must stay well below the softmax time of a tile.
     if (lane == 0) {
       uint32_t id8[4], id4[2];
 #pragma unroll
       for (int j = 0; j < 4; ++j) id8[j] = idesc_with_sf_id(idesc_block_scaled(p.fp8_fmt, p.fp8_fmt, ATT_BM, ATT_BN, 1), j, j);
 #pragma unroll
       for (int j = 0; j < 2; ++j) id4[j] = idesc_with_sf_id(idesc_block_scaled(1, 1, ATT_BM, ATT_BN, 1), 2 * j, 2 * j);
-      const uint32_t idesc_pv = idesc_f16(0, 0, ATT_BM, p.D);
+      const uint32_t idn = idesc_block_scaled(1, 1, ATT_BM, ATT_BN, 0);   // NVFP4: E4M3 scales, four per instruction
       const uint64_t q8d = sdesc_kmajor_sw128(smem_u32(sQ8));
       const uint64_t q4d = sdesc_kmajor_sw64(smem_u32(sQ4));
-      const uint64_t k8d0 = sdesc_kmajor_sw128(smem_u32(sK));       // + stage * (ATT_K_BYTES >> 4)
+      const uint64_t k8d0 = sdesc_kmajor_sw128(smem_u32(sK));
       const uint64_t k4d0 = sdesc_kmajor_sw64(smem_u32(sK));
-      const uint64_t vd0 = sdesc_kmajor_sw128(smem_u32(sV));        // + stage * (ATT_V_BYTES >> 4)
-      const uint64_t sfk0 = sdesc_sf_tile(smem_u32(sSF + 3 * 512)); // + stage * (1024 >> 4)
-      const uint32_t idn = idesc_block_scaled(1, 1, ATT_BM, ATT_BN, 0);   // NVFP4: E4M3 scales, four per instruction
-      const uint32_t v_half16 = (uint32_t)v_half_bytes >> 4;
-      const uint64_t v4d0 = sdesc_kmajor_sw64(smem_u32(sV));        // MXFP4 V^T tile (64-byte rows)
-      const uint64_t sfp0 = sdesc_sf_tile(smem_u32(sPSF));          // P scale tiles [2], then V scale tiles per stage
-      uint32_t idp8[4], idp4[2];                                    // P.V block-scaled: M=128, N=D
-#pragma unroll
-      for (int j = 0; j < 4; ++j) idp8[j] = idesc_with_sf_id(idesc_block_scaled(p.fp8_fmt, p.fp8_fmt, ATT_BM, p.D, 1), j, j);
-#pragma unroll
-      for (int j = 0; j < 2; ++j) idp4[j] = idesc_with_sf_id(idesc_block_scaled(1, 1, ATT_BM, p.D, 1), 2 * j, 2 * j);
-      uint32_t fmt_ring = 0;                                        // bit (t & 3): tile t is an FP8 tile
-      constexpr int PW = 128 / NSPLIT;                              // keys per softmax column split
+      const uint64_t sfk0 = sdesc_sf_tile(smem_u32(sSF + 3 * 512));
       bool ok = mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
       if (ok) {
         tc_fence_after();
@@ -481,110 +522,136 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
           tc_cp_32x128b_warpx4(tmem + ATT_COL_SFQ4, sdesc_sf_tile(smem_u32(sSF + 512)));
         }
       }
-      int jq = j_lo;                               // scan position in the map row
-      int tq = 0, tp = 0;                          // tiles issued: Q.K^T and P.V
-      int jn = -1;                                 // key-tile index of the next Q.K^T to issue (-1: none)
-      auto find_next = [&]() {
-        while (jq < j_hi && map_row[jq] == TILE_SKIP) ++jq;
-        jn = (jq < j_hi) ? jq++ : -1;
-      };
-      auto wait_k = [&]() {                        // K tile of Q.K^T number tq has landed
-        ok = mbar_wait(&k_full[tq % ATT_KSTAGES], (tq / ATT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
-      };
-      auto issue_qk = [&]() {                      // needs jn >= 0 and wait_k() done
-        const int s = tq % ATT_KSTAGES;
-        const bool f8 = map_row[jn] == TILE_FP8;
-        fmt_ring = (fmt_ring & ~(1u << (tq & 3))) | ((f8 ? 1u : 0u) << (tq & 3));
+      int sk = 0;                                   // K ring slot of the next Q.K^T
+      uint32_t k_par = 0;                           // phase parity of k_full[sk]
+      // S(t) = Q.K(t)^T into accumulator t & 1; the caller has waited for the accumulator to be free
+      auto issue_qk = [&](int t, uint32_t e) {
+        ok = mbar_wait(&k_full[sk], k_par, p.status, KS_TIMEOUT_TMA);
+        if (!ok) return;
         tc_fence_after();
-        const uint32_t sfk = tmem + ATT_COL_SFK + (tq & 1) * 4;
+        const int bsel = t & 1;
+        const bool f8 = (e & 0x8000) != 0;
+        const uint32_t d = tmem + ATT_COL_S + bsel * 128;
+        const uint32_t sfk = tmem + ATT_COL_SFK + bsel * 4;
+        const uint64_t ksf = sfk0 + (uint64_t)(sk * (1024 >> 4));
         if (NVF4 && !f8) {
-          const uint32_t sfkn = tmem + ATT_COL_SFKN + (tq & 1) * 8;
-          tc_cp_32x128b_warpx4(sfkn, sfk0 + (uint64_t)(s * (1024 >> 4)));
-          tc_cp_32x128b_warpx4(sfkn + 4, sfk0 + (uint64_t)(s * (1024 >> 4) + (512 >> 4)));
-        } else {
-          tc_cp_32x128b_warpx4(sfk, sfk0 + (uint64_t)(s * (1024 >> 4)));
-        }
-        const uint32_t d = tmem + ATT_COL_S + (tq & 1) * 128;
-        if (f8) {
-          const uint64_t kd = k8d0 + (uint64_t)(s * (ATT_K_BYTES >> 4));
+          const uint32_t sfkn = tmem + ATT_COL_SFKN + bsel * 8;
+          tc_cp_32x128b_warpx4(sfkn, ksf);
+          tc_cp_32x128b_warpx4(sfkn + 4, ksf + (512 >> 4));
+          const uint64_t kd = k4d0 + (uint64_t)(sk * (ATT_K_BYTES >> 4));
+#pragma unroll
+          for (int j = 0; j < 2; ++j) mma_nvf4(d, q4d + 2 * j, kd + 2 * j, idn, tmem + ATT_COL_SFQN + 4 * j, sfkn + 4 * j, j > 0);
+        } else if (f8) {
+          tc_cp_32x128b_warpx4(sfk, ksf);
+          const uint64_t kd = k8d0 + (uint64_t)(sk * (ATT_K_BYTES >> 4));
 #pragma unroll
           for (int j = 0; j < 4; ++j) mma_mxf8f6f4(d, q8d + 2 * j, kd + 2 * j, id8[j], tmem + ATT_COL_SFQ8, sfk, j > 0);
         } else {
-          const uint64_t kd = k4d0 + (uint64_t)(s * (ATT_K_BYTES >> 4));
+          tc_cp_32x128b_warpx4(sfk, ksf);
+          const uint64_t kd = k4d0 + (uint64_t)(sk * (ATT_K_BYTES >> 4));
 #pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            if (NVF4) mma_nvf4(d, q4d + 2 * j, kd + 2 * j, idn, tmem + ATT_COL_SFQN + 4 * j, tmem + ATT_COL_SFKN + (tq & 1) * 8 + 4 * j, j > 0);
-            else mma_mxf4(d, q4d + 2 * j, kd + 2 * j, id4[j], tmem + ATT_COL_SFQ4, sfk, j > 0);
-          }
+          for (int j = 0; j < 2; ++j) mma_mxf4(d, q4d + 2 * j, kd + 2 * j, id4[j], tmem + ATT_COL_SFQ4, sfk, j > 0);
         }
-        tc_commit(&k_empty[s]);
-        tc_commit(&s_full[tq & 1]);
-        ++tq;
+        tc_commit(&k_empty[sk]);
+        tc_commit(&s_full[bsel]);
+        if (++sk == ATT_KSTAGES) { sk = 0; k_par ^= 1; }
       };
-      if (ok) {
-        find_next();
-        if (jn >= 0) { wait_k(); if (ok) issue_qk(); }
-        if (ok && tq == 1) {
-          find_next();
-          if (jn >= 0) { wait_k(); if (ok) issue_qk(); }
+      if (PVQ) {
+        // Quantised P lives in its own TMEM columns, so an accumulator is free as soon as the softmax threads have
+        // read it: this warp issues nothing but Q.K^T, two tiles ahead of the softmax; P.V has its own issuer.
+        uint32_t f_par = 0;                         // phase parity of s_free[t & 1] (the release of tile t - 2)
+        uint32_t e = nv > 0 ? vlist[0] : 0;
+        for (int t = 0; t < nv && ok; ++t) {
+          const uint32_t e_next = t + 1 < nv ? vlist[t + 1] : 0;    // fetched a tile ahead of its use
+          if (t >= 2) {
+            ok = mbar_wait(&s_free[t & 1], f_par, p.status, KS_TIMEOUT_PIPE);
+            if (t & 1) f_par ^= 1;
+            if (!ok) break;
+          }
+          issue_qk(t, e);
+          e = e_next;
         }
-        if (ok) find_next();
-      }
-      while (ok && tp < tq) {
-        const int bsel = tp & 1, s = tp % ATT_VSTAGES;
-        if (PVQ && jn >= 0) {
-          // Quantised P lives in its own TMEM columns, so the S buffer is free as soon as the softmax threads
-          // have read it: Q.K^T of tile tp+2 goes out BEFORE P.V of tile tp and runs while P is still being stored.
-          wait_k();
-          if (ok) ok = mbar_wait(&s_free[bsel], (tp >> 1) & 1, p.status, KS_TIMEOUT_PIPE);
+      } else {
+        // fp16 P overwrites S in place, so Q.K^T of tile t + 2 must stay behind P.V of tile t: one thread issues both,
+        // in that order (the tensor pipe executes a thread's instructions in order).
+        const uint32_t idesc_pv = idesc_f16(0, 0, ATT_BM, p.D);
+        const uint64_t vd0 = sdesc_kmajor_sw128(smem_u32(sV));      // + stage * (ATT_V_BYTES >> 4)
+        const uint32_t v_half16 = (uint32_t)v_half_bytes >> 4;
+        constexpr int PW = 128 / NSPLIT;                            // keys per softmax column split
+        if (ok && nv > 0) issue_qk(0, vlist[0]);
+        if (ok && nv > 1) issue_qk(1, vlist[1]);
+        int sv = 0;
+        uint32_t v_par = 0, r_par = 0;              // phase parities: v_full[sv]; p_ready[t & 1]
+        for (int t = 0; t < nv && ok; ++t) {
+          const int bsel = t & 1;
+          const uint32_t e2 = t + 2 < nv ? vlist[t + 2] : 0;
+          ok = mbar_wait(&v_full[sv], v_par, p.status, KS_TIMEOUT_TMA);
+          if (ok) ok = mbar_wait(&p_ready[bsel], r_par, p.status, KS_TIMEOUT_PIPE);
+          if (bsel) r_par ^= 1;
           if (!ok) break;
-          issue_qk();
-          find_next();
-        }
-        ok = mbar_wait(&v_full[s], (tp / ATT_VSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
-        if (!PVQ && ok && jn >= 0) wait_k();
-        if (!ok) break;
-        ok = mbar_wait(&p_ready[bsel], (tp >> 1) & 1, p.status, KS_TIMEOUT_PIPE);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t ptm = PVQ ? tmem + ATT_COL_P + bsel * 32 : tmem + ATT_COL_S + bsel * 128;   // P, see the softmax role for its columns
-        const uint32_t acc0 = tp > 0 ? 1u : 0u;
-        if (PVQ == 0) {
-          const uint64_t vd = vd0 + (uint64_t)(s * (ATT_V_BYTES >> 4));
+          tc_fence_after();
+          const uint32_t ptm = tmem + ATT_COL_S + bsel * 128;
+          const uint64_t vd = vd0 + (uint64_t)(sv * (ATT_V_BYTES >> 4));
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint32_t pcol = ((ks * 16) / PW) * PW + ((ks * 16) % PW) / 2;
             mma_f16_ts(tmem + ATT_COL_O, ptm + pcol, vd + (uint64_t)((ks >> 2) * v_half16 + 2 * (ks & 3)), idesc_pv,
-                       ks > 0 ? 1u : acc0);
+                       ks > 0 ? 1u : (t > 0 ? 1u : 0u));
           }
-        } else {
-          const uint32_t sfp = tmem + ATT_COL_SFP + bsel * 4, sfv = tmem + ATT_COL_SFV + (tp & 1) * 4;
-          tc_cp_32x128b_warpx4(sfp, sfp0 + (uint64_t)(bsel * (512 >> 4)));
-          tc_cp_32x128b_warpx4(sfv, sfp0 + (uint64_t)((2 + s) * (512 >> 4)));
-          if ((fmt_ring >> (tp & 3)) & 1) {
-            const uint64_t vd = vd0 + (uint64_t)(s * (ATT_V_BYTES >> 4));
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {                     // 32 keys per instruction, 8 TMEM columns of P
-              mma_mxf8f6f4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp8[ks], sfp, sfv, ks > 0 ? 1u : acc0);
-            }
-          } else {
-            const uint64_t vd = v4d0 + (uint64_t)(s * (ATT_V_BYTES >> 4));
-#pragma unroll
-            for (int ks = 0; ks < 2; ++ks) {                     // 64 keys per instruction, 8 TMEM columns of P
-              mma_mxf4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp4[ks], sfp, sfv, ks > 0 ? 1u : acc0);
-            }
-          }
-        }
-        tc_commit(&v_empty[s]);
-        tc_commit(&pv_done[bsel]);
-        ++tp;
-        if (!PVQ && jn >= 0) {
-          issue_qk();
-          find_next();
+          tc_commit(&v_empty[sv]);
+          tc_commit(&pv_done[bsel]);
+          if (++sv == ATT_VSTAGES) { sv = 0; v_par ^= 1; }
+          if (t + 2 < nv) issue_qk(t + 2, e2);
         }
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp == 2) {
+    // ------------------------------ P.V issuer (quantised P.V) ----------------
+    // O += P(t).V(t) as soon as V has landed and every softmax thread of the tile has stored its part of P.
+    if (PVQ && lane == 0) {
+      const uint64_t vd0 = sdesc_kmajor_sw128(smem_u32(sV));        // + stage * (ATT_V_BYTES >> 4)
+      const uint64_t v4d0 = sdesc_kmajor_sw64(smem_u32(sV));        // MXFP4 V^T tile (64-byte rows)
+      const uint64_t sfp0 = sdesc_sf_tile(smem_u32(sPSF));          // P scale tiles [2], then V scale tiles per stage
+      uint32_t idp8[4], idp4[2];                                    // P.V block-scaled: M=128, N=D
+#pragma unroll
+      for (int j = 0; j < 4; ++j) idp8[j] = idesc_with_sf_id(idesc_block_scaled(p.fp8_fmt, p.fp8_fmt, ATT_BM, p.D, 1), j, j);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) idp4[j] = idesc_with_sf_id(idesc_block_scaled(1, 1, ATT_BM, p.D, 1), 2 * j, 2 * j);
+      bool ok = true;
+      int sv = 0;
+      uint32_t v_par = 0, r_par = 0;                // phase parities: v_full[sv]; p_ready[t & 1]
+      uint32_t e = nv > 0 ? vlist[0] : 0;
+      for (int t = 0; t < nv && ok; ++t) {
+        const uint32_t e_next = t + 1 < nv ? vlist[t + 1] : 0;
+        const int bsel = t & 1;
+        ok = mbar_wait(&v_full[sv], v_par, p.status, KS_TIMEOUT_TMA);
+        if (ok) ok = mbar_wait(&p_ready[bsel], r_par, p.status, KS_TIMEOUT_PIPE);
+        if (bsel) r_par ^= 1;
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t acc0 = t > 0 ? 1u : 0u;
+        const uint32_t ptm = tmem + ATT_COL_P + bsel * 32;          // quantised P has its own columns
+        const uint32_t sfp = tmem + ATT_COL_SFP + bsel * 4, sfv = tmem + ATT_COL_SFV + bsel * 4;
+        tc_cp_32x128b_warpx4(sfp, sfp0 + (uint64_t)(bsel * (512 >> 4)));
+        tc_cp_32x128b_warpx4(sfv, sfp0 + (uint64_t)((2 + sv) * (512 >> 4)));
+        if (e & 0x8000) {
+          const uint64_t vd = vd0 + (uint64_t)(sv * (ATT_V_BYTES >> 4));
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)                             // 32 keys per instruction, 8 TMEM columns of P
+            mma_mxf8f6f4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp8[ks], sfp, sfv, ks > 0 ? 1u : acc0);
+        } else {
+          const uint64_t vd = v4d0 + (uint64_t)(sv * (ATT_V_BYTES >> 4));
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks)                             // 64 keys per instruction, 8 TMEM columns of P
+            mma_mxf4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp4[ks], sfp, sfv, ks > 0 ? 1u : acc0);
+        }
+        tc_commit(&v_empty[sv]);
+        tc_commit(&pv_done[bsel]);
+        if (++sv == ATT_VSTAGES) { sv = 0; v_par ^= 1; }
+        e = e_next;
+      }
+    }
+  } else {
     // ------------------------------ softmax / correction / epilogue -----------
     // Per tile and thread: ONE pass over the S slice computes P = exp2(S - m) with the row reference
     // m known so far, the slice maximum and the partial row sum; P stays in registers.  Afterwards
@@ -594,7 +661,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     // tile is redone from S, which is still intact in TMEM.  P is written over S only then.
     constexpr int W = 128 / NSPLIT;                 // keys of a tile owned by this thread
     constexpr int NCH = W / 32;                     // 32-column chunks of the slice
-    const int sw = warp - 4;                        // warps 0-3 are the service warpgroup
+    const int sw = warp - ATT_SERVICE_THREADS / 32; // warps 0-2 are the service warps
     const int q = warp & 3;                         // TMEM lane quarter this warp may access
     const int g = (sw >> 2) % NSPLIT;               // column split owned by this warp
     const int wg = (sw >> 2) / NSPLIT;              // warpgroup: owns tiles t with t % NWG == wg
@@ -608,10 +675,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     [[maybe_unused]] bool have_ref = false;
     float l_run = 0.0f;                             // partial row sum over this thread's tiles / columns
     bool ok = true;
-    int t = 0;                                      // index among the non-skipped tiles
-    for (int j = j_lo; j < j_hi && ok; ++j) {
-      if (map_row[j] == TILE_SKIP) continue;
-      if (t % NWG != wg) { ++t; continue; }
+    for (int t = wg; t < nv && ok; t += NWG) {      // t: index in the visit list; this warpgroup owns every NWG-th tile
+      const uint32_t entry = vlist[t];
+      const int j = entry & 0x7fff;                 // key tile
+      const bool tile_f8 = (entry & 0x8000) != 0;
       const int bsel = t & 1, lt = t / NWG;         // S buffer; count of tiles this warpgroup has done
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[bsel], (t >> 1) & 1, p.status, KS_TIMEOUT_MMA));
       if (!ok) break;
@@ -620,7 +687,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       const int n0 = j * ATT_BN + g * W;            // first key of this thread's slice
       const bool need_mask = (p.causal && (j * ATT_BN + ATT_BN - 1 > qi * ATT_BM + off)) || (j * ATT_BN + ATT_BN > p.Skv);
       const int lim = p.causal ? min(p.Skv - 1, m_glob + off) : (p.Skv - 1);   // last visible key
-      [[maybe_unused]] const bool nv_tile = NVF4 && map_row[j] == TILE_FP4;     // scores still lack the tensor scales
+      [[maybe_unused]] const bool nv_tile = NVF4 && !tile_f8;                   // scores still lack the tensor scales
       // all chunk loads go out up front when the slice and its packed P fit in the register budget
       constexpr int REG_BUDGET = ((16384 / 32) / (1 + NWG * NSPLIT)) >= 255 ? 255 : (((16384 / 32) / (1 + NWG * NSPLIT)) & ~7);
       constexpr bool ALL_UP = (W + W / 2 + 40 <= REG_BUDGET);
@@ -630,7 +697,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       float lsum0 = 0.0f, lsum1 = 0.0f;
       uint32_t psc = 0;                             // E8M0 codes of this thread's P blocks (pv_mode 1)
       // precision of P for this tile: 0 fp16; 1 MXFP8 E5M2; 2 MXFP8 E4M3; 3 MXFP4
-      const int pmode = (PVQ == 0) ? 0 : ((map_row[j] == TILE_FP8) ? (p.fp8_fmt == 0 ? 2 : 1) : 3);
+      const int pmode = (PVQ == 0) ? 0 : (tile_f8 ? (p.fp8_fmt == 0 ? 2 : 1) : 3);
       // reference to start with: this thread's own on one warpgroup, else the latest published hint
       const bool lazy_tile = PVQ && LAZY && t > 0;
       if (lazy_tile && !have_ref) {                  // the first tile's owner has fixed the reference
@@ -644,6 +711,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       }
       const float m0 = (t == 0) ? -INFINITY : (lazy_tile ? m_fix : ((NWG > 1) ? mhint[r_in] : m_seen));
       const float mref0 = (m0 == -INFINITY) ? 0.0f : m0;
+      if (!lazy_tile) {
       // ---- the pass ----
       if (ALL_UP) {
 #pragma unroll
@@ -676,11 +744,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         }
         if (!ALL_UP && c + 1 < NCH) tmem_ld32p(slice_addr + (c + 1) * 32, sr);
       }
-      float mx = mx0;
+      }
+      [[maybe_unused]] float mx = mx0;
       if (lazy_tile) {
-        // nothing to agree on: P and the partial sum already refer to the fixed reference; S is free
+        // Fixed reference: nothing to agree on between the threads of a row.  The whole slice goes to registers and the
+        // S buffer is released at once, so that Q.K^T of the tile after next runs under this tile's arithmetic.
+        uint32_t sl[W];
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) tmem_ld32p(slice_addr + c * 32, sl + c * 32);
+        tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(&s_free[bsel]);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          uint32_t* sc = sl + c * 32;
+          if (NVF4 && nv_tile) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) sc[i] = __float_as_uint(__uint_as_float(sc[i]) * p.fp4_scale);
+          }
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (n0 + c * 32 + i > lim) sc[i] = 0xff800000u;      // -inf
+          }
+          const float bm = block_max32(sc);
+          mx0 = fmaxf(mx0, bm);
+          uint32_t code;
+          if (pmode == 3) code = softmax_block_q<3>(sc, mref0, bm, pk + c * 4, lsum0, lsum1);
+          else if (pmode == 1) code = softmax_block_q<1>(sc, mref0, bm, pk + c * 8, lsum0, lsum1);
+          else code = softmax_block_q<2>(sc, mref0, bm, pk + c * 8, lsum0, lsum1);
+          psc |= code << (8 * c);
+        }
         if (m_glob < p.S && mx0 > mref0 + ATT_LAZY_HEADROOM) *p.range_flag = 1;   // rows of the ragged tail hold no data
       } else {
       if (NSPLIT > 1) {
@@ -803,8 +897,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_ready[bsel]);
-      ++t;
     }
+    const int t = nv;                               // tiles visited by the CTA (whoever owned them)
     // ---- epilogue: bring every partial sum to the final reference, add them, O / l ----
     float l_tot = l_run;
     float m_final = m_seen;                         // reference the partial sums end up referring to
@@ -1047,7 +1141,7 @@ int launch_attn(dim3 grid, cudaStream_t st, const AttnMaps& m, const AttnParams&
     cudaGetLastError();
     return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
   }
-  kern<<<grid, 128 + 128 * NWG * NSPLIT, ATT_SMEM, st>>>(*m.q8, *m.q4, *m.k8, *m.k4, *m.vt, *m.vt8, *m.vt4, p);
+  kern<<<grid, ATT_SERVICE_THREADS + 128 * NWG * NSPLIT, ATT_SMEM, st>>>(*m.q8, *m.q4, *m.k8, *m.k4, *m.vt, *m.vt8, *m.vt4, p);
   return check_launch("attn_fwd");
 }
 }  // namespace
@@ -1075,6 +1169,7 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
     return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: merging needs fp32 out, lse, 16-byte aligned acc_in, and outputs distinct from the inputs");
   if (fp4_kind == 1 && !(fp4_scale > 0.0f)) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: NVFP4 needs a positive fp4_scale");
   if (causal && Skv < S) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: causal needs Skv >= S");
+  if ((Skv + ATT_BN - 1) / ATT_BN > ATT_MAP_SMEM) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: at most %d keys", ATT_MAP_SMEM * ATT_BN);
   if (Skv_pad < Skv || Skv_pad % 128) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: Skv_pad must be a multiple of 128, at least Skv");
   const void* ptrs[] = {q8, q8_sf, q4, q4_sf, k8, k8_sf, k4, k4_sf, vt, vt8, v8_sf, vt4, v4_sf, out};
   for (const void* ptr : ptrs)

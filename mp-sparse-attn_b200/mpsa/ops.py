@@ -623,12 +623,16 @@ def _host_chunks(B, Hkv, grp):
 
 
 def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, out: Optional[torch.Tensor] = None,
-                           device=None, out_dtype: torch.dtype = torch.bfloat16, **kw) -> torch.Tensor:
+                           device=None, out_dtype: torch.dtype = torch.bfloat16, non_blocking: bool = False, **kw):
     """The fused forward for operands that live in (pinned) HOST memory: q [B,Hq,S,D], k/v [B,Hkv,S,D] CPU tensors,
     result a pinned CPU tensor [B,Hq,S,D].  The work is cut into (batch, KV group) chunks - independent units of
     the path - and pipelined over copy and compute streams: while chunk i is computed, the inputs of chunk i+1 cross
     PCIe and the output of chunk i-1 goes back, so that a call costs about max(copy, compute) rather than their sum.
-    Keyword arguments are those of attention_forward."""
+    Keyword arguments are those of attention_forward.
+
+    The call returns when the result IS in `out`: it waits (on the host, for this call's last copy only) before
+    returning.  non_blocking=True returns at once with (out, event) instead; `out` may be read after
+    event.synchronize() - or after any later synchronisation of the current stream, which is ordered behind the copies."""
     if q.is_cuda or k.is_cuda or v.is_cuda:
         raise ValueError("attention_forward_host expects CPU tensors; use attention_forward for device tensors")
     B, Hq, S, D = q.shape
@@ -698,6 +702,10 @@ def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     main.wait_event(fin)
     for o in keep:
         o.record_stream(pipe.d2h)
+    if non_blocking:
+        return out, fin
+    fin.synchronize()
+    check_status(dev)
     return out
 
 

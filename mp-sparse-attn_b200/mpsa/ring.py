@@ -214,7 +214,7 @@ class CudaRingBackend:
         """Attention of one query block against sequence blocks [0, n_key_blocks), all tiles MXFP4, no mask."""
         kq, vq, G = gkv
         nt = self.nt
-        key = ("map", G, n_key_blocks)
+        key = ("map", nt, G, n_key_blocks)       # the map is [nt, G * nt]: every length gets its own
         if key not in self._zeros:
             m = torch.zeros((nt, G * nt), dtype=torch.uint8, device=self.device)      # 0 = skip
             m[:, :n_key_blocks * nt] = self.ops.TILE_FP4

@@ -13,7 +13,7 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
     """q [B,Hq,S,D], k/v [B,Hkv,Skv,D] (HND) or [B,S,H,D] (NHD) -> o in q's layout.
 
     block_scale_type: "mxfp4" / "mxfp8" quantise every tile of Q.K^T to that format (the two modes
-    of the reference); "diag" keeps the diagonal tiles in MXFP8 and the rest in MXFP4; "diag_requant"
+    of the reference that run); "nvfp4" does the same with NVFP4 operands; "diag" keeps the diagonal tiles in MXFP8 and the rest in MXFP4; "diag_requant"
     additionally re-quantises P to the tile's format before P.V (V quantised along the sequence);
     "online" / "online_requant" are the same two with the online router on top of the diagonal rule: a tile
     is also MXFP8 if its MXFP4 statistic reaches promote_thresh (default 1.1) times that of the row's first key
@@ -22,7 +22,8 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
     (ours/mxfp_attn_kernel.py:272-297).  return_sparsity then also returns the share of visible tiles dropped.
     attn_mask, dropout_p and attention_sink are accepted and ignored, as in the reference wrapper, and so are
     skip_thresh and return_sparsity outside the online modes; is_causal, scale and output_dtype are honoured
-    (the reference ignores them)."""
+    (the reference ignores them).  Any other block_scale_type raises ValueError, "mixed" included (not built).
+    Host (CPU) tensors are streamed through the GPU and the call returns when the result is in host memory."""
     host = not v.is_cuda
     if host and tensor_layout != "HND":
         raise ValueError("host tensors are taken in the HND layout only")
@@ -37,18 +38,27 @@ def mxfp_attn_kernel(q, k, v, attn_mask=None, dropout_p=0.0,
     if smooth_k and host:
         k = k - k.mean(dim=-2, keepdim=True)                 # :33-34; device tensors: inside the K quantizer, below
     assert q.shape[-1] in [64, 128], "headdim should be in [64, 128]."
+    fp4_kind = "mxfp4"
     if block_scale_type == "mxfp4":
         uniform = "fp4"
+    elif block_scale_type == "mxfp8":
+        uniform = "fp8"
+    elif block_scale_type == "nvfp4":
+        # every tile of Q.K^T in NVFP4 (16-element blocks, E4M3 scales, one tensor scale per operand)
+        uniform, fp4_kind = "fp4", "nvfp4"
     elif block_scale_type in ("diag", "diag_requant", "online", "online_requant"):
         uniform = None
+    elif block_scale_type == "mixed":
+        # the reference's fp8 Q x fp4 K mode (ours/mxfp_attn_kernel.py:170, :264-265) has no kernel here
+        raise ValueError("block_scale_type 'mixed' (MXFP8 Q x MXFP4 K) is not built; use 'diag' for per-tile mixed precision")
     else:
-        uniform = "fp8"
+        raise ValueError(f"Invalid block scale type: {block_scale_type}")      # the reference asserts the set (:452)
     online = block_scale_type.startswith("online")
     kw = dict(causal=bool(is_causal), uniform=uniform, sm_scale=scale, out_dtype=output_dtype,
               pv_mode="requant" if block_scale_type.endswith("requant") else "fp16",
               router="online" if online else "band",
               tau=(1.1 if promote_thresh is None else float(promote_thresh)) if online else 1.0,
-              skip_thresh=skip_thresh if online else None)
+              skip_thresh=skip_thresh if online else None, fp4_kind=fp4_kind)
     if host:
         o = _ops.attention_forward_host(q, k, v, out=out, **kw)      # `out`: a pinned CPU tensor to fill (optional)
     else:

@@ -186,12 +186,29 @@ def test_host_tensors_are_streamed():
                                      pv_mode="requant", check=True).cpu()
     for _ in range(2):                            # second call reuses the staging buffers
         host_out = mxfp_attn_kernel(q, k, v, is_causal=True, block_scale_type="diag_requant", output_dtype=torch.bfloat16)
-        torch.cuda.synchronize()
-        assert not host_out.is_cuda and torch.equal(host_out, dev_out)
+        assert not host_out.is_cuda and torch.equal(host_out, dev_out)     # no synchronisation: the call returned the data
     buf = torch.empty_like(host_out).pin_memory()
     r = mxfp_attn_kernel(q, k, v, is_causal=True, block_scale_type="diag_requant", output_dtype=torch.bfloat16, out=buf)
-    torch.cuda.synchronize()
     assert r is buf and torch.equal(buf, dev_out)
+    # the non-blocking form hands back the event to wait on
+    buf2 = torch.zeros_like(buf).pin_memory()
+    r2, done = mpsa.attention_forward_host(q, k, v, causal=True, out=buf2, out_dtype=torch.bfloat16, pv_mode="requant",
+                                           non_blocking=True)
+    done.synchronize()
+    assert r2 is buf2 and torch.equal(buf2, dev_out)
+
+
+def test_block_scale_type_names_are_checked():
+    """The reference asserts the set of block_scale_type names (ours/mxfp_attn_kernel.py:452); a name outside the
+    set of this library raises instead of silently running another format."""
+    from ours.mxfp_attn_kernel import mxfp_attn_kernel
+    q, k, v = (t.cuda() for t in O.make_qkv(1, 1, 2, 2, 256, 128))
+    for name in ("mixed", "mxfp6", "MXFP8", ""):
+        with pytest.raises(ValueError):
+            mxfp_attn_kernel(q, k, v, block_scale_type=name)
+    o = mxfp_attn_kernel(q, k, v, block_scale_type="nvfp4", output_dtype=torch.float32)
+    ref = O.attention_mxfp(q.cpu(), k.cpu(), v.cpu(), causal=False, uniform="fp4", fp4_kind="nvfp4")
+    _check(o.cpu(), ref, "nvfp4 by name")
 
 
 def test_fixed_reference_kernel_and_its_fallback():

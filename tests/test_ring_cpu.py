@@ -191,3 +191,60 @@ def test_assemble_lays_the_gathered_blocks_out_in_sequence_order():
     with pytest.raises(ValueError):
         be.rows = 200
         be.assemble(gathered, order)
+
+
+class _FailingBackend(MergingRefBackend):
+    """Raises on the rank `bad` at its first block pair: the exchange of step 0 is posted, that of step 1 never is."""
+
+    def __init__(self, rows, D, B, H, fail):
+        super().__init__(rows, D, B, H)
+        self.fail, self.calls = fail, 0
+
+    def partial(self, qq, local_kv, payload, kind):
+        self.calls += 1
+        if self.fail and self.calls == 1:
+            raise RuntimeError("injected failure on this rank")
+        return super().partial(qq, local_kv, payload, kind)
+
+
+def _failing_worker(rank, world, port, bad, ret):
+    import datetime
+    import time
+    sys.path.insert(0, os.path.join(os.path.dirname(HERE), "mp-sparse-attn_b200"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=10))
+    t0 = time.time()
+    g = torch.Generator().manual_seed(rank)
+    q, k, v = (torch.randn(1, 2, 24, 16, generator=g) for _ in range(3))
+    try:
+        ring_attention(q, k, v, causal=True, layout="contiguous", backend=_FailingBackend(24, 16, 1, 2, rank == bad),
+                       out_dtype=torch.float32, exchange="ring")
+        ret[rank] = ("finished", time.time() - t0)
+    except Exception as e:  # noqa: BLE001  (the point of the test: which exception, and how soon)
+        ret[rank] = (type(e).__name__ + ": " + str(e)[:80], time.time() - t0)
+    # no destroy_process_group: the failed rank leaves as a crashed process would
+
+
+def test_a_failing_rank_ends_the_ring_with_an_error_not_a_hang():
+    """Failure detection on the host: one rank raises during the first ring step and leaves.  The rank downstream of it
+    never gets its next block: its receive must end with an exception (peer gone, or the process group's 10 s timeout)
+    instead of waiting for ever; the rank upstream either finishes (it needed nothing from the failed rank) or gets an
+    error from its send.  No rank may hang.  (CPU ranks over gloo: nothing here touches a GPU.)"""
+    world, bad = 3, 1
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, bad, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+    hung = [p for p in procs if p.is_alive()]
+    for p in hung:
+        p.kill()                                    # exactly the processes started above
+    assert not hung, "a rank was still waiting after 90 s"
+    assert set(ret.keys()) == set(range(world)), dict(ret)
+    assert ret[bad][0].startswith("RuntimeError: injected failure")
+    what, secs = ret[(bad + 1) % world]
+    assert what != "finished" and secs < 60, (what, secs)       # the downstream rank saw the failure
+    assert all(v[1] < 60 for v in ret.values()), dict(ret)
