@@ -46,7 +46,8 @@
 namespace mpsa {
 
 constexpr int ATT_BM = 128, ATT_BN = 128, ATT_DQK = 128;
-constexpr int ATT_KSTAGES = 3, ATT_VSTAGES = 2;
+constexpr int ATT_KSTAGES = 4;                        // K ring
+constexpr int ATT_VSLOTS_MAX = 4;                     // V ring: 2 slots of 32 KB (fp16 V^T) or 4 of 16 KB (quantised V^T)
 constexpr int ATT_Q8_BYTES = ATT_BM * 128, ATT_Q4_BYTES = ATT_BM * 64;
 constexpr int ATT_K_BYTES = ATT_BN * 128;             // slot sized for the FP8 tile; FP4 uses half
 constexpr int ATT_V_BYTES = 128 * ATT_BN * 2;         // V^T tile, up to D=128 rows of 128 fp16
@@ -54,12 +55,12 @@ constexpr int ATT_OFF_Q8 = 0;
 constexpr int ATT_OFF_Q4 = ATT_OFF_Q8 + ATT_Q8_BYTES;
 constexpr int ATT_OFF_K = ATT_OFF_Q4 + ATT_Q4_BYTES;
 constexpr int ATT_OFF_V = ATT_OFF_K + ATT_KSTAGES * ATT_K_BYTES;
-constexpr int ATT_OFF_SF = ATT_OFF_V + ATT_VSTAGES * ATT_V_BYTES;   // scale tiles: Q8 (512 B), Q4 (1024), K[stages] (1024 each;
+constexpr int ATT_OFF_SF = ATT_OFF_V + 2 * ATT_V_BYTES;   // scale tiles: Q8 (512 B), Q4 (1024), K[stages] (1024 each;
                                                                     // an NVFP4 operand has two 128x4 tiles per 128 rows)
 constexpr int ATT_MAX_SPLIT = 4, ATT_MAX_WG = 2;
-constexpr int ATT_SERVICE_THREADS = 96;               // warp 0 TMA producer, warp 1 Q.K^T issuer, warp 2 P.V issuer
+constexpr int ATT_SERVICE_THREADS = 128;              // warp 0 Q/K loads, warp 1 Q.K^T issuer, warp 2 P.V issuer, warp 3 V loads
 constexpr int ATT_OFF_PSF = ATT_OFF_SF + (3 + 2 * ATT_KSTAGES) * 512;    // P scale tiles [2], V scale tiles [VSTAGES]
-constexpr int ATT_OFF_XMAX = ATT_OFF_PSF + (2 + ATT_VSTAGES) * 512;   // float [WG][2][SPLIT][128] partial row maxima
+constexpr int ATT_OFF_XMAX = ATT_OFF_PSF + (2 + ATT_VSLOTS_MAX) * 512;   // float [WG][2][SPLIT][128] partial row maxima
 constexpr int ATT_OFF_XSUM = ATT_OFF_XMAX + ATT_MAX_WG * 2 * ATT_MAX_SPLIT * 128 * 4;   // float [WG*SPLIT][128] partial sums
 constexpr int ATT_OFF_MROW = ATT_OFF_XSUM + ATT_MAX_WG * ATT_MAX_SPLIT * 128 * 4;       // float [3][128] running row max: per tile parity, and an unsynchronised hint
 constexpr int ATT_OFF_BAR = ATT_OFF_MROW + 3 * 128 * 4;
@@ -355,9 +356,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   uint64_t* q_full = bars;                         // 1
   uint64_t* k_full = bars + 1;                     // KSTAGES
   uint64_t* k_empty = k_full + ATT_KSTAGES;        // KSTAGES
-  uint64_t* v_full = k_empty + ATT_KSTAGES;        // VSTAGES
-  uint64_t* v_empty = v_full + ATT_VSTAGES;        // VSTAGES
-  uint64_t* s_full = v_empty + ATT_VSTAGES;        // 2
+  uint64_t* v_full = k_empty + ATT_KSTAGES;        // VSLOTS_MAX
+  uint64_t* v_empty = v_full + ATT_VSLOTS_MAX;     // VSLOTS_MAX
+  uint64_t* s_full = v_empty + ATT_VSLOTS_MAX;     // 2
   uint64_t* p_ready = s_full + 2;                  // 2
   uint64_t* pv_done = p_ready + 2;                 // 2
   uint64_t* x_bar = pv_done + 2;                   // [WG][2][4] partial-max exchange inside a warpgroup
@@ -386,7 +387,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < ATT_KSTAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
-    for (int s = 0; s < ATT_VSTAGES; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int s = 0; s < ATT_VSLOTS_MAX; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 128 * NSPLIT); mbar_init(&pv_done[s], 1); mbar_init(&s_free[s], 128 * NSPLIT); }
     for (int s = 0; s < ATT_MAX_WG * 8; ++s) mbar_init(&x_bar[s], NSPLIT);
     for (int s = 0; s < 8; ++s) mbar_init(&m_bar[s], NSPLIT);
@@ -422,13 +423,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   uint8_t* sPSF = smem + ATT_OFF_PSF;               // [0..1] P scale tiles per S buffer, [2+s] V stage s
   const int v_half_bytes = p.D * 128;               // one 64-key half of a V^T tile
   constexpr int SF4 = NVF4 ? 1024 : 512;            // bytes of FP4 scales per 128 rows
+  constexpr int VSTAGES = PVQ ? 4 : 2;              // V ring depth, and the bytes of one slot
+  constexpr int VSLOT = PVQ ? ATT_V_BYTES / 2 : ATT_V_BYTES;
 
   if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
-    // Consumption order of the issuing warps: K0, K1, (V0, K2), (V1, K3), ...; the rings are filled in that order.
+    // ------------------------------ Q and K loads ------------------------------
     if (lane == 0) {
-      tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_q4); tma_prefetch_desc(&tm_k8);
-      tma_prefetch_desc(&tm_k4); tma_prefetch_desc(&tm_vt); tma_prefetch_desc(&tm_vt8); tma_prefetch_desc(&tm_vt4);
+      tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_q4); tma_prefetch_desc(&tm_k8); tma_prefetch_desc(&tm_k4);
       const int q_row = (b * p.Hq + h) * p.S + qi * ATT_BM;
       const long long qsf = ((long long)(b * p.Hq + h) * nq + qi) * 512;
       mbar_arrive_expect_tx(q_full, ATT_Q8_BYTES + ATT_Q4_BYTES + 512 + SF4);
@@ -440,58 +441,58 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       const int k_row0 = (b * p.Hkv + hk) * p.Skv;
       const uint8_t* k8sf = p.k8_sf + (long long)(b * p.Hkv + hk) * nk * 512;
       const uint8_t* k4sf = p.k4_sf + (long long)(b * p.Hkv + hk) * nk * SF4;
-      const long long vsf0 = (long long)(b * p.Hkv + hk) * p.v_tiles * 512;
-      const int v_row = (b * p.Hkv + hk) * p.D;
       bool ok = true;
-      int sk = 0, sv = 0;                          // ring slots, and the parity of the `empty` phase to wait for
-      uint32_t pk_par = 0, pv_par = 0;
-      auto issue_k = [&](int t) {
+      int sk = 0, t = 0;                           // ring slot of tile t
+      uint32_t par = 0;                            // parity of the `empty` phase to wait for
+      for (; t < nv && ok; ++t) {
         const uint32_t e = vlist[t];
         const int j = e & 0x7fff;
         const bool f8 = (e & 0x8000) != 0;
-        if (t >= ATT_KSTAGES) ok = mbar_wait(&k_empty[sk], pk_par, p.status, KS_TIMEOUT_PIPE);
-        if (!ok) return;
+        if (t >= ATT_KSTAGES) ok = mbar_wait(&k_empty[sk], par, p.status, KS_TIMEOUT_PIPE);
+        if (!ok) break;
         mbar_arrive_expect_tx(&k_full[sk], (f8 ? ATT_K_BYTES + 512 : ATT_K_BYTES / 2 + SF4));
         tma_load_2d(sK + sk * ATT_K_BYTES, f8 ? &tm_k8 : &tm_k4, &k_full[sk], 0, k_row0 + j * ATT_BN);
         if (f8) bulk_load(sSF + (3 + 2 * sk) * 512, k8sf + (long long)j * 512, 512, &k_full[sk]);
         else bulk_load(sSF + (3 + 2 * sk) * 512, k4sf + (long long)j * SF4, SF4, &k_full[sk]);
-        if (++sk == ATT_KSTAGES) { sk = 0; if (t >= ATT_KSTAGES) pk_par ^= 1; }
-      };
-      auto issue_v = [&](int t) {
+        if (++sk == ATT_KSTAGES) { sk = 0; if (t >= ATT_KSTAGES) par ^= 1; }
+      }
+      if (!ok) {
+        // unwind: give copies in flight a chance to land before shared memory is released
+        mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
+        for (int u = max(0, t - ATT_KSTAGES); u < t; ++u)
+          mbar_wait(&k_full[u % ATT_KSTAGES], (u / ATT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
+      }
+    }
+  } else if (warp == 3) {
+    // ------------------------------ V loads ------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_vt); tma_prefetch_desc(&tm_vt8); tma_prefetch_desc(&tm_vt4);
+      const long long vsf0 = (long long)(b * p.Hkv + hk) * p.v_tiles * 512;
+      const int v_row = (b * p.Hkv + hk) * p.D;
+      bool ok = true;
+      int sv = 0, t = 0;
+      uint32_t par = 0;
+      for (; t < nv && ok; ++t) {
         const uint32_t e = vlist[t];
         const int j = e & 0x7fff;
-        if (t >= ATT_VSTAGES) ok = mbar_wait(&v_empty[sv], pv_par, p.status, KS_TIMEOUT_PIPE);
-        if (!ok) return;
+        if (t >= VSTAGES) ok = mbar_wait(&v_empty[sv], par, p.status, KS_TIMEOUT_PIPE);
+        if (!ok) break;
         if (PVQ == 0) {
           mbar_arrive_expect_tx(&v_full[sv], 2 * v_half_bytes);
-          tma_load_2d(sV + sv * ATT_V_BYTES, &tm_vt, &v_full[sv], j * ATT_BN, v_row);
-          tma_load_2d(sV + sv * ATT_V_BYTES + v_half_bytes, &tm_vt, &v_full[sv], j * ATT_BN + 64, v_row);
+          tma_load_2d(sV + sv * VSLOT, &tm_vt, &v_full[sv], j * ATT_BN, v_row);
+          tma_load_2d(sV + sv * VSLOT + v_half_bytes, &tm_vt, &v_full[sv], j * ATT_BN + 64, v_row);
         } else {
           // V^T tile in the tile's format: D rows of 128 (MXFP8) or 64 (MXFP4) bytes, and its scale tile
           const bool f8 = (e & 0x8000) != 0;
           mbar_arrive_expect_tx(&v_full[sv], (f8 ? v_half_bytes : v_half_bytes / 2) + 512);
-          tma_load_2d(sV + sv * ATT_V_BYTES, f8 ? &tm_vt8 : &tm_vt4, &v_full[sv], f8 ? j * ATT_BN : j * (ATT_BN / 2), v_row);
+          tma_load_2d(sV + sv * VSLOT, f8 ? &tm_vt8 : &tm_vt4, &v_full[sv], f8 ? j * ATT_BN : j * (ATT_BN / 2), v_row);
           bulk_load(sPSF + (2 + sv) * 512, (f8 ? p.v8_sf : p.v4_sf) + vsf0 + (long long)j * 512, 512, &v_full[sv]);
         }
-        if (++sv == ATT_VSTAGES) { sv = 0; if (t >= ATT_VSTAGES) pv_par ^= 1; }
-      };
-      int tk = 0, tv = 0;                          // tiles issued on each ring
-      if (nv > 0) { issue_k(0); tk = 1; }
-      while (ok && tk < nv) {
-        issue_k(tk);
-        if (!ok) break;
-        ++tk;
-        issue_v(tv);
-        if (ok) ++tv;
+        if (++sv == VSTAGES) { sv = 0; if (t >= VSTAGES) par ^= 1; }
       }
-      while (ok && tv < nv) { issue_v(tv); if (ok) ++tv; }
       if (!ok) {
-        // unwind: give copies in flight a chance to land before shared memory is released
-        mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
-        for (int t = max(0, tk - ATT_KSTAGES); t < tk; ++t)
-          mbar_wait(&k_full[t % ATT_KSTAGES], (t / ATT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
-        for (int t = max(0, tv - ATT_VSTAGES); t < tv; ++t)
-          mbar_wait(&v_full[t % ATT_VSTAGES], (t / ATT_VSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
+        for (int u = max(0, t - VSTAGES); u < t; ++u)
+          mbar_wait(&v_full[u % VSTAGES], (u / VSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
       }
     }
   } else if (warp == 1) {
@@ -575,7 +576,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         // fp16 P overwrites S in place, so Q.K^T of tile t + 2 must stay behind P.V of tile t: one thread issues both,
         // in that order (the tensor pipe executes a thread's instructions in order).
         const uint32_t idesc_pv = idesc_f16(0, 0, ATT_BM, p.D);
-        const uint64_t vd0 = sdesc_kmajor_sw128(smem_u32(sV));      // + stage * (ATT_V_BYTES >> 4)
+        const uint64_t vd0 = sdesc_kmajor_sw128(smem_u32(sV));      // + slot * (VSLOT >> 4)
         const uint32_t v_half16 = (uint32_t)v_half_bytes >> 4;
         constexpr int PW = 128 / NSPLIT;                            // keys per softmax column split
         if (ok && nv > 0) issue_qk(0, vlist[0]);
@@ -591,7 +592,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
           if (!ok) break;
           tc_fence_after();
           const uint32_t ptm = tmem + ATT_COL_S + bsel * 128;
-          const uint64_t vd = vd0 + (uint64_t)(sv * (ATT_V_BYTES >> 4));
+          const uint64_t vd = vd0 + (uint64_t)(sv * (VSLOT >> 4));
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint32_t pcol = ((ks * 16) / PW) * PW + ((ks * 16) % PW) / 2;
@@ -600,7 +601,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
           }
           tc_commit(&v_empty[sv]);
           tc_commit(&pv_done[bsel]);
-          if (++sv == ATT_VSTAGES) { sv = 0; v_par ^= 1; }
+          if (++sv == VSTAGES) { sv = 0; v_par ^= 1; }
           if (t + 2 < nv) issue_qk(t + 2, e2);
         }
       }
@@ -609,7 +610,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     // ------------------------------ P.V issuer (quantised P.V) ----------------
     // O += P(t).V(t) as soon as V has landed and every softmax thread of the tile has stored its part of P.
     if (PVQ && lane == 0) {
-      const uint64_t vd0 = sdesc_kmajor_sw128(smem_u32(sV));        // + stage * (ATT_V_BYTES >> 4)
+      const uint64_t vd0 = sdesc_kmajor_sw128(smem_u32(sV));        // + slot * (VSLOT >> 4)
       const uint64_t v4d0 = sdesc_kmajor_sw64(smem_u32(sV));        // MXFP4 V^T tile (64-byte rows)
       const uint64_t sfp0 = sdesc_sf_tile(smem_u32(sPSF));          // P scale tiles [2], then V scale tiles per stage
       uint32_t idp8[4], idp4[2];                                    // P.V block-scaled: M=128, N=D
@@ -635,19 +636,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         tc_cp_32x128b_warpx4(sfp, sfp0 + (uint64_t)(bsel * (512 >> 4)));
         tc_cp_32x128b_warpx4(sfv, sfp0 + (uint64_t)((2 + sv) * (512 >> 4)));
         if (e & 0x8000) {
-          const uint64_t vd = vd0 + (uint64_t)(sv * (ATT_V_BYTES >> 4));
+          const uint64_t vd = vd0 + (uint64_t)(sv * (VSLOT >> 4));
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)                             // 32 keys per instruction, 8 TMEM columns of P
             mma_mxf8f6f4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp8[ks], sfp, sfv, ks > 0 ? 1u : acc0);
         } else {
-          const uint64_t vd = v4d0 + (uint64_t)(sv * (ATT_V_BYTES >> 4));
+          const uint64_t vd = v4d0 + (uint64_t)(sv * (VSLOT >> 4));
 #pragma unroll
           for (int ks = 0; ks < 2; ++ks)                             // 64 keys per instruction, 8 TMEM columns of P
             mma_mxf4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp4[ks], sfp, sfv, ks > 0 ? 1u : acc0);
         }
         tc_commit(&v_empty[sv]);
         tc_commit(&pv_done[bsel]);
-        if (++sv == ATT_VSTAGES) { sv = 0; v_par ^= 1; }
+        if (++sv == VSTAGES) { sv = 0; v_par ^= 1; }
         e = e_next;
       }
     }
@@ -747,17 +748,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       }
       [[maybe_unused]] float mx = mx0;
       if (lazy_tile) {
-        // Fixed reference: nothing to agree on between the threads of a row.  The whole slice goes to registers and the
-        // S buffer is released at once, so that Q.K^T of the tile after next runs under this tile's arithmetic.
-        uint32_t sl[W];
-#pragma unroll
-        for (int c = 0; c < NCH; ++c) tmem_ld32p(slice_addr + c * 32, sl + c * 32);
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(&s_free[bsel]);
+        // Fixed reference: nothing to agree on between the threads of a row.
+        // 32 columns at a time (few live registers, so the arithmetic of a block interleaves freely); the S buffer is
+        // released as soon as the last block has been read, before its arithmetic.
+        uint32_t sl[32];
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
-          uint32_t* sc = sl + c * 32;
+          uint32_t* sc = sl;
+          tmem_ld32p(slice_addr + c * 32, sl);
+          tmem_ld_wait();
+          if (c == NCH - 1) {
+            tc_fence_before();
+            mbar_arrive(&s_free[bsel]);
+          }
           if (NVF4 && nv_tile) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) sc[i] = __float_as_uint(__uint_as_float(sc[i]) * p.fp4_scale);
