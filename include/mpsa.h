@@ -29,6 +29,13 @@ int mpsa_version(void);
 /* Copies the calling thread's last error message (NUL terminated) into buf[0..n). HOST pointer. */
 int mpsa_last_error(char* buf, unsigned long long n);
 
+/* Self-test of the failure path every kernel here shares.  No counterpart in the reference (its kernels have no waits
+ * of their own).  Launches one thread that waits, with the library's bounded wait, on a barrier that nothing ever
+ * arrives at: after `limit_cycles` SM clock cycles (1 .. 2e9) the wait gives up, writes `code` (1 TMA, 2 tensor-core
+ * commit, 3 pipeline hand-off) into the device word *status if that word is still 0, and the kernel returns normally.
+ * The context stays usable; the host learns of the failure by reading *status, as after any other kernel. */
+int mpsa_selftest_wait_timeout(int* status, long long limit_cycles, int code, void* stream);
+
 /* MX block quantizer, one side (Q or K) per call.
  * Replaces quant_mxfp4 / quant_mxfp8e5 and their Triton kernels (ours/quant_mxint8.py:276-351,
  * :453-512 and :164-272) and the scale relayout (ours/mxfp_attn_kernel.py:56-57).

@@ -296,8 +296,8 @@ __device__ __forceinline__ int block_shift(float d, int emax, float& sh_f) {
   return sh;
 }
 
-// One 32-key block of a query row for the quantised P.V, written word by word (eight MXFP4 or four MXFP8 codes at a
-// time) so that few values are live at once.  Same arithmetic as softmax_block<1..3>.
+// One 32-key block of a query row for the quantised P.V (the fixed-reference kernel's form of softmax_block<1..3>:
+// same arithmetic, no conversion instructions for the block exponent).
 template <int PMODE>
 __device__ __forceinline__ uint32_t softmax_block_q(const uint32_t* sc, float mref, float bmax, uint32_t* pk,
                                                     float& lsum0, float& lsum1) {
@@ -311,21 +311,28 @@ __device__ __forceinline__ uint32_t softmax_block_q(const uint32_t* sc, float mr
   float sh_f;
   const int sh = block_shift(bmax - mref, EMAX, sh_f);
   const float ncb = -(mref + sh_f);               // exact: mref is integral in this mode
-  float a0 = 0.0f, a1 = 0.0f;
+  // Three passes over the block, each of independent instructions (the values are rewritten in place): all
+  // subtractions, then all exponentials back to back - a warp then keeps its share of the exponential unit busy
+  // without waiting for results - then the sums and the packing.
+  float y[32];
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) sub2(y[i], y[i + 1], __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]), ncb);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) y[i] = ex2(y[i]);
+  float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    add2(a0, a1, y[i], y[i + 1]);
+    add2(b0, b1, y[i + 2], y[i + 3]);
+  }
+  a0 += b0;
+  a1 += b1;
 #pragma unroll
   for (int w = 0; w < NW; ++w) {
     constexpr int E = 32 / NW;                    // elements per word
-    float y[E];
-#pragma unroll
-    for (int i = 0; i < E; i += 2) {
-      float x0, x1;
-      sub2(x0, x1, __uint_as_float(sc[w * E + i]), __uint_as_float(sc[w * E + i + 1]), ncb);
-      y[i] = ex2(x0);
-      y[i + 1] = ex2(x1);
-      add2(a0, a1, y[i], y[i + 1]);
-    }
-    if (PMODE == 3) pk[w] = pack_e2m1x8(y[0], y[1], y[2], y[3], y[E > 4 ? 4 : 0], y[E > 4 ? 5 : 1], y[E > 4 ? 6 : 2], y[E > 4 ? 7 : 3]);
-    else pk[w] = pack_fp8x4<PMODE == 2>(y[0], y[1], y[2], y[3]);
+    if (PMODE == 3) pk[w] = pack_e2m1x8(y[w * E], y[w * E + 1], y[w * E + 2], y[w * E + 3], y[w * E + (E > 4 ? 4 : 0)], y[w * E + (E > 4 ? 5 : 1)],
+                                        y[w * E + (E > 4 ? 6 : 2)], y[w * E + (E > 4 ? 7 : 3)]);
+    else pk[w] = pack_fp8x4<PMODE == 2>(y[w * E], y[w * E + 1], y[w * E + 2], y[w * E + 3]);
   }
   const float two_sh = __uint_as_float((uint32_t)(sh + 127) << 23);
   lsum0 = fmaf(a0, two_sh, lsum0);

@@ -65,9 +65,10 @@ constexpr long long kWaitLimitCycles = 4000000000ll;
 // Bounded wait.  Returns false when the limit expired (and records `code` in *status) or when
 // another role already recorded a failure, so that every role unwinds promptly.
 // BACKOFF = false is for pipelines whose phases last a few hundred cycles, where the back-off below would
-// cost more than the wait itself.
+// cost more than the wait itself.  `limit` (SM clock cycles) defaults to kWaitLimitCycles.
 template <bool BACKOFF = true>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
+                                          long long limit = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
 #if MPSA_WAIT_MODE == 0
   // Reading the global nanosecond timer is slow; doing it once after the first unsuccessful probe
@@ -87,7 +88,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
 #endif
     if ((++spins & 0x3ff) == 0) {
       if (*(volatile int*)status != KS_OK) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit) {
         atomicCAS(status, KS_OK, code);
         return false;
       }

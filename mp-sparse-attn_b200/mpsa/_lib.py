@@ -16,6 +16,7 @@ c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlon
 _SIGNATURES = {
     "mpsa_version": ([], c_int),
     "mpsa_last_error": ([ctypes.c_char_p, ctypes.c_ulonglong], c_int),
+    "mpsa_selftest_wait_timeout": ([c_void_p, c_ll, c_int, c_void_p], c_int),
     "mpsa_quant_mx": ([c_void_p, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_float, c_int,
                        c_void_p, c_ll, c_ll, c_ll, c_void_p, c_ll, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_void_p], c_int),

@@ -35,22 +35,34 @@ def _require_cuda(*ts):
 
 
 def status_word(device) -> torch.Tensor:
-    """Per-device int32 word the kernels write when one of their bounded waits expires."""
+    """Per-device int32 word the kernels write when one of their bounded waits expires.  It lives in pinned host memory
+    (reachable from the device under unified addressing: the kernels touch it only after a wait has already failed
+    1024 probes), so the host can look at it before every launch without synchronising."""
     key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
     if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+        _status[key] = torch.zeros(1, dtype=torch.int32).pin_memory()
     return _status[key]
 
 
-def check_status(device=None):
-    """Synchronise and raise if a kernel recorded an expired wait (1 TMA, 2 MMA, 3 pipeline)."""
-    dev = torch.cuda.current_device() if device is None else device
-    w = status_word(dev)
-    code = int(w.item())
+_WAIT_NAMES = {1: "TMA bytes", 2: "tensor-core commit", 3: "pipeline hand-off"}
+
+
+def _raise_if_failed(device):
+    """Raise if a kernel that has already finished on `device` recorded an expired wait.  No synchronisation: called by
+    the wrappers before they launch, so that a failure surfaces at the next call at the latest instead of being carried
+    along silently (a kernel that finds the word set gives up its own long waits too)."""
+    w = status_word(device)
+    code = int(w[0])
     if code != 0:
         w.zero_()
-        raise _lib.MpsaError(f"a kernel gave up waiting (status {code}: "
-                             f"{ {1: 'TMA bytes', 2: 'tensor-core commit', 3: 'pipeline hand-off'}.get(code, '?')})")
+        raise _lib.MpsaError(f"a kernel gave up waiting (status {code}: {_WAIT_NAMES.get(code, '?')})")
+
+
+def check_status(device=None):
+    """Synchronise the device and raise if a kernel recorded an expired wait (1 TMA, 2 MMA, 3 pipeline)."""
+    dev = torch.cuda.current_device() if device is None else device
+    torch.cuda.synchronize(dev)
+    _raise_if_failed(dev)
 
 
 def q_side_scale(head_dim: int, sm_scale: Optional[float] = None) -> float:
@@ -327,6 +339,7 @@ def router_statistic(qq: "QuantizedOperand", kq: "QuantizedOperand", B: int, Hq:
     nq, nk = -(-S // 128), -(-Skv // 128)
     stat = torch.empty((B, Hq, nq, nk), dtype=torch.float32, device=dev)
     scratch = torch.empty((B, Hq, nq, nk, 4), dtype=torch.float32, device=dev)
+    _raise_if_failed(dev)
     status = status_word(dev)
     with torch.cuda.device(dev):
         rc = _lib.load().mpsa_route_stat(qq.fp4.data_ptr(), qq.fp4_sf.data_ptr(), kq.fp4.data_ptr(), kq.fp4_sf.data_ptr(),
@@ -538,6 +551,7 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
         out_dtype, return_lse = torch.float32, True
     out = torch.empty((B, Hq, S, D), dtype=out_dtype, device=dev)
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev) if return_lse else None
+    _raise_if_failed(dev)
     st = status_word(dev)
     # quantised P.V: a per-call word lets the library run the fixed-reference kernel with the exact one as its
     # conditional fallback (same results, see include/mpsa.h)
@@ -705,7 +719,7 @@ def attention_forward_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
     if non_blocking:
         return out, fin
     fin.synchronize()
-    check_status(dev)
+    _raise_if_failed(dev)
     return out
 
 
@@ -728,6 +742,7 @@ def gemm_block_scaled(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b
         b = b.contiguous()
     a_scale, b_scale = a_scale.contiguous(), b_scale.contiguous()
     c = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    _raise_if_failed(a.device)
     st = status_word(a.device)
     with torch.cuda.device(a.device):
         rc = _lib.load().mpsa_gemm_block_scaled(
@@ -765,6 +780,7 @@ def gemm_block_scaled_batched(a: torch.Tensor, a_scale: torch.Tensor, b: torch.T
         if t.numel() * t.element_size() != batch * (-(-rows // 128)) * (K // vec // 4) * 512:
             raise ValueError("scale tiles have the wrong size")
     c = torch.empty((*lead, M, N), dtype=out_dtype, device=a.device)
+    _raise_if_failed(a.device)
     st = status_word(a.device)
     with torch.cuda.device(a.device):
         rc = _lib.load().mpsa_gemm_block_scaled_batched(
