@@ -124,16 +124,20 @@ __device__ __forceinline__ uint32_t cvt_fp8x4_regs(float y0, float y1, float y2,
 // with x1 / x2 the two halves of a row; fp32 products and sum, the result rounded to the input dtype, i.e. the tensor an
 // unfused pipeline would have stored).  A thread then holds a 16-element run of the first half and its partner run of
 // the second half of the same row; D <= 128.
-template <typename T, bool ROPE>
+// W8 / W4: which formats this instance can produce (a caller that wants one format gets a kernel without the other's
+// arithmetic and registers; more CTAs then fit an SM, i.e. more loads in flight).
+template <typename T, bool ROPE, bool W8, bool W4>
 __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantParams p) {
   __shared__ __align__(16) uint8_t sf8[512];
   __shared__ __align__(16) uint8_t sf4[512];
+  __shared__ __align__(16) uint8_t rm8[512];      // row-major scale codes of the tile: [row][k-block & 3]
+  __shared__ __align__(16) uint8_t rm4[512];
   const int tile_l = blockIdx.x, tile_d = blockIdx.y, bh = blockIdx.z;
   const int b = bh / p.H, h = bh % p.H;
   const int row0 = tile_l * 128, col0 = tile_d * 128;
   const int tid = threadIdx.x;
-  const bool want8 = p.fp8_codes || p.fp8_scales_rm || p.fp8_scales_tiled;
-  const bool want4 = p.fp4_codes_unpacked || p.fp4_codes_packed || p.fp4_scales_rm || p.fp4_scales_tiled;
+  const bool want8 = W8 && (p.fp8_codes || p.fp8_scales_rm || p.fp8_scales_tiled);
+  const bool want4 = W4 && (p.fp4_codes_unpacked || p.fp4_codes_packed || p.fp4_scales_rm || p.fp4_scales_tiled);
 
   // padding of the scale tile: rows beyond L and k-blocks beyond D carry E8M0 1.0
   if (tid < 256) {
@@ -239,7 +243,7 @@ __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantPara
       }
       if (writer) {
         sf8[sf_off] = bs.code;
-        if (p.fp8_scales_rm) p.fp8_scales_rm[row_lin * nblk + kb] = bs.code;
+        rm8[rl * 4 + (kb & 3)] = bs.code;
       }
     }
     if (want4) {
@@ -268,7 +272,7 @@ __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantPara
       }
       if (writer) {
         sf4[sf_off] = bs.code;
-        if (p.fp4_scales_rm) p.fp4_scales_rm[row_lin * nblk + kb] = bs.code;
+        rm4[rl * 4 + (kb & 3)] = bs.code;
       }
     }
   }
@@ -283,6 +287,21 @@ __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantPara
     if (p.fp4_scales_tiled && want4)
       reinterpret_cast<uint4*>(p.fp4_scales_tiled + tile_lin * 512)[tid - 32] =
           reinterpret_cast<uint4*>(sf4)[tid - 32];
+  } else if (tid >= 128 && tid < 384) {
+    // row-major scales (the reference's output format): one row of the tile per thread, its up to four codes in one store
+    const bool f8 = tid < 256;
+    const int rl = tid & 127, r = row0 + rl;
+    uint8_t* dst = f8 ? p.fp8_scales_rm : p.fp4_scales_rm;
+    if (dst && (f8 ? want8 : want4) && r < p.L) {
+      const uint8_t* src = (f8 ? rm8 : rm4) + rl * 4;
+      const int kb0 = tile_d * 4, n = min(4, nblk - kb0);
+      uint8_t* o = dst + (((long long)b * p.H + h) * p.L + r) * nblk + kb0;
+      if (n == 4 && (nblk & 3) == 0) {
+        *reinterpret_cast<uint32_t*>(o) = *reinterpret_cast<const uint32_t*>(src);
+      } else {
+        for (int i = 0; i < n; ++i) o[i] = src[i];
+      }
+    }
   }
 }
 
@@ -621,15 +640,25 @@ static int quant_mx_launch(const void* x, int in_dtype, int B, int H, int L, int
   dim3 grid((L + 127) / 128, (D + 127) / 128, B * H);
   if (grid.y > 65535 || grid.z > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "quant_mx: B*H and D/128 must be below 65536");
   cudaStream_t st = (cudaStream_t)stream;
+  const bool w8 = p.fp8_codes || p.fp8_scales_rm || p.fp8_scales_tiled;
+  const bool w4 = p.fp4_codes_unpacked || p.fp4_codes_packed || p.fp4_scales_rm || p.fp4_scales_tiled;
+  if (!w8 && !w4) return set_error(MPSA_ERR_BAD_ARG, "quant_mx: no output requested");
+#define MPSA_QMX(T, ROPE)                                                                       \
+  do {                                                                                          \
+    if (w8 && w4) quant_mx_kernel<T, ROPE, true, true><<<grid, kMxThreads, 0, st>>>(p);         \
+    else if (w8) quant_mx_kernel<T, ROPE, true, false><<<grid, kMxThreads, 0, st>>>(p);         \
+    else quant_mx_kernel<T, ROPE, false, true><<<grid, kMxThreads, 0, st>>>(p);                 \
+  } while (0)
   if (p.rope_cos) {
-    if (in_dtype == 0) quant_mx_kernel<__nv_bfloat16, true><<<grid, kMxThreads, 0, st>>>(p);
-    else if (in_dtype == 1) quant_mx_kernel<__half, true><<<grid, kMxThreads, 0, st>>>(p);
-    else quant_mx_kernel<float, true><<<grid, kMxThreads, 0, st>>>(p);
+    if (in_dtype == 0) MPSA_QMX(__nv_bfloat16, true);
+    else if (in_dtype == 1) MPSA_QMX(__half, true);
+    else MPSA_QMX(float, true);
   } else {
-    if (in_dtype == 0) quant_mx_kernel<__nv_bfloat16, false><<<grid, kMxThreads, 0, st>>>(p);
-    else if (in_dtype == 1) quant_mx_kernel<__half, false><<<grid, kMxThreads, 0, st>>>(p);
-    else quant_mx_kernel<float, false><<<grid, kMxThreads, 0, st>>>(p);
+    if (in_dtype == 0) MPSA_QMX(__nv_bfloat16, false);
+    else if (in_dtype == 1) MPSA_QMX(__half, false);
+    else MPSA_QMX(float, false);
   }
+#undef MPSA_QMX
   return check_launch("quant_mx");
 }
 

@@ -25,6 +25,7 @@ constexpr int RT_OFF_K = RT_OFF_Q + RT_MAXH * RT_Q_BYTES;
 constexpr int RT_OFF_SF = RT_OFF_K + RT_KSTAGES * RT_K_BYTES;       // Q scale tile per head, then K scale tile per stage
 constexpr int RT_OFF_BAR = RT_OFF_SF + (RT_MAXH + RT_KSTAGES) * 512;
 constexpr int RT_SMEM = RT_OFF_BAR + 512 + 1024;
+constexpr int RT_THREADS = 128 + RT_SBUF * 128;                     // 4 service warps + one reducing warpgroup per accumulator
 // TMEM: three S accumulators (128 columns each), then the scale columns: Q per head, K per issuer x 2
 constexpr uint32_t RT_TMEM_COLS = 512, RT_COL_SFQ = 384, RT_COL_SFK = 392;
 
@@ -35,23 +36,18 @@ struct RouteParams {
   int* status;
 };
 
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-  return pred != 0;
-}
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
 
-// Work of a CTA is a stream of units u = key tile * nh + head.  Unit u uses S accumulator u % 3 and is reduced by
-// warpgroup u & 1 (warps 4-7 / 8-11); with two heads per CTA a K tile is fetched once for both, and each head has
-// its own issuing warp.  A unit's chain (wait, tcgen05.mma, commit, wait, tcgen05.ld, maxima, shuffles) is several
-// times longer than its MMAs, hence three accumulators in flight, two issuers and two reducing warpgroups.
-__global__ void __launch_bounds__(384, 1)
+// Work of a CTA is a stream of units u = key tile * nh + head.  Unit u uses S accumulator u % 3, which belongs to
+// reducing warpgroup u % 3 (warps 4-7 / 8-11 / 12-15); with two heads per CTA a K tile is fetched once for both, and
+// each head has its own issuing thread.  A unit's chain (wait, tcgen05.mma, commit, wait, tcgen05.ld, maxima,
+// shuffles) is several times longer than its MMAs (2 x 64 cycles), hence three units in flight.  The issuing loops
+// hold nothing but two waits, the scale copy, the MMAs and the commits.
+__global__ void __launch_bounds__(RT_THREADS, 1)
 route_stat_kernel(const __grid_constant__ CUtensorMap tm_q4, const __grid_constant__ CUtensorMap tm_k4,
                   const RouteParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -60,11 +56,9 @@ route_stat_kernel(const __grid_constant__ CUtensorMap tm_q4, const __grid_consta
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;
   uint64_t* k_empty = k_full + RT_KSTAGES;
-  // One barrier per (reducing warpgroup, accumulator): unit u uses number (u & 1) * 3 + u % 3, phase u / 6, so that
-  // each waiter sees every phase of the barriers it waits on.
-  uint64_t* s_full = k_empty + RT_KSTAGES;       // 2 * RT_SBUF: the unit's MMAs are complete
-  uint64_t* s_free = s_full + 2 * RT_SBUF;       // 2 * RT_SBUF: the four warps of the group have read the accumulator
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2 * RT_SBUF);
+  uint64_t* s_full = k_empty + RT_KSTAGES;       // RT_SBUF: the unit's MMAs are complete
+  uint64_t* s_free = s_full + RT_SBUF;           // RT_SBUF: the four warps of the group have read the accumulator
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + RT_SBUF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.S + RT_BM - 1) / RT_BM, nk = (p.Skv + RT_BN - 1) / RT_BN;
@@ -80,7 +74,7 @@ route_stat_kernel(const __grid_constant__ CUtensorMap tm_q4, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < RT_KSTAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], nh); }
-    for (int s = 0; s < 2 * RT_SBUF; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 4); }
+    for (int s = 0; s < RT_SBUF; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 4); }
     fence_mbar_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, RT_TMEM_COLS);
@@ -101,17 +95,18 @@ route_stat_kernel(const __grid_constant__ CUtensorMap tm_q4, const __grid_consta
         bulk_load(sSF + j * 512, p.q4_sf + ((long long)(b * p.Hq + h0 + j) * nq + qi) * 512, 512, q_full);
       }
       const int k_row0 = (b * p.Hkv + hk) * p.Skv;
-      const long long ksf0 = (long long)(b * p.Hkv + hk) * nk * 512;
+      const uint8_t* ksf = p.k4_sf + (long long)(b * p.Hkv + hk) * nk * 512;
       bool ok = true;
-      int issued = 0;
+      int issued = 0, s = 0;
+      uint32_t par = 0;
       for (int t = 0; t < n_tiles && ok; ++t) {
-        const int s = t % RT_KSTAGES;
-        if (t >= RT_KSTAGES) ok = mbar_wait(&k_empty[s], ((t / RT_KSTAGES) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
+        if (t >= RT_KSTAGES) ok = mbar_wait(&k_empty[s], par, p.status, KS_TIMEOUT_PIPE);
         if (!ok) break;
         mbar_arrive_expect_tx(&k_full[s], RT_K_BYTES + 512);
         tma_load_2d(sK + s * RT_K_BYTES, &tm_k4, &k_full[s], 0, k_row0 + t * RT_BN);
-        bulk_load(sSF + (RT_MAXH + s) * 512, p.k4_sf + ksf0 + (long long)t * 512, 512, &k_full[s]);
+        bulk_load(sSF + (RT_MAXH + s) * 512, ksf + (long long)t * 512, 512, &k_full[s]);
         issued = t + 1;
+        if (++s == RT_KSTAGES) { s = 0; if (t >= RT_KSTAGES) par ^= 1; }
       }
       if (!ok) {                                 // unwind: let the copies in flight land before the CTA exits
         mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
@@ -120,85 +115,96 @@ route_stat_kernel(const __grid_constant__ CUtensorMap tm_q4, const __grid_consta
       }
     }
   } else if (warp == 1 || (warp == 2 && nh == 2)) {
-    // MMA issuer of head j: the whole warp walks the loop, one elected lane issues.
-    const int j = warp - 1;
-    const bool leader = elect_one();
-    const uint32_t id0 = idesc_with_sf_id(idesc_block_scaled(1, 1, RT_BM, RT_BN, 1), 0, 0);
-    const uint32_t id1 = idesc_with_sf_id(idesc_block_scaled(1, 1, RT_BM, RT_BN, 1), 2, 2);
-    const uint64_t qd = sdesc_kmajor_sw64(smem_u32(sQ + j * RT_Q_BYTES));
-    const uint32_t sfq = tmem + RT_COL_SFQ + j * 4;
-    bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA));
-    if (ok) {
-      tc_fence_after();
-      if (leader) tc_cp_32x128b_warpx4(sfq, sdesc_sf_tile(smem_u32(sSF + j * 512)));
-    }
-    for (int t = 0; t < n_tiles && ok; ++t) {
-      const int s = t % RT_KSTAGES;
-      const int u = t * nh + j, bsel = u % RT_SBUF;
-      ok = __all_sync(0xffffffffu, mbar_wait<false>(&k_full[s], (t / RT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA));
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t sfk = tmem + RT_COL_SFK + j * 8 + (t & 1) * 4;
-      const uint64_t ksf = sdesc_sf_tile(smem_u32(sSF + (RT_MAXH + s) * 512));
-      if (leader) tc_cp_32x128b_warpx4(sfk, ksf);
-      const uint64_t kd = sdesc_kmajor_sw64(smem_u32(sK + s * RT_K_BYTES));
-      if (u >= RT_SBUF)                          // the accumulator's previous unit, u - 3, has been read
-        ok = __all_sync(0xffffffffu, mbar_wait<false>(&s_free[((u - 3) & 1) * 3 + bsel], ((u - 3) / 6) & 1, p.status, KS_TIMEOUT_PIPE));
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t d = tmem + bsel * 128;
-      if (leader) {
+    // MMA issuer of head j (one thread)
+    if (lane == 0) {
+      const int j = warp - 1;
+      const uint32_t id0 = idesc_with_sf_id(idesc_block_scaled(1, 1, RT_BM, RT_BN, 1), 0, 0);
+      const uint32_t id1 = idesc_with_sf_id(idesc_block_scaled(1, 1, RT_BM, RT_BN, 1), 2, 2);
+      const uint64_t qd = sdesc_kmajor_sw64(smem_u32(sQ + j * RT_Q_BYTES));
+      const uint64_t kd0 = sdesc_kmajor_sw64(smem_u32(sK));
+      const uint64_t ksf0 = sdesc_sf_tile(smem_u32(sSF + RT_MAXH * 512));
+      const uint32_t sfq = tmem + RT_COL_SFQ + j * 4;
+      bool ok = mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
+      if (ok) {
+        tc_fence_after();
+        tc_cp_32x128b_warpx4(sfq, sdesc_sf_tile(smem_u32(sSF + j * 512)));
+      }
+      int s = 0, u = j;                          // K ring slot of tile t; unit index
+      uint32_t k_par = 0;
+      for (int t = 0; t < n_tiles && ok; ++t, u += nh) {
+        const int cnt = u / RT_SBUF, bsel = u - cnt * RT_SBUF;       // uses of the accumulator before this one
+        ok = mbar_wait<false>(&k_full[s], k_par, p.status, KS_TIMEOUT_TMA);
+        if (ok && cnt > 0) ok = mbar_wait<false>(&s_free[bsel], (uint32_t)(cnt - 1) & 1u, p.status, KS_TIMEOUT_PIPE);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sfk = tmem + RT_COL_SFK + j * 8 + (t & 1) * 4;
+        tc_cp_32x128b_warpx4(sfk, ksf0 + (uint64_t)(s * (512 >> 4)));
+        const uint64_t kd = kd0 + (uint64_t)(s * (RT_K_BYTES >> 4));
+        const uint32_t d = tmem + bsel * 128;
         mma_mxf4(d, qd, kd, id0, sfq, sfk, 0);
         mma_mxf4(d, qd + 2, kd + 2, id1, sfq, sfk, 1);
-        tc_commit(&s_full[(u & 1) * 3 + bsel]);
+        tc_commit(&s_full[bsel]);
         tc_commit(&k_empty[s]);
+        if (++s == RT_KSTAGES) { s = 0; k_par ^= 1; }
       }
     }
   } else if (warp >= 4) {
-    const int q = warp & 3, g = (warp - 4) >> 2;           // TMEM lane quarter, warpgroup
+    const int q = warp & 3, g = (warp - 4) >> 2;           // TMEM lane quarter; warpgroup = accumulator it owns
     const int m_glob = qi * RT_BM + q * 32 + lane;
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
     const float inv_rows = 1.0f / (float)min(RT_BM, p.S - qi * RT_BM);
     const bool row_ok = m_glob < p.S;
     const int lim = p.causal ? min(p.Skv - 1, m_glob + off) : (p.Skv - 1);      // last visible key of this row
     const int lim_all = p.causal ? min(p.Skv - 1, qi * RT_BM + off) : (p.Skv - 1);  // ... of every row of the tile
+    float* part_row = p.part + (((long long)(b * p.Hq + h0) * nq + qi) * nk) * 4 + q;
+    const long long head_stride = (long long)nq * nk * 4;
     bool ok = true;
-    for (int u = g; u < n_units && ok; u += 2) {
-      const int t = u / nh, hh = u - t * nh, bsel = u % RT_SBUF, bar = g * 3 + bsel;
-      ok = __all_sync(0xffffffffu, mbar_wait<false>(&s_full[bar], (u / 6) & 1, p.status, KS_TIMEOUT_MMA));
+    uint32_t par = 0;
+    for (int u = g; u < n_units && ok; u += RT_SBUF, par ^= 1) {
+      const int t = u / nh, hh = u - t * nh;
+      ok = __all_sync(0xffffffffu, mbar_wait<false>(&s_full[g], par, p.status, KS_TIMEOUT_MMA));
       if (!ok) break;
       tc_fence_after();
       const int n0 = t * RT_BN;
-      // the whole row of the tile goes to registers, so that the accumulator is free again before the arithmetic
-      uint32_t r[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tmem + lane_base + bsel * 128 + c * 32, r[c]);
-      tmem_ld_wait();
-      tc_fence_before();
-      if (lane == 0) mbar_arrive(&s_free[bar]);    // count 4: one per warp of the group
+      // the row of the tile goes through registers in two halves of 64 columns; the accumulator is released as soon
+      // as the second half has been read, before its arithmetic
       float m[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) m[i] = -INFINITY;
       // the reference's statistic knows no mask; keys beyond the sequence end (zero padding) and, on
       // the tiles the causal diagonal crosses, keys above the query are left out here
-      if (n0 + RT_BN - 1 <= lim_all) {
+      const bool full_tile = n0 + RT_BN - 1 <= lim_all;
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r[2][32];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2)
-            m[c * 2 + ((i >> 1) & 1)] = max3(m[c * 2 + ((i >> 1) & 1)], __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
-      } else {
+        for (int c = 0; c < 2; ++c) tmem_ld32(tmem + lane_base + g * 128 + (half * 2 + c) * 32, r[c]);
+        tmem_ld_wait();
+        if (half == 1) {
+          tc_fence_before();
+          if (lane == 0) mbar_arrive(&s_free[g]);    // count 4: one per warp of the group
+        }
+        if (full_tile) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (n0 + c * 32 + i <= lim) m[c] = fmaxf(m[c], __uint_as_float(r[c][i]));
+            for (int i = 0; i < 32; i += 2) {
+              const int k = (half * 2 + c) * 2 + ((i >> 1) & 1);
+              m[k] = max3(m[k], __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+            }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (n0 + (half * 2 + c) * 32 + i <= lim) m[half * 2 + c] = fmaxf(m[half * 2 + c], __uint_as_float(r[c][i]));
+        }
       }
       const float mx = fmaxf(fmaxf(max3(m[0], m[1], m[2]), max3(m[3], m[4], m[5])), fmaxf(m[6], m[7]));
       float v = (row_ok && mx != -INFINITY) ? mx * inv_rows : 0.0f;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0) p.part[(((long long)(b * p.Hq + h0 + hh) * nq + qi) * nk + t) * 4 + q] = v;
+      if (lane == 0) part_row[hh * head_stride + (long long)t * 4] = v;
     }
   }
   tc_fence_before();
@@ -274,7 +280,7 @@ extern "C" int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4
   if (cudaMemsetAsync(scratch, 0, cells * 16, (cudaStream_t)stream) != cudaSuccess)
     return set_error(MPSA_ERR_LAUNCH, "route_stat: memset failed");
   dim3 grid(nq, Hq / p.nh, B);
-  route_stat_kernel<<<grid, 384, RT_SMEM, (cudaStream_t)stream>>>(tq, tk, p);
+  route_stat_kernel<<<grid, RT_THREADS, RT_SMEM, (cudaStream_t)stream>>>(tq, tk, p);
   if (int rc = check_launch("route_stat")) return rc;
   route_stat_finish_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const float4*)scratch, (float*)stat, cells);
   return check_launch("route_stat_finish");
