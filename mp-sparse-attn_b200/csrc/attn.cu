@@ -74,6 +74,9 @@ constexpr uint32_t ATT_COL_SFP = 400, ATT_COL_SFV = 408;
 constexpr uint32_t ATT_COL_SFQN = 416, ATT_COL_SFKN = 424;        // NVFP4 scales: Q 8 columns, K 2 x 8
 constexpr uint32_t ATT_COL_P = 448;                              // quantised P: 2 buffers of 32 columns (128 keys x 1 byte)
 constexpr float ATT_RESCALE_LOG2 = 8.0f;
+#ifndef ATT_POLY_PER_BLOCK
+#define ATT_POLY_PER_BLOCK 4                          // of the 32 exponentials of a block (fixed-reference kernel, MXFP4 tiles)
+#endif
 constexpr float ATT_LAZY_HEADROOM = 64.0f;            // log2: P up to 2^64 relative to the fixed reference stays far from fp32 overflow
 
 constexpr int TILE_SKIP = 0, TILE_FP8 = 1, TILE_FP4 = 2;
@@ -287,6 +290,31 @@ __device__ __forceinline__ uint32_t softmax_block(const uint32_t* sc, float mref
   }
 }
 
+// 2^x for a pair of values on the FMA pipe, for the share of the exponentials taken off the special-function unit:
+// x = n + f with n = round(x) (adding 1.5 * 2^23 leaves n in the low mantissa bits), 2^f on [-0.5, 0.5] by a degree-4
+// polynomial (relative error 8e-6, far below half a step of any P format), 2^n by adding n to the exponent field.
+// x is clamped at -125: anything smaller is zero in every P format.
+__device__ __forceinline__ void fma2(float& a, float& b, float c, float d, float e) {   // (a, b) = (a, b) * (c, d) + (e, e)
+  asm("{\n\t.reg .b64 x, y, z;\n\tmov.b64 x, {%0, %1};\n\tmov.b64 y, {%2, %3};\n\tmov.b64 z, {%4, %4};\n\t"
+      "fma.rn.f32x2 x, x, y, z;\n\tmov.b64 {%0, %1}, x;\n\t}"
+      : "+f"(a), "+f"(b) : "f"(c), "f"(d), "f"(e));
+}
+__device__ __forceinline__ void ex2_poly2(float& y0, float& y1, float x0, float x1) {
+  x0 = fmaxf(x0, -125.0f);
+  x1 = fmaxf(x1, -125.0f);
+  float t0, t1, n0, n1;
+  sub2(t0, t1, x0, x1, 12582912.0f);              // t = x + 1.5 * 2^23
+  sub2(n0, n1, t0, t1, -12582912.0f);             // n = round(x), as a float
+  float f0 = x0 - n0, f1 = x1 - n1;
+  float p0 = 0.009278289f, p1 = 0.009278289f;
+  fma2(p0, p1, f0, f1, 0.055865023f);
+  fma2(p0, p1, f0, f1, 0.240308955f);
+  fma2(p0, p1, f0, f1, 0.693129539f);
+  fma2(p0, p1, f0, f1, 0.999997854f);
+  y0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  y1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
 // floor(d) - emax as an integer and as a float, without conversion instructions (which share the exponential's
 // pipe): d + 1.5 * 2^23 rounded DOWN holds floor(d) in its low mantissa bits (|d| < 2^22).
 __device__ __forceinline__ int block_shift(float d, int emax, float& sh_f) {
@@ -317,8 +345,13 @@ __device__ __forceinline__ uint32_t softmax_block_q(const uint32_t* sc, float mr
   float y[32];
 #pragma unroll
   for (int i = 0; i < 32; i += 2) sub2(y[i], y[i + 1], __uint_as_float(sc[i]), __uint_as_float(sc[i + 1]), ncb);
+  // MXFP4 tiles (nearly all of them): a few of the exponentials are computed on the FMA pipe instead (measured
+  // at S=32768: 4 of 32 is the best split; 8 or more lose to the extra instructions)
+  constexpr int NPOLY = (PMODE == 3) ? ATT_POLY_PER_BLOCK : 0;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) y[i] = ex2(y[i]);
+  for (int i = 0; i < 32 - NPOLY; ++i) y[i] = ex2(y[i]);
+#pragma unroll
+  for (int i = 32 - NPOLY; i < 32; i += 2) ex2_poly2(y[i], y[i + 1], y[i], y[i + 1]);
   float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
