@@ -6,8 +6,10 @@ Workload (N=1): causal prefill attention shaped like a Llama-3-8B layer - B=1, H
 D=128, S=32768, bf16 inputs N(0,1) with 5 of the 128 K channels scaled x20, diagonal tiles in
 MXFP8 and the rest in MXFP4 unless the online router promotes them (statistic of the MXFP4 score tile >=
 TAU x that of the row's first key tile), P re-quantised to the tile's format before P.V (V quantised along
-the sequence).  One step = quantise Q and K (both formats, one pass each), quantise V, compute the router
-statistic, build the precision map and run the fused forward.  Metric: effective attention TFLOP/s =
+the sequence).  One step = quantise Q and K (both formats, one pass each), quantise V and run the fused forward
+with the router inside it (band map, first pass that leaves the promoted tiles out, second pass over the promoted
+tiles in MXFP8 merged in place; the exact stand-alone path is launched behind the first pass as its conditional
+fallback).  Metric: effective attention TFLOP/s =
 4*B*Hq*S^2*D/2 / time.  With N > 1 every rank runs the same workload on its own batch element
 (batch x head sharding, no collective; weak scaling) and the value is the sum over ranks divided by
 the slowest rank's time.
@@ -39,8 +41,8 @@ import torch  # noqa: E402
 
 HQ, HKV, D = 32, 8, 128
 OUTLIERS = 5
-LAUNCHES_PER_STEP = 8      # quant Q, quant K, quant V, router statistic + its finish kernel, precision map, fused forward
-                           # + the exact kernel behind it as conditional fallback (its CTAs return at once)
+LAUNCHES_PER_STEP = 10     # quant Q, quant K, quant V, band map, first pass, second pass + the conditional fallback behind the
+                           # first pass (router statistic + its finish kernel, precision map, exact forward: they return at once)
 TAU = 1.1                  # online router: a tile is promoted to MXFP8 iff its statistic >= TAU x the first key tile's
 # DRAM bytes (read + written) of one launch of the fused forward at S=8192, from an ncu capture; every term of it
 # (Q, K, V codes and scales, the output) grows linearly with S
@@ -202,7 +204,14 @@ def run_ours(args):
         return a0.elapsed_time(a1) / K
 
     vt = mpsa.quantize_v_seq(v)
-    attn_ms = time_forward(vt)
+    plain_ms = time_forward(vt)                  # one launch over the final map (no router inside)
+    # the dominant kernel of the step: the first pass of the routed forward (router inside; the band-map launch before it
+    # takes a few microseconds and is inside the bracket), and the whole routed forward
+    attn_ms = timed(lambda: mpsa.attention_forward_routed(qq, kq, vt, 1, HQ, HKV, S, S, D, band=1, tau=TAU, stages=3))
+    routed_ms = timed(lambda: mpsa.attention_forward_routed(qq, kq, vt, 1, HQ, HKV, S, S, D, band=1, tau=TAU))
+    band = mpsa.precision_map_band(S, S, True, 1, 128, dev)
+    n_band = int((band == mpsa.TILE_FP8).sum()) * HQ
+    n_promoted = n_fp8 - n_band
     vt = mpsa.prepare_vt(v)
     attn_fp16_ms = time_forward(vt)              # the reference's P.V precision (P and V in fp16)
     # quantizer alone (Q operand, both formats): HBM-bound leg
@@ -258,11 +267,13 @@ def run_ours(args):
     pk = measured_peaks()
     # blended tensor peak: both products of a diagonal tile at the MXFP8 rate (2x the measured bf16
     # rate), both products of an off-diagonal tile at the MXFP4 rate (4x)
+    # work the first pass executes: both products of the band tiles (MXFP8 rate) and of the MXFP4 tiles it keeps
+    # (MXFP4 rate), and the score product alone of the tiles it leaves to the second pass (MXFP4 rate)
     f_tile = 2.0 * 128 * 128 * D
-    executed = (n_fp8 + n_fp4) * 2 * f_tile
+    executed = (n_band + n_fp4) * 2 * f_tile + n_promoted * f_tile
 
     def blended(base_tflops):
-        t_peak = n_fp8 * 2 * f_tile / (2 * base_tflops * 1e12) + n_fp4 * 2 * f_tile / (4 * base_tflops * 1e12)
+        t_peak = n_band * 2 * f_tile / (2 * base_tflops * 1e12) + (n_fp4 * 2 + n_promoted) * f_tile / (4 * base_tflops * 1e12)
         return executed / t_peak / 1e12
     # the forward is timed alone, back to back: the burst figure is its denominator; the sustained one is given beside it
     peak_tflops, peak_sustained = blended(pk["bf16"]), blended(pk["bf16_sustained"])
@@ -273,14 +284,17 @@ def run_ours(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8/mxfp4 (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": f"cfg3 causal prefill B=1 Hq=32 Hkv=8 D=128 S={S} per GPU, diag MXFP8 / off-diag MXFP4 with online "
                                f"promotion to MXFP8 (tau={TAU}), P re-quantised to the tile's format before P.V", "seq_len": S,
-                   "router": {"kind": "online", "tau": TAU, "fp8_tiles": n_fp8, "fp4_tiles": n_fp4, "ms": round(route_ms, 4)}, "l2": "inputs (403 MB per step) larger than L2",
+                   "router": {"kind": "online, inside the forward", "tau": TAU, "fp8_tiles": n_fp8, "fp4_tiles": n_fp4,
+                              "stand_alone_statistic_pass_ms": round(route_ms, 4)}, "l2": "inputs (403 MB per step) larger than L2",
                    "sharding": "batch x head replicas, no collective"},
-        "roofline": {"bound": "tensor", "kernel": "attn_fwd_kernel", "achieved": round(achieved, 2),
+        "roofline": {"bound": "tensor", "kernel": "attn_fwd_kernel (first pass of the routed forward, router inside)", "achieved": round(achieved, 2),
                      "peak": round(peak_tflops, 1), "unit": "TFLOP/s", "frac": round(achieved / peak_tflops, 4),
                      "traffic": ATTN_TRAFFIC_BYTES_S8192 * S // 8192, "ms": round(attn_ms, 4),
                      "peak_source": pk["source"] + " bf16 burst x2 (MXFP8 tiles) / x4 (MXFP4 tiles), blended by executed tiles",
                      "frac_of_sustained_peak": round(achieved / peak_sustained, 4), "peak_sustained": round(peak_sustained, 1),
-                     "effective_tflops": round(flops_rank / (attn_ms * 1e-3) / 1e12, 2),
+                     "routed_forward_ms": round(routed_ms, 4), "promoted_tiles": n_promoted,
+                     "single_launch_over_final_map_ms": round(plain_ms, 4),
+                     "effective_tflops": round(flops_rank / (routed_ms * 1e-3) / 1e12, 2),
                      "fp16_pv_variant": {"ms": round(attn_fp16_ms, 4), "effective_tflops": round(flops_rank / (attn_fp16_ms * 1e-3) / 1e12, 2)},
                      "quantizer": {"bound": "hbm", "achieved": round(HQ * S * D * (2 + 1 + 0.5 + 2 / 32) / (quant_ms * 1e-3) / 1e9, 1),
                                    "peak": pk["hbm_gbs"], "unit": "GB/s", "ms": round(quant_ms, 4)}},

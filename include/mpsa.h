@@ -198,6 +198,27 @@ int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void*
                   float fp4_scale, int* range_flag,
                   const void* acc_in, const void* lse_in, int* status, void* stream);
 
+/* The fused forward with the online router inside it: what mpsa_route_stat + mpsa_route_online + mpsa_attn_fwd do together
+ * for a causal problem with quantised P.V and MXFP4 operands, without the stand-alone statistic pass.  Replaces the same
+ * reference code as mpsa_attn_fwd, with the tile router of ours/mxfp_attn_kernel.py:272-297 deciding precision.
+ *   map           uint8 [B,Hq,nq,nk], OUTPUT: the precision map used (as mpsa_route_online with this band and tau writes it)
+ *   band, tau     MXFP8 within `band` tiles of the diagonal; elsewhere MXFP8 iff statistic >= tau x the row's first tile's
+ *   out           [B,Hq,S,D] of out_dtype;  lse fp32 [B,Hq,S] (work buffer: the first pass's log2 denominators)
+ *   lse_final     optional fp32 [B,Hq,S], another buffer than lse: log2 denominators of the final result
+ *   stat          fp32 [B,Hq,nq,nk] and stat_scratch fp32 [B,Hq,nq,nk,4]: used only when the fallback below runs
+ *   range_flag    device int, zero on entry.  The first pass runs with the row reference fixed after the first key tile; if
+ *                 a score leaves its 2^64 headroom the word is set and the exact path (statistic kernel, map, exact
+ *                 forward) runs behind it instead - same results either way.
+ * Three launches in the common case: band map, first pass (tiles to promote are left out and marked), second pass over
+ * the marked tiles in MXFP8 merged into `out` in place.  Skv_pad, fp8_fmt, the operand pointers: as in mpsa_attn_fwd.
+ *   stages        which of these to launch, a mask of 1 (band map), 2 (first pass), 4 (fallback), 8 (second pass); 15 for
+ *                 the operation itself, a subset for timing one stage alone (the output is then incomplete). */
+int mpsa_attn_fwd_routed(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
+                         const void* k8_sf, const void* k4, const void* k4_sf, const void* vt8, const void* v8_sf,
+                         const void* vt4, const void* v4_sf, void* map, int band, float tau, void* out, int out_dtype,
+                         void* lse, void* lse_final, void* stat, void* stat_scratch, int B, int Hq, int Hkv, int S, int Skv,
+                         int D, int Skv_pad, int fp8_fmt, int stages, int* range_flag, int* status, void* stream);
+
 /* Merges a partial attention result into an accumulator: acc fp32 [rows, D] and lse_acc fp32 [rows] are
  * updated in place with part [rows, D] (part_dtype 0 f32, 1 f16, 2 bf16) and lse_part, where every lse is
  * log2 of the softmax denominator of its (disjoint) key set as written by mpsa_attn_fwd; rows with

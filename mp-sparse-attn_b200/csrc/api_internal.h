@@ -14,4 +14,9 @@
 namespace mpsa {
 int set_error(int code, const char* fmt, ...);
 int check_launch(const char* what);
+// launchers shared between translation units; run_if: a device word, the kernels do nothing while it is zero (may be null)
+int launch_route_stat(const void* q4, const void* q4_sf, const void* k4, const void* k4_sf, void* stat, void* scratch, int B,
+                      int Hq, int Hkv, int S, int Skv, int causal, int* status, const int* run_if, void* stream);
+int launch_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv, int causal, int band, float tau,
+                        float skip_tau, int use_skip, const int* run_if, void* stream);
 }  // namespace mpsa

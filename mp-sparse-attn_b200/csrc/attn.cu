@@ -58,12 +58,13 @@ constexpr int ATT_OFF_V = ATT_OFF_K + ATT_KSTAGES * ATT_K_BYTES;
 constexpr int ATT_OFF_SF = ATT_OFF_V + 2 * ATT_V_BYTES;   // scale tiles: Q8 (512 B), Q4 (1024), K[stages] (1024 each;
                                                                     // an NVFP4 operand has two 128x4 tiles per 128 rows)
 constexpr int ATT_MAX_SPLIT = 4, ATT_MAX_WG = 2;
-constexpr int ATT_SERVICE_THREADS = 128;              // warp 0 Q/K loads, warp 1 Q.K^T issuer, warp 2 P.V issuer, warp 3 V loads
+constexpr int ATT_SERVICE_THREADS = 128;              // warp 0 TMA loads, warp 1 Q.K^T issuer, warp 2 P.V issuer, warp 3 router
 constexpr int ATT_OFF_PSF = ATT_OFF_SF + (3 + 2 * ATT_KSTAGES) * 512;    // P scale tiles [2], V scale tiles [VSTAGES]
 constexpr int ATT_OFF_XMAX = ATT_OFF_PSF + (2 + ATT_VSLOTS_MAX) * 512;   // float [WG][2][SPLIT][128] partial row maxima
 constexpr int ATT_OFF_XSUM = ATT_OFF_XMAX + ATT_MAX_WG * 2 * ATT_MAX_SPLIT * 128 * 4;   // float [WG*SPLIT][128] partial sums
 constexpr int ATT_OFF_MROW = ATT_OFF_XSUM + ATT_MAX_WG * ATT_MAX_SPLIT * 128 * 4;       // float [3][128] running row max: per tile parity, and an unsynchronised hint
-constexpr int ATT_OFF_BAR = ATT_OFF_MROW + 3 * 128 * 4;
+constexpr int ATT_OFF_RMAX = ATT_OFF_MROW + 3 * 128 * 4;               // float [2 buffers][MAX_SPLIT][128]: slice maxima for the router
+constexpr int ATT_OFF_BAR = ATT_OFF_RMAX + 2 * ATT_MAX_SPLIT * 128 * 4;
 constexpr int ATT_OFF_MAP = ATT_OFF_BAR + 512;                        // this CTA's row of the precision map
 constexpr int ATT_MAP_SMEM = 8192;                                    // longest row: 8192 key tiles (1M keys)
 constexpr int ATT_OFF_VLIST = ATT_OFF_MAP + ATT_MAP_SMEM;             // uint16 per visited tile
@@ -80,6 +81,7 @@ constexpr float ATT_RESCALE_LOG2 = 8.0f;
 constexpr float ATT_LAZY_HEADROOM = 64.0f;            // log2: P up to 2^64 relative to the fixed reference stays far from fp32 overflow
 
 constexpr int TILE_SKIP = 0, TILE_FP8 = 1, TILE_FP4 = 2;
+constexpr int TILE_AGAIN = 3;                         // between the two passes of a routed forward: MXFP8, not done yet
 
 struct AttnParams {
   int B, Hq, Hkv, S, Skv, D;        // D = value head dim (64 or 128); Q/K depth is padded to 128
@@ -94,8 +96,17 @@ struct AttnParams {
   const uint8_t* map; long long map_sb, map_sh; // [.., nq, nk], strides may be 0 (broadcast)
   void* out; int out_dtype;          // [B,Hq,S,D] contiguous; 0 f32, 1 f16, 2 bf16
   float* lse;                        // optional [B,Hq,S]: log2 of the softmax denominator (incl. the row reference)
-  const float* acc_in;               // optional [B,Hq,S,D] fp32 + lse_in [B,Hq,S]: an earlier partial result over OTHER keys;
-  const float* lse_in;               // the kernel then writes the merged result (out must be fp32, lse is required)
+  const void* acc_in;                // optional [B,Hq,S,D] (acc_dtype) + lse_in [B,Hq,S]: an earlier partial result over OTHER keys;
+  const float* lse_in;               // the kernel then writes the merged result (lse is required); may alias out / lse: each
+  int acc_dtype;                     // thread reads its own elements before it writes them.  acc_dtype: 0 f32, 1 f16, 2 bf16
+  // router inside the forward (ROUTE kernels): an MXFP4 tile whose statistic reaches tau x that of the row's first key
+  // tile is left OUT of this pass and marked TILE_AGAIN in map_rw; a second pass (map_mode 1) visits exactly the marked
+  // cells in MXFP8, rewrites them to TILE_FP8 and merges with this pass's result.
+  float tau;
+  uint8_t* map_rw;                   // the map again, writable (same buffer and strides as `map`)
+  float* stat_out;                   // optional [B,Hq,nq,nk]: the statistic of every MXFP4 tile visited
+  int map_mode;                      // 0: visit every non-skipped cell; 1: second pass (see above)
+  const int* skip_if;                // when given: the kernel does nothing if this word is non-zero
   int* range_flag;                   // LAZY kernels: set to 1 when a score leaves the fixed reference's headroom
   const int* run_if;                 // when given: the kernel does nothing unless this word is non-zero
   int* status;
@@ -315,6 +326,24 @@ __device__ __forceinline__ void ex2_poly2(float& y0, float& y1, float x0, float 
   y1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
 }
 
+// Bounded wait for a tagged word in shared memory: returns the word once its tag (bits 1..) equals `tag`, or -1 after
+// the limit (status set) or when another role has already recorded a failure.  The status word and the clock are looked
+// at every 1024 probes only.
+__device__ __forceinline__ int poll_tag(volatile int* word, int tag, int* status) {
+  int w = *word;
+  if ((w >> 1) == tag) return w;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    w = *word;
+    if ((w >> 1) == tag) return w;
+    if ((++spins & 0x3ff) == 0) {
+      if (*(volatile int*)status != KS_OK) return -1;
+      if (clock64() - t0 > kWaitLimitCycles) { atomicCAS(status, KS_OK, KS_TIMEOUT_PIPE); return -1; }
+    }
+  }
+}
+
 // floor(d) - emax as an integer and as a float, without conversion instructions (which share the exponential's
 // pipe): d + 1.5 * 2^23 rounded DOWN holds floor(d) in its low mantissa bits (|d| < 2^22).
 __device__ __forceinline__ int block_shift(float d, int emax, float& sh_f) {
@@ -382,7 +411,12 @@ __device__ __forceinline__ uint32_t softmax_block_q(const uint32_t* sc, float mr
 // warpgroups, a second look at S or a rescale of O, and S is released as soon as it has been read.  A score beyond
 // the headroom sets *range_flag; the launcher then re-runs the exact kernel, which is launched behind this one with
 // run_if = range_flag.
-template <int NWG, int NSPLIT, int PVQ, int NVF4, int LAZY>
+// ROUTE (fixed-reference kernel, two warpgroups, MXFP4 operands): the online router runs inside the forward.  The
+// softmax threads publish the maximum of their slice of every MXFP4 tile; the P.V-issuing warp reduces them to the
+// tile's statistic - mean over the query rows of the row maximum, in the very order of the stand-alone statistic
+// kernel, so the two agree bit for bit - compares it with tau x the statistic of the row's first key tile and either
+// issues P.V or leaves the tile out and marks it for the second pass.
+template <int NWG, int NSPLIT, int PVQ, int NVF4, int LAZY, int ROUTE = 0>
 __global__ void __launch_bounds__(ATT_SERVICE_THREADS + 128 * NWG * NSPLIT, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant__ CUtensorMap tm_q4,
                 const __grid_constant__ CUtensorMap tm_k8, const __grid_constant__ CUtensorMap tm_k4,
@@ -390,6 +424,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
                 const __grid_constant__ CUtensorMap tm_vt4, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   if (p.run_if && *(volatile const int*)p.run_if == 0) return;     // conditional re-run: nothing to do
+  if (p.skip_if && *(volatile const int*)p.skip_if != 0) return;   // second pass of a forward whose first pass was redone
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024 - (raw & 1023)) & 1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_OFF_BAR);
@@ -405,8 +440,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   uint64_t* m_bar = x_bar + ATT_MAX_WG * 8;        // [2][4] running-max hand-over, per tile parity and row quarter
   uint64_t* l_bar = m_bar + 8;                     // [4] partial-sum exchange in the epilogue
   uint64_t* s_free = l_bar + 4;                    // 2: quantised P.V only - every softmax thread is done with the S buffer
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
+  uint64_t* st_bar = s_free + 2;                   // 2: ROUTE - the owners of the tile have published their slice maxima
+  uint64_t* dec_bar = st_bar + 2;                  // 2: unused
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dec_bar + 2);
   int* n_visit = reinterpret_cast<int*>(tmem_slot + 1);
+  volatile int* dec = n_visit + 1;                 // [4], slot tile & 3: (tile << 1 | keep) once the router has decided on the tile
   float* xmax = reinterpret_cast<float*>(smem + ATT_OFF_XMAX);
   float* xsum = reinterpret_cast<float*>(smem + ATT_OFF_XSUM);
   float* mrow = reinterpret_cast<float*>(smem + ATT_OFF_MROW);
@@ -422,6 +460,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   const uint8_t* map_glob = p.map + (long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk;
   for (int i = threadIdx.x; i < nk; i += blockDim.x) smem[ATT_OFF_MAP + i] = map_glob[i];     // nk <= ATT_MAP_SMEM (host check)
   if (threadIdx.x < 128) reinterpret_cast<float*>(smem + ATT_OFF_MROW)[2 * 128 + threadIdx.x] = -INFINITY;   // reference hint
+  if (threadIdx.x < 4) dec[threadIdx.x] = -1;       // no tile decided yet
   const int off = p.Skv - p.S;                      // queries are aligned to the end of the keys
 
   if (threadIdx.x == 0) {
@@ -429,6 +468,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     for (int s = 0; s < ATT_KSTAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
     for (int s = 0; s < ATT_VSLOTS_MAX; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], 128 * NSPLIT); mbar_init(&pv_done[s], 1); mbar_init(&s_free[s], 128 * NSPLIT); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&st_bar[s], 128 * NSPLIT); mbar_init(&dec_bar[s], 1); }
     for (int s = 0; s < ATT_MAX_WG * 8; ++s) mbar_init(&x_bar[s], NSPLIT);
     for (int s = 0; s < 8; ++s) mbar_init(&m_bar[s], NSPLIT);
     for (int s = 0; s < 4; ++s) mbar_init(&l_bar[s], NSPLIT * NWG);
@@ -443,8 +483,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     for (int i0 = 0; i0 < nk; i0 += 32) {
       const int i = i0 + lane;
       const uint8_t c = i < nk ? smem[ATT_OFF_MAP + i] : (uint8_t)TILE_SKIP;
-      const uint32_t vis = __ballot_sync(0xffffffffu, c != TILE_SKIP);
-      if (c != TILE_SKIP) vl[base + __popc(vis & ((1u << lane) - 1u))] = (uint16_t)(i | (c == TILE_FP8 ? 0x8000 : 0));
+      const bool visit = p.map_mode == 1 ? (c == TILE_AGAIN) : (c != TILE_SKIP);
+      const uint32_t vis = __ballot_sync(0xffffffffu, visit);
+      if (visit) {
+        vl[base + __popc(vis & ((1u << lane) - 1u))] = (uint16_t)(i | ((c == TILE_FP8 || c == TILE_AGAIN) ? 0x8000 : 0));
+        if (p.map_mode == 1) p.map_rw[(long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk + i] = TILE_FP8;
+      }
       base += __popc(vis);
     }
     if (lane == 0) *n_visit = base;
@@ -454,6 +498,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const int nv = *n_visit;                          // number of tiles to visit (0: the row has none)
+  const bool idle = p.map_mode == 1 && nv == 0;     // second pass, nothing marked in this row: the first pass's result stands
 
   uint8_t* sQ8 = smem + ATT_OFF_Q8;
   uint8_t* sQ4 = smem + ATT_OFF_Q4;
@@ -466,8 +511,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   constexpr int VSTAGES = PVQ ? 4 : 2;              // V ring depth, and the bytes of one slot
   constexpr int VSLOT = PVQ ? ATT_V_BYTES / 2 : ATT_V_BYTES;
 
-  if (warp == 0) {
-    // ------------------------------ Q and K loads ------------------------------
+  if (idle) {
+    // nothing to do but to carry the first pass's log-denominators over when the caller wants them in another buffer
+    if (p.lse && p.lse_in && threadIdx.x < ATT_BM && qi * ATT_BM + (int)threadIdx.x < p.S) {
+      const long long r = (long long)(b * p.Hq + h) * p.S + qi * ATT_BM + threadIdx.x;
+      p.lse[r] = p.lse_in[r];
+    }
+  } else if (warp == 0) {
+    // ------------------------------ Q, K and V loads ---------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_q4); tma_prefetch_desc(&tm_k8); tma_prefetch_desc(&tm_k4);
       const int q_row = (b * p.Hq + h) * p.S + qi * ATT_BM;
@@ -481,42 +532,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       const int k_row0 = (b * p.Hkv + hk) * p.Skv;
       const uint8_t* k8sf = p.k8_sf + (long long)(b * p.Hkv + hk) * nk * 512;
       const uint8_t* k4sf = p.k4_sf + (long long)(b * p.Hkv + hk) * nk * SF4;
-      bool ok = true;
-      int sk = 0, t = 0;                           // ring slot of tile t
-      uint32_t par = 0;                            // parity of the `empty` phase to wait for
-      for (; t < nv && ok; ++t) {
-        const uint32_t e = vlist[t];
-        const int j = e & 0x7fff;
-        const bool f8 = (e & 0x8000) != 0;
-        if (t >= ATT_KSTAGES) ok = mbar_wait(&k_empty[sk], par, p.status, KS_TIMEOUT_PIPE);
-        if (!ok) break;
-        mbar_arrive_expect_tx(&k_full[sk], (f8 ? ATT_K_BYTES + 512 : ATT_K_BYTES / 2 + SF4));
-        tma_load_2d(sK + sk * ATT_K_BYTES, f8 ? &tm_k8 : &tm_k4, &k_full[sk], 0, k_row0 + j * ATT_BN);
-        if (f8) bulk_load(sSF + (3 + 2 * sk) * 512, k8sf + (long long)j * 512, 512, &k_full[sk]);
-        else bulk_load(sSF + (3 + 2 * sk) * 512, k4sf + (long long)j * SF4, SF4, &k_full[sk]);
-        if (++sk == ATT_KSTAGES) { sk = 0; if (t >= ATT_KSTAGES) par ^= 1; }
-      }
-      if (!ok) {
-        // unwind: give copies in flight a chance to land before shared memory is released
-        mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
-        for (int u = max(0, t - ATT_KSTAGES); u < t; ++u)
-          mbar_wait(&k_full[u % ATT_KSTAGES], (u / ATT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
-      }
-    }
-  } else if (warp == 3) {
-    // ------------------------------ V loads ------------------------------------
-    if (lane == 0) {
       tma_prefetch_desc(&tm_vt); tma_prefetch_desc(&tm_vt8); tma_prefetch_desc(&tm_vt4);
       const long long vsf0 = (long long)(b * p.Hkv + hk) * p.v_tiles * 512;
       const int v_row = (b * p.Hkv + hk) * p.D;
       bool ok = true;
-      int sv = 0, t = 0;
-      uint32_t par = 0;
-      for (; t < nv && ok; ++t) {
+      int sk = 0, sv = 0;                          // ring slots, and the parity of the `empty` phase to wait for
+      uint32_t pk_par = 0, pv_par = 0;
+      auto issue_k = [&](int t) {
         const uint32_t e = vlist[t];
         const int j = e & 0x7fff;
-        if (t >= VSTAGES) ok = mbar_wait(&v_empty[sv], par, p.status, KS_TIMEOUT_PIPE);
-        if (!ok) break;
+        const bool f8 = (e & 0x8000) != 0;
+        if (t >= ATT_KSTAGES) ok = mbar_wait(&k_empty[sk], pk_par, p.status, KS_TIMEOUT_PIPE);
+        if (!ok) return;
+        mbar_arrive_expect_tx(&k_full[sk], (f8 ? ATT_K_BYTES + 512 : ATT_K_BYTES / 2 + SF4));
+        tma_load_2d(sK + sk * ATT_K_BYTES, f8 ? &tm_k8 : &tm_k4, &k_full[sk], 0, k_row0 + j * ATT_BN);
+        if (f8) bulk_load(sSF + (3 + 2 * sk) * 512, k8sf + (long long)j * 512, 512, &k_full[sk]);
+        else bulk_load(sSF + (3 + 2 * sk) * 512, k4sf + (long long)j * SF4, SF4, &k_full[sk]);
+        if (++sk == ATT_KSTAGES) { sk = 0; if (t >= ATT_KSTAGES) pk_par ^= 1; }
+      };
+      auto issue_v = [&](int t) {
+        const uint32_t e = vlist[t];
+        const int j = e & 0x7fff;
+        if (t >= VSTAGES) ok = mbar_wait(&v_empty[sv], pv_par, p.status, KS_TIMEOUT_PIPE);
+        if (!ok) return;
         if (PVQ == 0) {
           mbar_arrive_expect_tx(&v_full[sv], 2 * v_half_bytes);
           tma_load_2d(sV + sv * VSLOT, &tm_vt, &v_full[sv], j * ATT_BN, v_row);
@@ -528,10 +566,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
           tma_load_2d(sV + sv * VSLOT, f8 ? &tm_vt8 : &tm_vt4, &v_full[sv], f8 ? j * ATT_BN : j * (ATT_BN / 2), v_row);
           bulk_load(sPSF + (2 + sv) * 512, (f8 ? p.v8_sf : p.v4_sf) + vsf0 + (long long)j * 512, 512, &v_full[sv]);
         }
-        if (++sv == VSTAGES) { sv = 0; if (t >= VSTAGES) par ^= 1; }
+        if (++sv == VSTAGES) { sv = 0; if (t >= VSTAGES) pv_par ^= 1; }
+      };
+      // consumption order: K0, K1, (V0, K2), (V1, K3), ...; with rings this deep neither wait below holds the other
+      // ring up for long
+      int tk = 0, tv = 0;                          // tiles issued on each ring
+      if (nv > 0) { issue_k(0); tk = 1; }
+      while (ok && tk < nv) {
+        issue_k(tk);
+        if (!ok) break;
+        ++tk;
+        issue_v(tv);
+        if (ok) ++tv;
       }
+      while (ok && tv < nv) { issue_v(tv); if (ok) ++tv; }
       if (!ok) {
-        for (int u = max(0, t - VSTAGES); u < t; ++u)
+        // unwind: give copies in flight a chance to land before shared memory is released
+        mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
+        for (int u = max(0, tk - ATT_KSTAGES); u < tk; ++u)
+          mbar_wait(&k_full[u % ATT_KSTAGES], (u / ATT_KSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
+        for (int u = max(0, tv - VSTAGES); u < tv; ++u)
           mbar_wait(&v_full[u % VSTAGES], (u / VSTAGES) & 1, p.status, KS_TIMEOUT_TMA);
       }
     }
@@ -648,7 +702,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     }
   } else if (warp == 2) {
     // ------------------------------ P.V issuer (quantised P.V) ----------------
-    // O += P(t).V(t) as soon as V has landed and every softmax thread of the tile has stored its part of P.
+    // O += P(t).V(t) as soon as V has landed and every softmax thread of the tile has stored its part of P.  ROUTE: an
+    // MXFP4 tile the router leaves out gets no MMA (the commits still go out: the loader and the softmax carry on).
     if (PVQ && lane == 0) {
       const uint64_t vd0 = sdesc_kmajor_sw128(smem_u32(sV));        // + slot * (VSLOT >> 4)
       const uint64_t v4d0 = sdesc_kmajor_sw64(smem_u32(sV));        // MXFP4 V^T tile (64-byte rows)
@@ -661,36 +716,88 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       bool ok = true;
       int sv = 0;
       uint32_t v_par = 0, r_par = 0;                // phase parities: v_full[sv]; p_ready[t & 1]
+      uint32_t acc_any = 0;                         // 1 once an MMA has written O
       uint32_t e = nv > 0 ? vlist[0] : 0;
       for (int t = 0; t < nv && ok; ++t) {
         const uint32_t e_next = t + 1 < nv ? vlist[t + 1] : 0;
         const int bsel = t & 1;
+        bool keep = true;
         ok = mbar_wait(&v_full[sv], v_par, p.status, KS_TIMEOUT_TMA);
+        if (ROUTE && ok && !(e & 0x8000)) {
+          // the router's word for this tile (it was written while P was being stored, as a rule)
+          const int w = poll_tag(&dec[t & 3], t, p.status);
+          if (w < 0) ok = false;
+          keep = (w & 1) != 0;
+        }
         if (ok) ok = mbar_wait(&p_ready[bsel], r_par, p.status, KS_TIMEOUT_PIPE);
         if (bsel) r_par ^= 1;
         if (!ok) break;
-        tc_fence_after();
-        const uint32_t acc0 = t > 0 ? 1u : 0u;
-        const uint32_t ptm = tmem + ATT_COL_P + bsel * 32;          // quantised P has its own columns
-        const uint32_t sfp = tmem + ATT_COL_SFP + bsel * 4, sfv = tmem + ATT_COL_SFV + bsel * 4;
-        tc_cp_32x128b_warpx4(sfp, sfp0 + (uint64_t)(bsel * (512 >> 4)));
-        tc_cp_32x128b_warpx4(sfv, sfp0 + (uint64_t)((2 + sv) * (512 >> 4)));
-        if (e & 0x8000) {
-          const uint64_t vd = vd0 + (uint64_t)(sv * (VSLOT >> 4));
+        if (keep) {
+          tc_fence_after();
+          const uint32_t ptm = tmem + ATT_COL_P + bsel * 32;          // quantised P has its own columns
+          const uint32_t sfp = tmem + ATT_COL_SFP + bsel * 4, sfv = tmem + ATT_COL_SFV + bsel * 4;
+          tc_cp_32x128b_warpx4(sfp, sfp0 + (uint64_t)(bsel * (512 >> 4)));
+          tc_cp_32x128b_warpx4(sfv, sfp0 + (uint64_t)((2 + sv) * (512 >> 4)));
+          if (e & 0x8000) {
+            const uint64_t vd = vd0 + (uint64_t)(sv * (VSLOT >> 4));
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)                             // 32 keys per instruction, 8 TMEM columns of P
-            mma_mxf8f6f4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp8[ks], sfp, sfv, ks > 0 ? 1u : acc0);
-        } else {
-          const uint64_t vd = v4d0 + (uint64_t)(sv * (VSLOT >> 4));
+            for (int ks = 0; ks < 4; ++ks)                             // 32 keys per instruction, 8 TMEM columns of P
+              mma_mxf8f6f4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp8[ks], sfp, sfv, ks > 0 ? 1u : acc_any);
+          } else {
+            const uint64_t vd = v4d0 + (uint64_t)(sv * (VSLOT >> 4));
 #pragma unroll
-          for (int ks = 0; ks < 2; ++ks)                             // 64 keys per instruction, 8 TMEM columns of P
-            mma_mxf4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp4[ks], sfp, sfv, ks > 0 ? 1u : acc0);
+            for (int ks = 0; ks < 2; ++ks)                             // 64 keys per instruction, 8 TMEM columns of P
+              mma_mxf4_ts(tmem + ATT_COL_O, ptm + ks * 8, vd + 2 * ks, idp4[ks], sfp, sfv, ks > 0 ? 1u : acc_any);
+          }
+          acc_any = 1;
         }
         tc_commit(&v_empty[sv]);
         tc_commit(&pv_done[bsel]);
         if (++sv == VSTAGES) { sv = 0; v_par ^= 1; }
         e = e_next;
       }
+    }
+  } else if (warp == 3) {
+    if (ROUTE) {
+    // ------------------------------ router -------------------------------------
+    // Statistic of every MXFP4 tile: mean over the query rows of the row maximum.  Lane l takes rows l, 32 + l, 64 + l,
+    // 96 + l of the published slice maxima; the four 32-row sums are formed by the same butterfly and added in the same
+    // order as in route_stat_kernel / route_stat_finish_kernel, so the statistic is the same bit for bit.
+    bool ok = true;
+    uint32_t st_par0 = 0, st_par1 = 0;              // phase parity of st_bar[0], st_bar[1]
+    float sink = 0.0f;                              // statistic of the row's first key tile (0 until it has been seen)
+    const float inv_rows = 1.0f / (float)min(ATT_BM, p.S - qi * ATT_BM);
+    for (int t = 0; t < nv && ok; ++t) {
+      const uint32_t e = vlist[t];
+      if (e & 0x8000) continue;                     // MXFP8 by the band rule: nothing to decide
+      const int bsel = t & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait<false>(&st_bar[bsel], bsel ? st_par1 : st_par0, p.status, KS_TIMEOUT_PIPE));
+      if (bsel) st_par1 ^= 1; else st_par0 ^= 1;
+      if (!ok) break;
+      const float* rm = reinterpret_cast<const float*>(smem + ATT_OFF_RMAX) + bsel * ATT_MAX_SPLIT * 128;
+      float pq[4];
+#pragma unroll
+      for (int qq = 0; qq < 4; ++qq) {
+        const int r = qq * 32 + lane;
+        float mxr = rm[r];
+#pragma unroll
+        for (int gg = 1; gg < NSPLIT; ++gg) mxr = fmaxf(mxr, rm[gg * 128 + r]);
+        float v = (qi * ATT_BM + r < p.S && mxr != -INFINITY) ? mxr * inv_rows : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        pq[qq] = v;
+      }
+      const float stat = ((pq[0] + pq[1]) + pq[2]) + pq[3];
+      const int j = e & 0x7fff;
+      if (j == 0) sink = stat;
+      const bool keep = !(stat >= sink * p.tau);
+      if (lane == 0) {
+        if (!keep) p.map_rw[(long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk + j] = TILE_AGAIN;
+        if (p.stat_out) p.stat_out[(((long long)b * p.Hq + h) * nq + qi) * nk + j] = stat;
+        dec[t & 3] = (t << 1) | (keep ? 1 : 0);     // one word: readers poll it, nothing else to publish
+      }
+      __syncwarp();
+    }
     }
   } else {
     // ------------------------------ softmax / correction / epilogue -----------
@@ -702,7 +809,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     // tile is redone from S, which is still intact in TMEM.  P is written over S only then.
     constexpr int W = 128 / NSPLIT;                 // keys of a tile owned by this thread
     constexpr int NCH = W / 32;                     // 32-column chunks of the slice
-    const int sw = warp - ATT_SERVICE_THREADS / 32; // warps 0-2 are the service warps
+    const int sw = warp - ATT_SERVICE_THREADS / 32; // warps 0-3 are the service warps
     const int q = warp & 3;                         // TMEM lane quarter this warp may access
     const int g = (sw >> 2) % NSPLIT;               // column split owned by this warp
     const int wg = (sw >> 2) / NSPLIT;              // warpgroup: owns tiles t with t % NWG == wg
@@ -716,6 +823,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     [[maybe_unused]] bool have_ref = false;
     float l_run = 0.0f;                             // partial row sum over this thread's tiles / columns
     bool ok = true;
+    static_assert(!ROUTE || (NWG == 2 && PVQ && LAZY && !NVF4), "the router runs in the fixed-reference MXFP4 kernel with two warpgroups");
     for (int t = wg; t < nv && ok; t += NWG) {      // t: index in the visit list; this warpgroup owns every NWG-th tile
       const uint32_t entry = vlist[t];
       const int j = entry & 0x7fff;                 // key tile
@@ -812,6 +920,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
           }
           const float bm = block_max32(sc);
           mx0 = fmaxf(mx0, bm);
+          if (ROUTE && !tile_f8 && c == NCH - 1) {
+            // the slice maximum is complete: publish it now, so that the router decides while this thread still
+            // does the arithmetic of its last block
+            reinterpret_cast<float*>(smem + ATT_OFF_RMAX)[(bsel * ATT_MAX_SPLIT + g) * 128 + r_in] = mx0;
+            mbar_arrive(&st_bar[bsel]);
+          }
           uint32_t code;
           if (pmode == 3) code = softmax_block_q<3>(sc, mref0, bm, pk + c * 4, lsum0, lsum1);
           else if (pmode == 1) code = softmax_block_q<1>(sc, mref0, bm, pk + c * 8, lsum0, lsum1);
@@ -902,7 +1016,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       }
       if (PVQ && LAZY && t == 0) { m_fix = m_used; have_ref = true; }
       }  // !lazy_tile
-      l_run += lsum0 + lsum1;
+      if (ROUTE && !tile_f8) {
+        if (!lazy_tile) {                           // the first tile went through the exact path and knows the row's maximum
+          reinterpret_cast<float*>(smem + ATT_OFF_RMAX)[(bsel * ATT_MAX_SPLIT + g) * 128 + r_in] = mx;
+          mbar_arrive(&st_bar[bsel]);
+        }
+        // the tile's sum counts only if the router keeps the tile (its word is there by now, as a rule)
+        const int w = poll_tag(&dec[t & 3], t, p.status);
+        if (w < 0) { ok = false; break; }
+        if (w & 1) l_run += lsum0 + lsum1;
+      } else {
+        l_run += lsum0 + lsum1;
+      }
       if (PVQ) {
         if (!lazy_tile) {
           tc_fence_before();
@@ -1006,31 +1131,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
           for (int i = 0; i < 32; ++i) o[i] = 0;
         }
         if (m_glob < p.S) {
-          if (p.out_dtype == 0) {
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o_off + c * 32);
-            if (p.acc_in) {
-              const float4* src = reinterpret_cast<const float4*>(p.acc_in + o_off + c * 32);
+          float val[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) val[i] = __uint_as_float(o[i]) * inv_l;
+          if (p.acc_in) {
+            // the earlier partial result of the same elements (it may be the very buffer written below)
+            if (p.acc_dtype == 0) {
+              const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.acc_in) + o_off + c * 32);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const float4 a = src[i];
-                dst[i] = make_float4(fmaf(a.x, w_prev, __uint_as_float(o[4 * i]) * inv_l), fmaf(a.y, w_prev, __uint_as_float(o[4 * i + 1]) * inv_l),
-                                     fmaf(a.z, w_prev, __uint_as_float(o[4 * i + 2]) * inv_l), fmaf(a.w, w_prev, __uint_as_float(o[4 * i + 3]) * inv_l));
+                val[4 * i] = fmaf(a.x, w_prev, val[4 * i]);
+                val[4 * i + 1] = fmaf(a.y, w_prev, val[4 * i + 1]);
+                val[4 * i + 2] = fmaf(a.z, w_prev, val[4 * i + 2]);
+                val[4 * i + 3] = fmaf(a.w, w_prev, val[4 * i + 3]);
               }
             } else {
+              const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.acc_in) + o_off + c * 32);
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                dst[i] = make_float4(__uint_as_float(o[4 * i]) * inv_l, __uint_as_float(o[4 * i + 1]) * inv_l,
-                                     __uint_as_float(o[4 * i + 2]) * inv_l, __uint_as_float(o[4 * i + 3]) * inv_l);
+              for (int i = 0; i < 4; ++i) {
+                const uint4 a = src[i];
+                const uint32_t w4[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  float2 f;
+                  if (p.acc_dtype == 1) f = __half22float2(*reinterpret_cast<const __half2*>(&w4[k]));
+                  else f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w4[k]));
+                  val[8 * i + 2 * k] = fmaf(f.x, w_prev, val[8 * i + 2 * k]);
+                  val[8 * i + 2 * k + 1] = fmaf(f.y, w_prev, val[8 * i + 2 * k + 1]);
+                }
+              }
             }
+          }
+          if (p.out_dtype == 0) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o_off + c * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_float4(val[4 * i], val[4 * i + 1], val[4 * i + 2], val[4 * i + 3]);
           } else {
             uint32_t w[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const float a = __uint_as_float(o[2 * i]) * inv_l, c2 = __uint_as_float(o[2 * i + 1]) * inv_l;
               if (p.out_dtype == 1) {
-                w[i] = pack_f16x2(a, c2);
+                w[i] = pack_f16x2(val[2 * i], val[2 * i + 1]);
               } else {
-                __nv_bfloat162 hb = __floats2bfloat162_rn(a, c2);
+                __nv_bfloat162 hb = __floats2bfloat162_rn(val[2 * i], val[2 * i + 1]);
                 w[i] = *reinterpret_cast<uint32_t*>(&hb);
               }
             }
@@ -1121,6 +1265,7 @@ __global__ void __launch_bounds__(256) prepare_vt_kernel(const T* v, __half* vt,
 __global__ void route_band_kernel(uint8_t* map, int nq, int nk, int T, int causal, int band, int off, int S) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x, i = blockIdx.y;
   if (j >= nk) return;
+  map += (long long)blockIdx.z * nq * nk;             // one copy of the map per (batch, head) when launched with grid.z > 1
   uint8_t v = (abs(i + off / T - j) < band) ? TILE_FP8 : TILE_FP4;
   if (causal) {
     const int last_q = min(S - 1, i * T + T - 1);       // last query row of the tile
@@ -1177,9 +1322,9 @@ struct AttnMaps { const CUtensorMap *q8, *q4, *k8, *k4, *vt, *vt8, *vt4; };
 // One launch of one organisation of the forward.  The opt-in for more than 48 KB of dynamic shared memory is a
 // per-device attribute of the kernel: it is set before every launch (a host-side table write), so that any device and
 // any thread may make the first call.
-template <int NWG, int NSPLIT, int PVQ, int NVF4, int LAZY>
+template <int NWG, int NSPLIT, int PVQ, int NVF4, int LAZY, int ROUTE = 0>
 int launch_attn(dim3 grid, cudaStream_t st, const AttnMaps& m, const AttnParams& p) {
-  auto kern = attn_fwd_kernel<NWG, NSPLIT, PVQ, NVF4, (PVQ ? LAZY : 0)>;
+  auto kern = attn_fwd_kernel<NWG, NSPLIT, PVQ, NVF4, (PVQ ? LAZY : 0), ROUTE>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess) {
     cudaGetLastError();
     return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cannot reserve %d bytes of shared memory", ATT_SMEM);
@@ -1189,13 +1334,19 @@ int launch_attn(dim3 grid, cudaStream_t st, const AttnMaps& m, const AttnParams&
 }
 }  // namespace
 
-extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
+namespace {
+struct AttnLaunch {
+  CUtensorMap tq8, tq4, tk8, tk4, tvt, tvt8, tvt4;
+  AttnParams p;
+};
+
+// argument checks, tensor maps and the parameter block shared by the forward entry points
+int prepare_attn(AttnLaunch& L, const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
                              const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* vt8,
                              const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
                              long long map_sb, long long map_sh, void* out, int out_dtype, void* lse, int B, int Hq,
                              int Hkv, int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int fp4_kind,
-                             float fp4_scale, int* range_flag, const void* acc_in, const void* lse_in, int* status,
-                             void* stream) {
+                             float fp4_scale, const void* acc_in, const void* lse_in, int acc_dtype, int* status) {
   if (!q8 || !q8_sf || !q4 || !q4_sf || !k8 || !k8_sf || !k4 || !k4_sf || !map || !out || !status)
     return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: null pointer");
   if (pv_mode != 0 && pv_mode != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: pv_mode must be 0 (fp16 P.V) or 1 (quantised P.V)");
@@ -1208,8 +1359,8 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   if (fp8_fmt != 0 && fp8_fmt != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: fp8_fmt must be 0 (E4M3) or 1 (E5M2)");
   if (fp4_kind != 0 && fp4_kind != 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: fp4_kind must be 0 (MXFP4) or 1 (NVFP4)");
   if ((acc_in != nullptr) != (lse_in != nullptr)) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: acc_in and lse_in go together");
-  if (acc_in && (out_dtype != 0 || !lse || acc_in == out || lse_in == lse || ((uintptr_t)acc_in % 16)))
-    return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: merging needs fp32 out, lse, 16-byte aligned acc_in, and outputs distinct from the inputs");
+  if (acc_in && (acc_dtype < 0 || acc_dtype > 2 || lse_in == lse || ((uintptr_t)acc_in % 16)))
+    return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: merging needs a 16-byte aligned acc_in of dtype 0..2 and an lse output distinct from lse_in");
   if (fp4_kind == 1 && !(fp4_scale > 0.0f)) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: NVFP4 needs a positive fp4_scale");
   if (causal && Skv < S) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: causal needs Skv >= S");
   if ((Skv + ATT_BN - 1) / ATT_BN > ATT_MAP_SMEM) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: at most %d keys", ATT_MAP_SMEM * ATT_BN);
@@ -1219,7 +1370,7 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
     if ((uintptr_t)ptr % 16) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: every tensor base must be 16-byte aligned");
   if ((long long)B * Hq * S >= (1ll << 31) || (long long)B * Hkv * Skv >= (1ll << 31))
     return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: B*H*S must fit in 31 bits");
-  CUtensorMap tq8, tq4, tk8, tk4, tvt, tvt8, tvt4;
+  CUtensorMap &tq8 = L.tq8, &tq4 = L.tq4, &tk8 = L.tk8, &tk4 = L.tk4, &tvt = L.tvt, &tvt8 = L.tvt8, &tvt4 = L.tvt4;
   const uint64_t qrows = (uint64_t)B * Hq * S, krows = (uint64_t)B * Hkv * Skv;
   if (make_tmap_2d_bytes(&tq8, q8, ATT_DQK, qrows, ATT_DQK, 128, ATT_BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
       make_tmap_2d_bytes(&tq4, q4, ATT_DQK / 2, qrows, ATT_DQK / 2, 64, ATT_BM, CU_TENSOR_MAP_SWIZZLE_64B) ||
@@ -1238,7 +1389,7 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
       return set_error(MPSA_ERR_LAUNCH, "attn_fwd: cuTensorMapEncodeTiled failed");
     tvt = tvt8;                  // not dereferenced in this mode
   }
-  AttnParams p;
+  AttnParams& p = L.p;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S = S; p.Skv = Skv; p.D = D; p.causal = causal; p.fp8_fmt = fp8_fmt;
   p.q8_sf = (const uint8_t*)q8_sf; p.q4_sf = (const uint8_t*)q4_sf;
   p.k8_sf = (const uint8_t*)k8_sf; p.k4_sf = (const uint8_t*)k4_sf;
@@ -1247,7 +1398,29 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   p.map = (const uint8_t*)map; p.map_sb = map_sb; p.map_sh = map_sh;
   p.out = out; p.out_dtype = out_dtype; p.lse = (float*)lse; p.status = status;
   p.range_flag = nullptr; p.run_if = nullptr;
-  p.acc_in = (const float*)acc_in; p.lse_in = (const float*)lse_in;
+  p.acc_in = acc_in; p.lse_in = (const float*)lse_in; p.acc_dtype = acc_dtype;
+  p.tau = 0.0f; p.map_rw = nullptr; p.stat_out = nullptr; p.map_mode = 0; p.skip_if = nullptr;
+  if (Hq > 65535 || B > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: Hq and B must be below 65536");
+  return MPSA_OK;
+}
+}  // namespace
+
+extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
+                             const void* k8_sf, const void* k4, const void* k4_sf, const void* vt, const void* vt8,
+                             const void* v8_sf, const void* vt4, const void* v4_sf, int pv_mode, const void* map,
+                             long long map_sb, long long map_sh, void* out, int out_dtype, void* lse, int B, int Hq,
+                             int Hkv, int S, int Skv, int D, int Skv_pad, int causal, int fp8_fmt, int fp4_kind,
+                             float fp4_scale, int* range_flag, const void* acc_in, const void* lse_in, int* status,
+                             void* stream) {
+  if (acc_in && (out_dtype != 0 || !lse || acc_in == out))
+    return set_error(MPSA_ERR_BAD_ARG, "attn_fwd: merging needs fp32 out, lse, and an output distinct from acc_in");
+  AttnLaunch L;
+  if (int rc = prepare_attn(L, q8, q8_sf, q4, q4_sf, k8, k8_sf, k4, k4_sf, vt, vt8, v8_sf, vt4, v4_sf, pv_mode, map, map_sb, map_sh,
+                            out, out_dtype, lse, B, Hq, Hkv, S, Skv, D, Skv_pad, causal, fp8_fmt, fp4_kind, fp4_scale, acc_in, lse_in,
+                            0, status))
+    return rc;
+  AttnParams& p = L.p;
+  CUtensorMap &tq8 = L.tq8, &tq4 = L.tq4, &tk8 = L.tk8, &tk4 = L.tk4, &tvt = L.tvt, &tvt8 = L.tvt8, &tvt4 = L.tvt4;
   // Softmax organisation: warpgroups taking tiles in turn (1 or 2) x threads per query row inside a
   // warpgroup (1, 2 or 4).  MPSA_ATTN_WG / MPSA_ATTN_SPLIT override the defaults (read once per process):
   // fp16 P.V 2 warpgroups x 1, quantised P.V 2 x 2.
@@ -1266,7 +1439,6 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   });
   const int cfg = cfg_of[pv_mode];
   const int nq = (S + ATT_BM - 1) / ATT_BM;
-  if (Hq > 65535 || B > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: Hq and B must be below 65536");
   const dim3 grid(nq, Hq, B);
   cudaStream_t st = (cudaStream_t)stream;
   const AttnMaps maps{&tq8, &tq4, &tk8, &tk4, &tvt, &tvt8, &tvt4};
@@ -1305,3 +1477,63 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
   }
 #undef MPSA_GO
 }
+
+// The forward with the online router inside (no stand-alone statistic pass): MXFP8 inside the diagonal band, MXFP4
+// elsewhere unless the MXFP4 statistic of a tile reaches tau x that of the row's first key tile, in which case the tile is
+// done in MXFP8.  Quantised P.V, causal.  Three launches in the common case:
+//   1. the band map for every (batch, head) into `map`;
+//   2. the fixed-reference forward with the router (ROUTE): tiles to promote are left out and marked in `map`, `out` and
+//      `lse` hold the result over all other tiles;
+//   3. a second forward over exactly the marked tiles in MXFP8, merged into `out` in place (the marks become TILE_FP8,
+//      so that `map` ends up as mpsa_route_online would have written it).
+// If a score left the fixed reference's headroom in (2), *range_flag is set and the stand-alone path (statistic kernel,
+// map, exact forward) runs instead, conditionally, behind it; (3) then does nothing.
+extern "C" int mpsa_attn_fwd_routed(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
+                                    const void* k8_sf, const void* k4, const void* k4_sf, const void* vt8, const void* v8_sf,
+                                    const void* vt4, const void* v4_sf, void* map, int band, float tau, void* out,
+                                    int out_dtype, void* lse, void* lse_final, void* stat, void* stat_scratch, int B, int Hq,
+                                    int Hkv, int S, int Skv, int D, int Skv_pad, int fp8_fmt, int stages, int* range_flag,
+                                    int* status, void* stream) {
+  if (!map || !lse || !stat || !stat_scratch || !range_flag) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: null pointer");
+  if (stages < 1 || stages > 15) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: stages is a mask of 1 (band map), 2 (first pass), 4 (fallback), 8 (second pass)");
+  if (band < 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: band must be at least 1");
+  if (lse_final == lse) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: lse_final must be another buffer than lse (or null)");
+  if (((uintptr_t)stat_scratch % 16)) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: stat_scratch must be 16-byte aligned");
+  const int nq = (S + ATT_BM - 1) / ATT_BM, nk = (Skv + ATT_BN - 1) / ATT_BN;
+  const long long msh = (long long)nq * nk, msb = msh * Hq;
+  AttnLaunch L;
+  if (int rc = prepare_attn(L, q8, q8_sf, q4, q4_sf, k8, k8_sf, k4, k4_sf, nullptr, vt8, v8_sf, vt4, v4_sf, 1, map, msb, msh, out,
+                            out_dtype, lse, B, Hq, Hkv, S, Skv, D, Skv_pad, 1, fp8_fmt, 0, 0.0f, nullptr, nullptr, 0, status))
+    return rc;
+  if (nq > 65535 || (long long)B * Hq > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd_routed: too many tiles or heads");
+  cudaStream_t st = (cudaStream_t)stream;
+  const AttnMaps maps{&L.tq8, &L.tq4, &L.tk8, &L.tk4, &L.tvt, &L.tvt8, &L.tvt4};
+  const dim3 grid(nq, Hq, B);
+  // 1. band map, one copy per (batch, head)
+  if (stages & 1) {
+    route_band_kernel<<<dim3((nk + 127) / 128, nq, B * Hq), 128, 0, st>>>((uint8_t*)map, nq, nk, 128, 1, band, Skv - S, S);
+    if (int rc = check_launch("route_band")) return rc;
+  }
+  // 2. first pass: router inside, promoted tiles left out
+  if (stages & 2) {
+    AttnParams pa = L.p;
+    pa.tau = tau; pa.map_rw = (uint8_t*)map; pa.stat_out = nullptr; pa.range_flag = range_flag;
+    if (int rc = launch_attn<2, 2, 1, 0, 1, 1>(grid, st, maps, pa)) return rc;
+  }
+  // fallback, conditional on *range_flag: statistic, map and the exact kernel over everything
+  if (stages & 4) {
+    if (int rc = launch_route_stat(q4, q4_sf, k4, k4_sf, stat, stat_scratch, B, Hq, Hkv, S, Skv, 1, status, range_flag, stream)) return rc;
+    if (int rc = launch_route_online(map, stat, B, Hq, S, Skv, 1, band, tau, 0.0f, 0, range_flag, stream)) return rc;
+    AttnParams pf = L.p;
+    pf.run_if = range_flag;
+    if (lse_final) pf.lse = (float*)lse_final;
+    if (int rc = launch_attn<2, 2, 1, 0, 0>(grid, st, maps, pf)) return rc;
+  }
+  // 3. second pass: the marked tiles in MXFP8, merged in place
+  if (!(stages & 8)) return MPSA_OK;
+  AttnParams pb = L.p;
+  pb.map_mode = 1; pb.map_rw = (uint8_t*)map; pb.skip_if = range_flag;
+  pb.acc_in = out; pb.acc_dtype = out_dtype; pb.lse_in = (const float*)lse; pb.lse = (float*)lse_final;
+  return launch_attn<2, 2, 1, 0, 0>(grid, st, maps, pb);
+}
+

@@ -34,6 +34,7 @@ struct RouteParams {
   const uint8_t* q4_sf; const uint8_t* k4_sf;
   float* part;            // [B,Hq,nq,nk,4] per-warp partial means; cells of tiles above the causal diagonal are not written
   int* status;
+  const int* run_if;      // when given: the kernel does nothing unless this word is non-zero
 };
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -51,6 +52,7 @@ __global__ void __launch_bounds__(RT_THREADS, 1)
 route_stat_kernel(const __grid_constant__ CUtensorMap tm_q4, const __grid_constant__ CUtensorMap tm_k4,
                   const RouteParams p) {
   extern __shared__ uint8_t smem_raw[];
+  if (p.run_if && *(volatile const int*)p.run_if == 0) return;
   uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + RT_OFF_BAR);
   uint64_t* q_full = bars;
@@ -213,7 +215,8 @@ route_stat_kernel(const __grid_constant__ CUtensorMap tm_q4, const __grid_consta
 }
 
 // stat = ((p0 + p1) + p2) + p3: the four per-warp partial means of a tile, added in a fixed order
-__global__ void route_stat_finish_kernel(const float4* part, float* stat, long long n) {
+__global__ void route_stat_finish_kernel(const float4* part, float* stat, long long n, const int* run_if) {
+  if (run_if && *(volatile const int*)run_if == 0) return;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
     const float4 v = part[i];
@@ -224,7 +227,8 @@ __global__ void route_stat_finish_kernel(const float4* part, float* stat, long l
 // map[b,h,i,j]: SKIP above the causal diagonal, FP8 inside the band, else FP8 iff stat >= sink * tau, else FP4;
 // with use_skip, tiles outside the band whose statistic is below sink * skip_tau are SKIP as well.
 __global__ void route_online_kernel(uint8_t* map, const float* stat, int nq, int nk, int tile, int causal, int band,
-                                    float tau, float skip_tau, int use_skip, int S, int Skv) {
+                                    float tau, float skip_tau, int use_skip, int S, int Skv, const int* run_if) {
+  if (run_if && *(volatile const int*)run_if == 0) return;
   const int j = blockIdx.x * blockDim.x + threadIdx.x, i = blockIdx.y;
   const long long bh = blockIdx.z;
   if (j >= nk) return;
@@ -250,8 +254,8 @@ __global__ void route_online_kernel(uint8_t* map, const float* stat, int nq, int
 
 using namespace mpsa;
 
-extern "C" int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4, const void* k4_sf, void* stat,
-                               void* scratch, int B, int Hq, int Hkv, int S, int Skv, int causal, int* status, void* stream) {
+int mpsa::launch_route_stat(const void* q4, const void* q4_sf, const void* k4, const void* k4_sf, void* stat, void* scratch, int B,
+                            int Hq, int Hkv, int S, int Skv, int causal, int* status, const int* run_if, void* stream) {
   if (!q4 || !q4_sf || !k4 || !k4_sf || !stat || !scratch || !status) return set_error(MPSA_ERR_BAD_ARG, "route_stat: null pointer");
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || Skv <= 0 || Hq % Hkv) return set_error(MPSA_ERR_BAD_ARG, "route_stat: bad shape");
   if (causal && Skv < S) return set_error(MPSA_ERR_UNSUPPORTED, "route_stat: causal needs Skv >= S");
@@ -268,6 +272,7 @@ extern "C" int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.S = S; p.Skv = Skv; p.causal = causal;
   p.nh = ((Hq / Hkv) % 2 == 0) ? 2 : 1;
   p.q4_sf = (const uint8_t*)q4_sf; p.k4_sf = (const uint8_t*)k4_sf; p.part = (float*)scratch; p.status = status;
+  p.run_if = run_if;
   // per-device attribute of the kernel: set before every launch, so that any device and any thread may call first
   if (cudaFuncSetAttribute(route_stat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RT_SMEM) != cudaSuccess) {
     cudaGetLastError();
@@ -282,17 +287,27 @@ extern "C" int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4
   dim3 grid(nq, Hq / p.nh, B);
   route_stat_kernel<<<grid, RT_THREADS, RT_SMEM, (cudaStream_t)stream>>>(tq, tk, p);
   if (int rc = check_launch("route_stat")) return rc;
-  route_stat_finish_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const float4*)scratch, (float*)stat, cells);
+  route_stat_finish_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const float4*)scratch, (float*)stat, cells, run_if);
   return check_launch("route_stat_finish");
 }
 
-extern "C" int mpsa_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv, int causal, int band,
-                                 float tau, float skip_tau, int use_skip, void* stream) {
+extern "C" int mpsa_route_stat(const void* q4, const void* q4_sf, const void* k4, const void* k4_sf, void* stat,
+                               void* scratch, int B, int Hq, int Hkv, int S, int Skv, int causal, int* status, void* stream) {
+  return mpsa::launch_route_stat(q4, q4_sf, k4, k4_sf, stat, scratch, B, Hq, Hkv, S, Skv, causal, status, nullptr, stream);
+}
+
+int mpsa::launch_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv, int causal, int band, float tau,
+                              float skip_tau, int use_skip, const int* run_if, void* stream) {
   if (!map || !stat || B <= 0 || Hq <= 0 || S <= 0 || Skv <= 0 || band < 0) return set_error(MPSA_ERR_BAD_ARG, "route_online: bad argument");
   const int nq = (S + 127) / 128, nk = (Skv + 127) / 128;
   if (nq > 65535 || (long long)B * Hq > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "route_online: too many tiles or heads");
   dim3 grid((nk + 127) / 128, nq, B * Hq);
   route_online_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((uint8_t*)map, (const float*)stat, nq, nk, 128, causal, band,
-                                                             tau, skip_tau, use_skip, S, Skv);
+                                                             tau, skip_tau, use_skip, S, Skv, run_if);
   return check_launch("route_online");
+}
+
+extern "C" int mpsa_route_online(void* map, const void* stat, int B, int Hq, int S, int Skv, int causal, int band,
+                                 float tau, float skip_tau, int use_skip, void* stream) {
+  return mpsa::launch_route_online(map, stat, B, Hq, S, Skv, causal, band, tau, skip_tau, use_skip, nullptr, stream);
 }

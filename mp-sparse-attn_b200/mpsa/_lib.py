@@ -47,6 +47,8 @@ _SIGNATURES = {
                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p], c_int),
     "mpsa_attn_fwd": ([c_void_p] * 13 + [c_int, c_void_p, c_ll, c_ll, c_void_p, c_int, c_void_p] + [c_int] * 10 +
                       [c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p], c_int),
+    "mpsa_attn_fwd_routed": ([c_void_p] * 13 + [c_int, c_float, c_void_p, c_int] + [c_void_p] * 4 + [c_int] * 9 +
+                             [c_void_p, c_void_p, c_void_p], c_int),
     "mpsa_attn_merge": ([c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_ll, c_int, c_void_p], c_int),
     "mpsa_gemm_block_scaled_batched": ([c_void_p] * 5 + [c_int] * 8 + [c_float, c_void_p, c_void_p], c_int),
     "mpsa_gemm_block_scaled": ([c_void_p] * 5 + [c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_int, c_int, c_int,

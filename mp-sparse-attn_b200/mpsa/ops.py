@@ -403,7 +403,7 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
                       out_dtype: torch.dtype = torch.bfloat16, pv_mode: str = "fp16", check: bool = False,
                       router: str = "band", tau: float = 1.0, fp4_kind: str = "mxfp4",
                       skip_thresh: Optional[float] = None, return_sparsity: bool = False, smooth_k: bool = False,
-                      rope=None, kv=None):
+                      rope=None, kv=None, fused_router: bool = True):
     """Quantise Q/K (both MXFP8 and MXFP4 in one pass each), prepare V, build the precision map and
     run the fused forward.  q [B,Hq,S,D], k/v [B,Hkv,Skv,D]; D in {64, 128}.
     smooth_k: subtract K's mean over the sequence inside the K quantizer (softmax is unchanged by it: every score
@@ -413,10 +413,11 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
     kv: the pair from prepare_kv (or mpsa.kvstore) in place of k and v, which may then be None; pv_mode follows the
     kind of V given, and smooth_k / the K side of rope have been applied when the pair was made.
 
-    router "band": the static diagonal-band map.  router "online": one extra MXFP4 pass over the score tiles
-    (router_statistic) promotes to MXFP8 every tile whose statistic reaches `tau` times that of the row's
-    first key tile (precision_map_online); with skip_thresh it also drops the tiles the reference's router would
-    drop.  return_sparsity: also return the share of visible tiles dropped.
+    router "band": the static diagonal-band map.  router "online": every tile whose MXFP4 statistic reaches `tau`
+    times that of the row's first key tile is promoted to MXFP8.  Causal with quantised P.V: the router runs inside
+    the forward (attention_forward_routed; fused_router=False forces the stand-alone form).  Otherwise one extra MXFP4
+    pass over the score tiles (router_statistic) and precision_map_online build the map first; with skip_thresh it also
+    drops the tiles the reference's router would drop.  return_sparsity: also return the share of visible tiles dropped.
 
     pv_mode "fp16": P and V in fp16, the P.V precision of the reference kernel.
     pv_mode "requant": P is re-quantised to the tile's MX format and V is quantised along the sequence.
@@ -451,6 +452,10 @@ def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, caus
             raise ValueError("the online router reads MXFP4 operands")
         if prec_map is not None or uniform is not None:
             raise ValueError("router='online' builds its own precision map")
+        if fused_router and causal and skip_thresh is None and isinstance(vt, QuantizedV) and not return_sparsity:
+            # the router runs inside the forward: no stand-alone statistic pass
+            return attention_forward_routed(qq, kq, vt, B, Hq, Hkv, S, Skv, D, band=band, tau=tau, out_dtype=out_dtype,
+                                            check=check)
         stat = router_statistic(qq, kq, B, Hq, Hkv, S, Skv, causal=causal, check=check)
         prec_map = precision_map_online(stat, S, Skv, causal=causal, band=band, tau=tau, skip_thresh=skip_thresh)
     elif router != "band":
@@ -569,6 +574,60 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
     if check:
         check_status(dev)
     return (out, lse) if return_lse else out
+
+
+def attention_forward_routed(qq: QuantizedOperand, kq: QuantizedOperand, vq: "QuantizedV", B: int, Hq: int, Hkv: int, S: int,
+                             Skv: int, D: int, *, band: int = 1, tau: float = 1.0, out_dtype: torch.dtype = torch.bfloat16,
+                             check: bool = False, return_map: bool = False, return_lse: bool = False, stages: int = 15):
+    """The causal forward with the online router inside it (quantised P.V, MXFP4/MXFP8 operands): no stand-alone
+    statistic pass.  Tiles the router promotes are left out of the first pass and done in MXFP8 by a second one that
+    merges into the output in place.  Same precision map as precision_map_online(router_statistic(...), tau=tau).
+    stages: mask of the launches to make (1 band map, 2 first pass, 4 conditional fallback, 8 second pass) - anything but
+    15 leaves the output incomplete and is for timing a stage alone."""
+    if not isinstance(vq, QuantizedV):
+        raise ValueError("the routed forward needs V quantised along the sequence (quantize_v_seq)")
+    if qq.fp4_kind != "mxfp4" or kq.fp4_kind != "mxfp4":
+        raise ValueError("the online router reads MXFP4 operands")
+    for t in (qq.fp8, qq.fp4, qq.fp8_sf, qq.fp4_sf, kq.fp8, kq.fp4, kq.fp8_sf, kq.fp4_sf):
+        if t is None:
+            raise ValueError("the routed forward needs both the MXFP8 and the MXFP4 form of Q and K")
+    if out_dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"Unsupported dtype: {out_dtype}")
+    if Skv < S:
+        raise ValueError("causal attention needs Skv >= S")
+    dev = vq.vt8.device
+    nq, nk = -(-S // 128), -(-Skv // 128)
+    skv_pad = vq.vt8.shape[-1]
+    if qq.fp8.numel() != B * Hq * S * 128 or kq.fp8.numel() != B * Hkv * Skv * 128 or tuple(vq.vt8.shape) != (B, Hkv, D, skv_pad):
+        raise ValueError("quantised operands have the wrong size (depth must be padded to 128)")
+    pm = torch.empty((B, Hq, nq, nk), dtype=torch.uint8, device=dev)
+    out = torch.empty((B, Hq, S, D), dtype=out_dtype, device=dev)
+    lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
+    lse_final = torch.empty((B, Hq, S), dtype=torch.float32, device=dev) if return_lse else None
+    stat = torch.empty((B, Hq, nq, nk), dtype=torch.float32, device=dev)
+    scratch = torch.empty((B, Hq, nq, nk, 4), dtype=torch.float32, device=dev)
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    global _last_range_flag
+    _last_range_flag = flag
+    _raise_if_failed(dev)
+    st = status_word(dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().mpsa_attn_fwd_routed(
+            qq.fp8.data_ptr(), qq.fp8_sf.data_ptr(), qq.fp4.data_ptr(), qq.fp4_sf.data_ptr(),
+            kq.fp8.data_ptr(), kq.fp8_sf.data_ptr(), kq.fp4.data_ptr(), kq.fp4_sf.data_ptr(),
+            vq.vt8.data_ptr(), vq.v8_sf.data_ptr(), vq.vt4.data_ptr(), vq.v4_sf.data_ptr(),
+            pm.data_ptr(), int(band), float(tau), out.data_ptr(), _OUT_DTYPE[out_dtype], lse.data_ptr(), _ptr(lse_final),
+            stat.data_ptr(), scratch.data_ptr(), B, Hq, Hkv, S, Skv, D, skv_pad, _FP8_DESC[qq.fp8_elem], int(stages), flag.data_ptr(),
+            st.data_ptr(), _stream())
+    _lib.check(rc)
+    if check:
+        check_status(dev)
+    res = (out,)
+    if return_map:
+        res += (pm,)
+    if return_lse:
+        res += (lse_final,)
+    return res[0] if len(res) == 1 else res
 
 
 def attention_merge(acc: torch.Tensor, lse_acc: torch.Tensor, part: torch.Tensor, lse_part: torch.Tensor) -> None:

@@ -29,10 +29,17 @@ def test_bench_workload_slices_match_the_oracle(S):
                                           out_dtype=torch.float32, check=True)
     # the fixed-reference kernel must have been enough: no score left its 2^64 headroom at this size
     assert int(ops._last_range_flag.item()) == 0
-    # ... and the one-call form (what the benchmark times) gives the same bits
-    out2 = mpsa.attention_forward(dq, dk, dv, causal=True, out_dtype=torch.float32, pv_mode="requant", router="online",
+    # ... and the one-call form (what the benchmark times: the router runs inside the forward, the promoted tiles
+    # are merged in by a second pass) gives the same result up to fp32 rounding, from the same map
+    out2, pm2 = ops.attention_forward_routed(qq, kq, vq, 1, Hq, Hkv, S, S, D, band=1, tau=TAU, out_dtype=torch.float32,
+                                             check=True, return_map=True)
+    assert int(ops._last_range_flag.item()) == 0
+    assert torch.equal(pm, pm2)
+    m2 = O.parity_metrics(out2.cpu(), out.cpu())
+    assert m2["rel_l2"] <= 1e-5, m2
+    out3 = mpsa.attention_forward(dq, dk, dv, causal=True, out_dtype=torch.float32, pv_mode="requant", router="online",
                                   tau=TAU, check=True)
-    assert torch.equal(out, out2)
+    assert torch.equal(out2, out3)
     pm_c, out_c = pm.cpu(), out.cpu()
     grp = Hq // Hkv
     for h in (3, 17):
