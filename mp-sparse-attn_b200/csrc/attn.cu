@@ -23,9 +23,14 @@
 //               TMEM (its own columns, so that Q.K^T of tile t+2 can be issued before P.V of tile t); the
 //               row reference is kept integral so that the codes do not depend on it.  By default the
 //               reference is fixed after the first key tile (template parameter LAZY, see the kernel).
-// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2.. softmax/correction/epilogue (a warp reaches the TMEM lane
-// quarter warp % 4, so any four consecutive warps cover the 128 rows).  S is
-// double-buffered in TMEM so that Q.K^T of tile t+1 overlaps the softmax of tile t.  NWG softmax
+// Roles: warp 0 TMA loads (Q once, then a K ring and a V ring), warp 1 Q.K^T issuer, warp 2 P.V issuer (quantised
+// P.V; with fp16 P.V warp 1 issues both products, in order, because P then overwrites S), warp 3 router (ROUTE
+// kernels), warps 4.. softmax / correction / epilogue (a warp reaches the TMEM lane quarter warp % 4, so any four
+// consecutive warps cover the 128 rows).  Every role walks the CTA's visit list - the non-skipped cells of its map row,
+// compacted once into shared memory.  The issuing threads' loops hold nothing but their waits, the scale copies, the
+// MMAs and the commits (measured: 64 cycles per MXFP4 MMA, ~48 per scale copy, ~44 per commit; a loop that also
+// searched the map and derived ring slots by division took ~2000 cycles per tile and bound the whole kernel).  S is
+// double-buffered in TMEM so that Q.K^T of tile t+2 overlaps the softmax of tile t.  NWG softmax
 // warpgroups take the key tiles in turn (warpgroup w owns tiles t = w mod NWG), so that the
 // exponentials of one tile (MUFU) overlap the max / pack / TMEM traffic of the next; the running
 // row maximum is handed from the owner of tile t to the owner of tile t+1 through shared memory.
