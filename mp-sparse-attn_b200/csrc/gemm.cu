@@ -83,6 +83,7 @@ __device__ __forceinline__ void store_row32(void* c, long long off, int out_dtyp
   }
 }
 
+template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const GemmParams p) {
@@ -97,13 +98,16 @@ gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * GEMM_BM, n0 = blockIdx.y * GEMM_BN;
-  // per-mode geometry
-  const int epb = p.mode == 0 ? 1 : 2;                   // elements per byte
-  const int k_stage = GEMM_SLAB * epb;                   // elements of K per stage
-  const int k_mma = p.mode == 0 ? 32 : 64;               // elements of K per instruction
-  const int chunk_elems = p.mode == 2 ? 64 : 128;        // K elements covered by one scale tile
-  const int nc_stage = k_stage / chunk_elems;            // scale tiles per stage and row tile
-  const int KT = (p.K + k_stage - 1) / k_stage;
+  // per-mode geometry, all compile-time: the two single-thread loops below must stay short (an MXFP8 K step is 512
+  // tensor-pipe cycles; a loop with run-time mode switches and divisions took ~1200)
+  constexpr int EPB = MODE == 0 ? 1 : 2;                 // elements per byte
+  constexpr int K_STAGE = GEMM_SLAB * EPB;               // elements of K per stage
+  constexpr int CHUNK = MODE == 2 ? 64 : 128;            // K elements covered by one scale tile
+  constexpr int NC = K_STAGE / CHUNK;                    // scale tiles per stage and row tile: 1, 2, 4
+  constexpr int MPC = 4 / NC;                            // instructions per scale tile (4 instructions per stage)
+  const int KT = (p.K + K_STAGE - 1) / K_STAGE;
+  const int n_row_tiles = (p.N + 127) / 128;
+  const bool two_b = n_row_tiles - (int)blockIdx.y * 2 >= 2;   // the CTA's second 128-row tile of B exists
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -121,30 +125,32 @@ gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (lane == 0) {
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_b);
-      const int mt = blockIdx.x, nt0 = blockIdx.y * 2;
-      const int n_row_tiles = (p.N + 127) / 128;
       // batched launch (blockIdx.z): operands, scale tiles and C of the batches lie one after the other
-      const uint8_t* sfa_z = p.sfa + (long long)blockIdx.z * ((p.M + 127) / 128) * p.nchunks * 512;
-      const uint8_t* sfb_z = p.sfb + (long long)blockIdx.z * n_row_tiles * p.nchunks * 512;
-      int issued = 0;
+      const uint8_t* sfa_g = p.sfa + ((long long)blockIdx.z * ((p.M + 127) / 128) + blockIdx.x) * p.nchunks * 512;
+      const uint8_t* sfb_g = p.sfb + ((long long)blockIdx.z * n_row_tiles + blockIdx.y * 2) * p.nchunks * 512;
+      const long long sfb_tile1 = (long long)p.nchunks * 512;           // the second B row tile's scale tiles
+      const int ya = (int)blockIdx.z * p.M + m0, yb = (int)blockIdx.z * p.N + n0;
+      int issued = 0, s = 0, left = p.nchunks;      // left: scale tiles along K not yet requested
+      uint32_t e_par = 1;                           // parity that a never-used barrier already satisfies
       bool ok = true;
-      for (int kt = 0; kt < KT && ok; ++kt) {
-        const int s = kt % GEMM_STAGES;
-        if (kt >= GEMM_STAGES) ok = mbar_wait(&empty[s], ((kt / GEMM_STAGES) - 1) & 1, p.status, KS_TIMEOUT_PIPE);
-        if (!ok) break;
+      for (int kt = 0; kt < KT; ++kt) {
+        if (kt >= GEMM_STAGES) {
+          ok = mbar_wait(&empty[s], e_par, p.status, KS_TIMEOUT_PIPE);
+          if (!ok) break;
+        }
         uint8_t* st = smem + s * GEMM_STAGE_BYTES;
-        const int c0 = kt * nc_stage;
-        const int ncv = min(nc_stage, p.nchunks - c0);          // valid scale tiles in this stage
-        const int nbt = min(2, n_row_tiles - nt0);              // valid B row tiles
-        const uint32_t bytes = GEMM_A_BYTES + GEMM_B_BYTES + (uint32_t)ncv * 512u * (1 + nbt);
-        mbar_arrive_expect_tx(&full[s], bytes);
-        tma_load_2d(st, &tmap_a, &full[s], kt * GEMM_SLAB, (int)blockIdx.z * p.M + m0);
-        tma_load_2d(st + GEMM_A_BYTES, &tmap_b, &full[s], kt * GEMM_SLAB, (int)blockIdx.z * p.N + n0);
-        bulk_load(st + GEMM_A_BYTES + GEMM_B_BYTES, sfa_z + ((long long)mt * p.nchunks + c0) * 512, ncv * 512, &full[s]);
-        for (int t = 0; t < nbt; ++t)
-          bulk_load(st + GEMM_A_BYTES + GEMM_B_BYTES + GEMM_SFA_BYTES + t * nc_stage * 512,
-                    sfb_z + ((long long)(nt0 + t) * p.nchunks + c0) * 512, ncv * 512, &full[s]);
+        const int ncv = left < NC ? left : NC;                  // valid scale tiles in this stage (fewer only in the last)
+        mbar_arrive_expect_tx(&full[s], GEMM_A_BYTES + GEMM_B_BYTES + (uint32_t)ncv * (two_b ? 1536u : 1024u));
+        tma_load_2d(st, &tmap_a, &full[s], kt * GEMM_SLAB, ya);
+        tma_load_2d(st + GEMM_A_BYTES, &tmap_b, &full[s], kt * GEMM_SLAB, yb);
+        bulk_load(st + GEMM_A_BYTES + GEMM_B_BYTES, sfa_g, ncv * 512, &full[s]);
+        bulk_load(st + GEMM_A_BYTES + GEMM_B_BYTES + GEMM_SFA_BYTES, sfb_g, ncv * 512, &full[s]);
+        if (two_b) bulk_load(st + GEMM_A_BYTES + GEMM_B_BYTES + GEMM_SFA_BYTES + NC * 512, sfb_g + sfb_tile1, ncv * 512, &full[s]);
+        sfa_g += NC * 512;
+        sfb_g += NC * 512;
+        left -= NC;
         issued = kt + 1;
+        if (++s == GEMM_STAGES) { s = 0; e_par ^= 1; }
       }
       if (!ok) {
         // unwind: let the copies already in flight land before the CTA's shared memory goes away
@@ -155,46 +161,61 @@ gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      uint32_t idesc;
-      if (p.mode == 0) idesc = idesc_block_scaled(p.a_fmt, p.b_fmt, GEMM_BM, GEMM_BN, 1);
-      else if (p.mode == 1) idesc = idesc_block_scaled(1, 1, GEMM_BM, GEMM_BN, 1);
-      else idesc = idesc_block_scaled(1, 1, GEMM_BM, GEMM_BN, 0);
+      uint32_t idj[4];                              // instruction descriptors of the four instructions of a stage
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (MODE == 0) idj[j] = idesc_with_sf_id(idesc_block_scaled(p.a_fmt, p.b_fmt, GEMM_BM, GEMM_BN, 1), j, j);
+        else if (MODE == 1) idj[j] = idesc_with_sf_id(idesc_block_scaled(1, 1, GEMM_BM, GEMM_BN, 1), (j & 1) * 2, (j & 1) * 2);
+        else idj[j] = idesc_block_scaled(1, 1, GEMM_BM, GEMM_BN, 0);
+      }
+      // descriptors of stage 0; a stage further on adds its byte offset >> 4 to the address field
+      const uint64_t adesc0 = sdesc_kmajor_sw128(smem_u32(smem)), bdesc0 = sdesc_kmajor_sw128(smem_u32(smem + GEMM_A_BYTES));
+      const uint64_t sfdesc0 = sdesc_sf_tile(smem_u32(smem + GEMM_A_BYTES + GEMM_B_BYTES));
+      constexpr uint64_t STAGE_STEP = GEMM_STAGE_BYTES >> 4, SFB_STEP = GEMM_SFA_BYTES >> 4, TILE_STEP = 512 >> 4;
       bool ok = true;
-      for (int kt = 0; kt < KT && ok; ++kt) {
-        const int s = kt % GEMM_STAGES;
-        ok = mbar_wait(&full[s], (kt / GEMM_STAGES) & 1, p.status, KS_TIMEOUT_TMA);
+      int s = 0, left = p.nchunks;
+      uint32_t f_par = 0, set = 0;
+      for (int kt = 0; kt < KT; ++kt) {
+        ok = mbar_wait(&full[s], f_par, p.status, KS_TIMEOUT_TMA);
         if (!ok) break;
         tc_fence_after();
-        uint8_t* st = smem + s * GEMM_STAGE_BYTES;
-        const uint32_t a_addr = smem_u32(st), b_addr = smem_u32(st + GEMM_A_BYTES);
-        const uint32_t sfa_s = smem_u32(st + GEMM_A_BYTES + GEMM_B_BYTES);
-        const uint32_t sfb_s = sfa_s + GEMM_SFA_BYTES;
-        const uint32_t sf_set = tmem + GEMM_SF_COL0 + (kt & 1) * GEMM_SF_SET_STRIDE;
-        const uint32_t sfa_t = sf_set, sfb_t = sf_set + 16;
-        const int c0 = kt * nc_stage;
-        const int ncv = min(nc_stage, p.nchunks - c0);
-        for (int c = 0; c < ncv; ++c) {
-          tc_cp_32x128b_warpx4(sfa_t + 4 * c, sdesc_sf_tile(sfa_s + c * 512));
-          tc_cp_32x128b_warpx4(sfb_t + 8 * c, sdesc_sf_tile(sfb_s + c * 512));
-          tc_cp_32x128b_warpx4(sfb_t + 8 * c + 4, sdesc_sf_tile(sfb_s + (nc_stage + c) * 512));
-        }
-        const int k_left = p.K - kt * k_stage;
-        const int nmma = min(k_stage, k_left + k_mma - 1) / k_mma;   // instructions with any valid K
-        const uint64_t adesc = sdesc_kmajor_sw128(a_addr), bdesc = sdesc_kmajor_sw128(b_addr);
-        for (int j = 0; j < nmma; ++j) {
-          const uint64_t ad = adesc + (uint64_t)(j * 2);   // +32 bytes of K per instruction (>>4)
-          const uint64_t bd = bdesc + (uint64_t)(j * 2);
-          const uint32_t acc = (kt > 0 || j > 0) ? 1u : 0u;
-          if (p.mode == 0) {
-            mma_mxf8f6f4(tmem, ad, bd, idesc_with_sf_id(idesc, j, j), sfa_t, sfb_t, acc);
-          } else if (p.mode == 1) {
-            const int c = j >> 1, id = (j & 1) * 2;
-            mma_mxf4(tmem, ad, bd, idesc_with_sf_id(idesc, id, id), sfa_t + 4 * c, sfb_t + 8 * c, acc);
-          } else {
-            mma_nvf4(tmem, ad, bd, idesc, sfa_t + 4 * j, sfb_t + 8 * j, acc);
+        const uint64_t ad = adesc0 + (uint64_t)s * STAGE_STEP, bd = bdesc0 + (uint64_t)s * STAGE_STEP;
+        const uint64_t sfa_d = sfdesc0 + (uint64_t)s * STAGE_STEP, sfb_d = sfa_d + SFB_STEP;
+        const uint32_t sfa_t = tmem + GEMM_SF_COL0 + set * GEMM_SF_SET_STRIDE, sfb_t = sfa_t + 16;
+        if (left >= NC) {
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+            tc_cp_32x128b_warpx4(sfa_t + 4 * c, sfa_d + c * TILE_STEP);
+            tc_cp_32x128b_warpx4(sfb_t + 8 * c, sfb_d + c * TILE_STEP);
+            if (two_b) tc_cp_32x128b_warpx4(sfb_t + 8 * c + 4, sfb_d + (NC + c) * TILE_STEP);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t acc = (kt > 0 || j > 0) ? 1u : 0u;
+            const int c = j / MPC;                  // scale tile of this instruction
+            if (MODE == 0) mma_mxf8f6f4(tmem, ad + 2 * j, bd + 2 * j, idj[j], sfa_t, sfb_t, acc);
+            else if (MODE == 1) mma_mxf4(tmem, ad + 2 * j, bd + 2 * j, idj[j], sfa_t + 4 * c, sfb_t + 8 * c, acc);
+            else mma_nvf4(tmem, ad + 2 * j, bd + 2 * j, idj[j], sfa_t + 4 * c, sfb_t + 8 * c, acc);
+          }
+        } else {
+          // the last stage of a K that is not a multiple of the stage: fewer scale tiles, fewer instructions
+          for (int c = 0; c < left; ++c) {
+            tc_cp_32x128b_warpx4(sfa_t + 4 * c, sfa_d + c * TILE_STEP);
+            tc_cp_32x128b_warpx4(sfb_t + 8 * c, sfb_d + c * TILE_STEP);
+            if (two_b) tc_cp_32x128b_warpx4(sfb_t + 8 * c + 4, sfb_d + (NC + c) * TILE_STEP);
+          }
+          for (int j = 0; j < left * MPC; ++j) {
+            const uint32_t acc = (kt > 0 || j > 0) ? 1u : 0u;
+            const int c = j / MPC;
+            if (MODE == 0) mma_mxf8f6f4(tmem, ad + 2 * j, bd + 2 * j, idj[j & 3], sfa_t, sfb_t, acc);
+            else if (MODE == 1) mma_mxf4(tmem, ad + 2 * j, bd + 2 * j, idj[j & 3], sfa_t + 4 * c, sfb_t + 8 * c, acc);
+            else mma_nvf4(tmem, ad + 2 * j, bd + 2 * j, idj[j & 3], sfa_t + 4 * c, sfb_t + 8 * c, acc);
           }
         }
         tc_commit(&empty[s]);
+        left -= NC;
+        set ^= 1;
+        if (++s == GEMM_STAGES) { s = 0; f_par ^= 1; }
       }
       if (ok) tc_commit(accum_full);
     }
@@ -257,13 +278,14 @@ static int launch_gemm(const void* a, const void* a_scale, const void* b, const 
   p.sfa = (const uint8_t*)a_scale; p.sfb = (const uint8_t*)b_scale; p.nchunks = K / chunk;
   p.c = c; p.ldc = ldc; p.out_dtype = out_dtype; p.alpha = alpha; p.status = status;
   // per-device attribute of the kernel: set before every launch, so that any device and any thread may call first
-  if (cudaFuncSetAttribute(gemm_block_scaled_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess) {
+  auto kernel = mode == 0 ? gemm_block_scaled_kernel<0> : (mode == 1 ? gemm_block_scaled_kernel<1> : gemm_block_scaled_kernel<2>);
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM) != cudaSuccess) {
     cudaGetLastError();
     return set_error(MPSA_ERR_LAUNCH, "gemm_block_scaled: cannot reserve %d bytes of shared memory", GEMM_SMEM);
   }
   dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + GEMM_BN - 1) / GEMM_BN, batch);
   if (grid.y > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "gemm_block_scaled: N too large");
-  gemm_block_scaled_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ta, tb, p);
+  kernel<<<grid, GEMM_THREADS, GEMM_SMEM, (cudaStream_t)stream>>>(ta, tb, p);
   return check_launch("gemm_block_scaled");
 }
 
