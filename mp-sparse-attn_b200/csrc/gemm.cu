@@ -221,21 +221,51 @@ gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
+    // A thread holds 32 consecutive columns of ONE row, so storing from registers sends 16-byte pieces to 32 different
+    // rows per instruction (measured: 6.3k of a CTA's 58k cycles at 8192^3 with bf16 output).  The operand stages are
+    // idle by now (every MMA has completed), so a warp parks its 32 rows there and writes whole rows instead.
     const int q = warp & 3;                       // TMEM lane quarter this warp may touch
     const bool ok = __all_sync(0xffffffffu, mbar_wait(accum_full, 0, p.status, KS_TIMEOUT_MMA));
     tc_fence_after();
     if (ok) {
-      const int row = m0 + q * 32 + lane;
-      for (int ch = 0; ch < GEMM_BN / 32; ++ch) {
-        uint32_t r[32];
-        tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + ch * 32, r);
-        tmem_ld_wait();
-        const int col = n0 + ch * 32;
-        if (row < p.M && col < p.N) {
+      const int esz = p.out_dtype == 0 ? 4 : (p.out_dtype == 3 ? 1 : 2);
+      const int row0 = m0 + q * 32;
+      const int rows_valid = min(32, p.M - row0);
+      uint8_t* cbase = reinterpret_cast<uint8_t*>(p.c) + (((long long)blockIdx.z * p.M + row0) * p.ldc + n0) * esz;
+      const long long row_bytes = p.ldc * esz;
+      const bool whole_rows = (n0 + GEMM_BN <= p.N) && ((uintptr_t)cbase % 16 == 0) && (row_bytes % 16 == 0);
+      if (whole_rows) {
+        const int pitch = GEMM_BN * esz + 16;     // 16 bytes of padding: the 16-byte pieces of 8 lanes fall into 32 banks
+        uint8_t* stg = smem + (size_t)q * 32 * pitch;
+        for (int ch = 0; ch < GEMM_BN / 32; ++ch) {
+          uint32_t r[32];
+          tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + ch * 32, r);
+          tmem_ld_wait();
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-          store_row32(p.c, ((long long)blockIdx.z * p.M + row) * p.ldc + col, p.out_dtype, v, min(32, p.N - col));
+          store_row32(stg + (size_t)lane * pitch, ch * 32, p.out_dtype, v, 32);
+        }
+        __syncwarp();
+        const int line = GEMM_BN * esz;           // bytes of a row of the tile
+        for (int r = 0; r < rows_valid; ++r) {
+          const uint8_t* src = stg + (size_t)r * pitch;
+          uint8_t* dst = cbase + r * row_bytes;
+          for (int o = lane * 16; o < line; o += 512) *reinterpret_cast<uint4*>(dst + o) = *reinterpret_cast<const uint4*>(src + o);
+        }
+      } else {
+        const int row = row0 + lane;
+        for (int ch = 0; ch < GEMM_BN / 32; ++ch) {
+          uint32_t r[32];
+          tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + ch * 32, r);
+          tmem_ld_wait();
+          const int col = n0 + ch * 32;
+          if (row < p.M && col < p.N) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+            store_row32(p.c, ((long long)blockIdx.z * p.M + row) * p.ldc + col, p.out_dtype, v, min(32, p.N - col));
+          }
         }
       }
     }
