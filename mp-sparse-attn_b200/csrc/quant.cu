@@ -126,29 +126,56 @@ __device__ __forceinline__ uint32_t cvt_fp8x4_regs(float y0, float y1, float y2,
 // the second half of the same row; D <= 128.
 // W8 / W4: which formats this instance can produce (a caller that wants one format gets a kernel without the other's
 // arithmetic and registers; more CTAs then fit an SM, i.e. more loads in flight).
+// 16 elements as they arrive from memory (two or four 16-byte pieces), unpacked to fp32 when their tile's turn comes:
+// a CTA asks for all its tiles' elements up front and holds them packed (8 registers per run of bf16 / fp16).
+template <typename T> struct Raw16 { uint4 q[sizeof(T) == 4 ? 4 : 2]; };
+template <typename T> __device__ __forceinline__ void load_raw(const T* p, Raw16<T>& r) {
+#pragma unroll
+  for (int j = 0; j < (sizeof(T) == 4 ? 4 : 2); ++j) r.q[j] = __ldg(reinterpret_cast<const uint4*>(p) + j);
+}
+__device__ __forceinline__ void unpack16(const Raw16<__nv_bfloat16>& r, float (&v)[16]) {
+  const uint32_t w[8] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void unpack16(const Raw16<__half>& r, float (&v)[16]) {
+  uint32_t w[8] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<__half2*>(&w[i]));
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void unpack16(const Raw16<float>& r, float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[4 * i] = __uint_as_float(r.q[i].x); v[4 * i + 1] = __uint_as_float(r.q[i].y);
+    v[4 * i + 2] = __uint_as_float(r.q[i].z); v[4 * i + 3] = __uint_as_float(r.q[i].w);
+  }
+}
+// tiles along L per CTA: twice the loads in flight per SM, half the CTA turn-overs (one tile where the registers are
+// needed otherwise: fp32 input, whose packed runs are twice as large, and the rotary variant, which unpacks two runs at once)
+template <typename T, bool ROPE> __host__ __device__ constexpr int mx_tiles_per_cta() { return (sizeof(T) == 4 || ROPE) ? 1 : 2; }
+
 template <typename T, bool ROPE, bool W8, bool W4>
 __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantParams p) {
-  __shared__ __align__(16) uint8_t sf8[512];
-  __shared__ __align__(16) uint8_t sf4[512];
-  __shared__ __align__(16) uint8_t rm8[512];      // row-major scale codes of the tile: [row][k-block & 3]
-  __shared__ __align__(16) uint8_t rm4[512];
-  const int tile_l = blockIdx.x, tile_d = blockIdx.y, bh = blockIdx.z;
+  constexpr int TPC = mx_tiles_per_cta<T, ROPE>();
+  __shared__ __align__(16) uint8_t sf8s[TPC][512];
+  __shared__ __align__(16) uint8_t sf4s[TPC][512];
+  __shared__ __align__(16) uint8_t rm8s[TPC][512];  // row-major scale codes of the tile: [row][k-block & 3]
+  __shared__ __align__(16) uint8_t rm4s[TPC][512];
+  const int tile_d = blockIdx.y, bh = blockIdx.z;
   const int b = bh / p.H, h = bh % p.H;
-  const int row0 = tile_l * 128, col0 = tile_d * 128;
+  const int col0 = tile_d * 128;
   const int tid = threadIdx.x;
   const bool want8 = W8 && (p.fp8_codes || p.fp8_scales_rm || p.fp8_scales_tiled);
   const bool want4 = W4 && (p.fp4_codes_unpacked || p.fp4_codes_packed || p.fp4_scales_rm || p.fp4_scales_tiled);
 
-  // padding of the scale tile: rows beyond L and k-blocks beyond D carry E8M0 1.0
-  if (tid < 256) {
-    reinterpret_cast<uint16_t*>(sf8)[tid] = 0x7f7f;
-    reinterpret_cast<uint16_t*>(sf4)[tid] = 0x7f7f;
-  }
-  __syncthreads();
-
   const T* xb = reinterpret_cast<const T*>(p.x) + (long long)b * p.xs_b + (long long)h * p.xs_h;
-  float v[kMxRuns][16];
-  bool live[kMxRuns];
   int rls[kMxRuns], cols[kMxRuns];              // row inside the tile and first column of each run
 #pragma unroll
   for (int i = 0; i < kMxRuns; ++i) {
@@ -162,12 +189,38 @@ __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantPara
       cols[i] = col0 + (g & 7) * 16;
     }
   }
+  // every load of the CTA goes out before any arithmetic
+  Raw16<T> raw[TPC][kMxRuns];
+#pragma unroll
+  for (int tt = 0; tt < TPC; ++tt) {
+#pragma unroll
+    for (int i = 0; i < kMxRuns; ++i) {
+      const int r = (blockIdx.x * TPC + tt) * 128 + rls[i];
+      if ((rls[i] < 128) && (r < p.L) && (cols[i] < p.D)) load_raw<T>(xb + (long long)r * p.xs_l + cols[i], raw[tt][i]);
+    }
+  }
+  // padding of the scale tiles: rows beyond L and k-blocks beyond D carry E8M0 1.0
+  for (int i = tid; i < TPC * 256; i += kMxThreads) {
+    reinterpret_cast<uint16_t*>(&sf8s[0][0])[i] = 0x7f7f;
+    reinterpret_cast<uint16_t*>(&sf4s[0][0])[i] = 0x7f7f;
+  }
+  __syncthreads();
+  const int nblk = p.D >> 5;
+  const bool scaled = (p.s != 1.0f);
+#pragma unroll
+  for (int tt = 0; tt < TPC; ++tt) {
+  const int tile_l = blockIdx.x * TPC + tt;
+  const int row0 = tile_l * 128;
+  if (row0 >= p.L) break;
+  uint8_t* sf8 = sf8s[tt]; uint8_t* sf4 = sf4s[tt]; uint8_t* rm8 = rm8s[tt]; uint8_t* rm4 = rm4s[tt];
+  float v[kMxRuns][16];
+  bool live[kMxRuns];
 #pragma unroll
   for (int i = 0; i < kMxRuns; ++i) {
     const int r = row0 + rls[i], c = cols[i];
     live[i] = (rls[i] < 128) && (r < p.L) && (c < p.D);
     if (live[i]) {
-      load16<T>(xb + (long long)r * p.xs_l + c, v[i]);
+      unpack16(raw[tt][i], v[i]);
       if (p.center) {
         // "smooth K": k - mean over the sequence (ours/mxfp_attn_kernel.py:33-34), an elementwise op in the input dtype
         const float4* cen = reinterpret_cast<const float4*>(p.center + ((long long)b * p.H + h) * p.D + c);
@@ -202,8 +255,6 @@ __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantPara
       }
     }
   }
-  const int nblk = p.D >> 5;
-  const bool scaled = (p.s != 1.0f);
 #pragma unroll
   for (int i = 0; i < kMxRuns; ++i) {
     const int rl = rls[i];                  // row inside the tile
@@ -276,8 +327,13 @@ __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantPara
       }
     }
   }
+  }  // tiles of the CTA
   __syncthreads();
   // one coalesced 512-byte store per scale tile
+  for (int tt = 0; tt < TPC; ++tt) {
+  const int tile_l = blockIdx.x * TPC + tt, row0 = tile_l * 128;
+  if (row0 >= p.L) break;
+  uint8_t* sf8 = sf8s[tt]; uint8_t* sf4 = sf4s[tt]; uint8_t* rm8 = rm8s[tt]; uint8_t* rm4 = rm4s[tt];
   const long long ntl = (p.L + 127) >> 7, ntd = (p.D + 127) >> 7;
   const long long tile_lin = (((long long)b * p.H + h) * ntl + tile_l) * ntd + tile_d;
   if (tid < 32) {
@@ -303,6 +359,7 @@ __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantPara
       }
     }
   }
+  }  // tiles of the CTA
 }
 
 // ---- per-32 int8 quantizer (ours/quant_mxint8.py:21-58) ------------------------------------
@@ -637,7 +694,8 @@ static int quant_mx_launch(const void* x, int in_dtype, int B, int H, int L, int
   p.fp8_scales_rm = (uint8_t*)fp8_scales_rm; p.fp4_scales_rm = (uint8_t*)fp4_scales_rm;
   p.fp4_codes_packed = (uint8_t*)fp4_codes_packed;
   p.fp8_scales_tiled = (uint8_t*)fp8_scales_tiled; p.fp4_scales_tiled = (uint8_t*)fp4_scales_tiled;
-  dim3 grid((L + 127) / 128, (D + 127) / 128, B * H);
+  const int tpc = (in_dtype == 2 || rope_cos) ? 1 : 2;     // mx_tiles_per_cta of the instance launched below
+  dim3 grid(((L + 127) / 128 + tpc - 1) / tpc, (D + 127) / 128, B * H);
   if (grid.y > 65535 || grid.z > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "quant_mx: B*H and D/128 must be below 65536");
   cudaStream_t st = (cudaStream_t)stream;
   const bool w8 = p.fp8_codes || p.fp8_scales_rm || p.fp8_scales_tiled;
