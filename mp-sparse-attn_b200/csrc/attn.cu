@@ -111,6 +111,9 @@ struct AttnParams {
   uint8_t* map_rw;                   // the map again, writable (same buffer and strides as `map`)
   float* stat_out;                   // optional [B,Hq,nq,nk]: the statistic of every MXFP4 tile visited
   int map_mode;                      // 0: visit every non-skipped cell; 1: second pass (see above)
+  const int* redo_if;                // second pass only: when this word is non-zero (the first pass left its fixed reference's
+                                     // headroom, its output is void) the pass visits EVERY non-skipped cell instead, marked
+                                     // ones in MXFP8, and writes the result without merging: the exact forward over the final map
   const int* skip_if;                // when given: the kernel does nothing if this word is non-zero
   int* range_flag;                   // LAZY kernels: set to 1 when a score leaves the fixed reference's headroom
   const int* run_if;                 // when given: the kernel does nothing unless this word is non-zero
@@ -463,6 +466,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
   const uint8_t* map_glob = p.map + (long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk;
+  const bool redo = p.redo_if && *(volatile const int*)p.redo_if != 0;
+  const int map_mode = redo ? 2 : p.map_mode;
+  const void* const acc_in = redo ? nullptr : p.acc_in;
+  if (map_mode == 1) {
+    // second pass: about half of the rows have no marked cell (measured on the Llama-shaped data); such a CTA leaves
+    // before it has set up barriers or TMEM, and the first pass's result stands
+    bool any = false;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) any |= (map_glob[i] == TILE_AGAIN);
+    if (!__syncthreads_or(any)) {
+      if (p.lse && p.lse_in && threadIdx.x < ATT_BM && qi * ATT_BM + (int)threadIdx.x < p.S) {
+        const long long r = (long long)(b * p.Hq + h) * p.S + qi * ATT_BM + threadIdx.x;
+        p.lse[r] = p.lse_in[r];                     // the caller wants the log-denominators in another buffer
+      }
+      return;
+    }
+  }
   for (int i = threadIdx.x; i < nk; i += blockDim.x) smem[ATT_OFF_MAP + i] = map_glob[i];     // nk <= ATT_MAP_SMEM (host check)
   if (threadIdx.x < 128) reinterpret_cast<float*>(smem + ATT_OFF_MROW)[2 * 128 + threadIdx.x] = -INFINITY;   // reference hint
   if (threadIdx.x < 4) dec[threadIdx.x] = -1;       // no tile decided yet
@@ -488,11 +507,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     for (int i0 = 0; i0 < nk; i0 += 32) {
       const int i = i0 + lane;
       const uint8_t c = i < nk ? smem[ATT_OFF_MAP + i] : (uint8_t)TILE_SKIP;
-      const bool visit = p.map_mode == 1 ? (c == TILE_AGAIN) : (c != TILE_SKIP);
+      const bool visit = map_mode == 1 ? (c == TILE_AGAIN) : (c != TILE_SKIP);
       const uint32_t vis = __ballot_sync(0xffffffffu, visit);
       if (visit) {
         vl[base + __popc(vis & ((1u << lane) - 1u))] = (uint16_t)(i | ((c == TILE_FP8 || c == TILE_AGAIN) ? 0x8000 : 0));
-        if (p.map_mode == 1) p.map_rw[(long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk + i] = TILE_FP8;
+        if (map_mode != 0 && c == TILE_AGAIN) p.map_rw[(long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk + i] = TILE_FP8;
       }
       base += __popc(vis);
     }
@@ -503,7 +522,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const int nv = *n_visit;                          // number of tiles to visit (0: the row has none)
-  const bool idle = p.map_mode == 1 && nv == 0;     // second pass, nothing marked in this row: the first pass's result stands
+  const bool idle = map_mode == 1 && nv == 0;     // second pass, nothing marked in this row: the first pass's result stands
 
   uint8_t* sQ8 = smem + ATT_OFF_Q8;
   uint8_t* sQ4 = smem + ATT_OFF_Q4;
@@ -1111,7 +1130,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       const long long o_off = ((long long)(b * p.Hq + h) * p.S + m_glob) * p.D;
       float lse_row = (t > 0 && l_tot > 0.0f) ? m_final + log2f(l_tot) : -INFINITY;
       float w_prev = 0.0f;                          // weight of the earlier partial result (merge mode)
-      if (p.acc_in && m_glob < p.S) {
+      if (acc_in && m_glob < p.S) {
         // two normalised partial results over disjoint key sets combine with weights 2^(lse_i - lse),
         // lse = log2(2^lse_a + 2^lse_b); every thread of a row computes the same numbers
         const float la = p.lse_in[(long long)(b * p.Hq + h) * p.S + m_glob];
@@ -1139,10 +1158,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
           float val[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) val[i] = __uint_as_float(o[i]) * inv_l;
-          if (p.acc_in) {
+          if (acc_in) {
             // the earlier partial result of the same elements (it may be the very buffer written below)
             if (p.acc_dtype == 0) {
-              const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.acc_in) + o_off + c * 32);
+              const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(acc_in) + o_off + c * 32);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const float4 a = src[i];
@@ -1152,7 +1171,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
                 val[4 * i + 3] = fmaf(a.w, w_prev, val[4 * i + 3]);
               }
             } else {
-              const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.acc_in) + o_off + c * 32);
+              const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(acc_in) + o_off + c * 32);
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 const uint4 a = src[i];
@@ -1404,7 +1423,7 @@ int prepare_attn(AttnLaunch& L, const void* q8, const void* q8_sf, const void* q
   p.out = out; p.out_dtype = out_dtype; p.lse = (float*)lse; p.status = status;
   p.range_flag = nullptr; p.run_if = nullptr;
   p.acc_in = acc_in; p.lse_in = (const float*)lse_in; p.acc_dtype = acc_dtype;
-  p.tau = 0.0f; p.map_rw = nullptr; p.stat_out = nullptr; p.map_mode = 0; p.skip_if = nullptr;
+  p.tau = 0.0f; p.map_rw = nullptr; p.stat_out = nullptr; p.map_mode = 0; p.skip_if = nullptr; p.redo_if = nullptr;
   if (Hq > 65535 || B > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: Hq and B must be below 65536");
   return MPSA_OK;
 }
@@ -1499,11 +1518,11 @@ extern "C" int mpsa_attn_fwd_routed(const void* q8, const void* q8_sf, const voi
                                     int out_dtype, void* lse, void* lse_final, void* stat, void* stat_scratch, int B, int Hq,
                                     int Hkv, int S, int Skv, int D, int Skv_pad, int fp8_fmt, int stages, int* range_flag,
                                     int* status, void* stream) {
-  if (!map || !lse || !stat || !stat_scratch || !range_flag) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: null pointer");
-  if (stages < 1 || stages > 15) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: stages is a mask of 1 (band map), 2 (first pass), 4 (fallback), 8 (second pass)");
+  if (!map || !lse || !range_flag) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: null pointer");
+  (void)stat_scratch;
+  if (stages < 1 || stages > 15) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: stages is a mask of 1 (band map), 2 (first pass), 8 (second pass)");
   if (band < 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: band must be at least 1");
   if (lse_final == lse) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: lse_final must be another buffer than lse (or null)");
-  if (((uintptr_t)stat_scratch % 16)) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: stat_scratch must be 16-byte aligned");
   const int nq = (S + ATT_BM - 1) / ATT_BM, nk = (Skv + ATT_BN - 1) / ATT_BN;
   const long long msh = (long long)nq * nk, msb = msh * Hq;
   AttnLaunch L;
@@ -1522,22 +1541,15 @@ extern "C" int mpsa_attn_fwd_routed(const void* q8, const void* q8_sf, const voi
   // 2. first pass: router inside, promoted tiles left out
   if (stages & 2) {
     AttnParams pa = L.p;
-    pa.tau = tau; pa.map_rw = (uint8_t*)map; pa.stat_out = nullptr; pa.range_flag = range_flag;
+    pa.tau = tau; pa.map_rw = (uint8_t*)map; pa.stat_out = (float*)stat; pa.range_flag = range_flag;
     if (int rc = launch_attn<2, 2, 1, 0, 1, 1>(grid, st, maps, pa)) return rc;
   }
-  // fallback, conditional on *range_flag: statistic, map and the exact kernel over everything
-  if (stages & 4) {
-    if (int rc = launch_route_stat(q4, q4_sf, k4, k4_sf, stat, stat_scratch, B, Hq, Hkv, S, Skv, 1, status, range_flag, stream)) return rc;
-    if (int rc = launch_route_online(map, stat, B, Hq, S, Skv, 1, band, tau, 0.0f, 0, range_flag, stream)) return rc;
-    AttnParams pf = L.p;
-    pf.run_if = range_flag;
-    if (lse_final) pf.lse = (float*)lse_final;
-    if (int rc = launch_attn<2, 2, 1, 0, 0>(grid, st, maps, pf)) return rc;
-  }
-  // 3. second pass: the marked tiles in MXFP8, merged in place
+  // 3. second pass (the exact kernel): the marked tiles in MXFP8, merged in place.  If the first pass raised *range_flag
+  // its output is void (its map is not: a slice maximum does not depend on the reference), and the same launch computes
+  // the whole forward over the final map instead, so the fallback costs no launch of its own.  (stages bit 4 is unused.)
   if (!(stages & 8)) return MPSA_OK;
   AttnParams pb = L.p;
-  pb.map_mode = 1; pb.map_rw = (uint8_t*)map; pb.skip_if = range_flag;
+  pb.map_mode = 1; pb.map_rw = (uint8_t*)map; pb.redo_if = range_flag;
   pb.acc_in = out; pb.acc_dtype = out_dtype; pb.lse_in = (const float*)lse; pb.lse = (float*)lse_final;
   return launch_attn<2, 2, 1, 0, 0>(grid, st, maps, pb);
 }

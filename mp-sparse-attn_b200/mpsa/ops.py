@@ -578,12 +578,14 @@ def attention_forward_quantized(qq: QuantizedOperand, kq: QuantizedOperand, vt, 
 
 def attention_forward_routed(qq: QuantizedOperand, kq: QuantizedOperand, vq: "QuantizedV", B: int, Hq: int, Hkv: int, S: int,
                              Skv: int, D: int, *, band: int = 1, tau: float = 1.0, out_dtype: torch.dtype = torch.bfloat16,
-                             check: bool = False, return_map: bool = False, return_lse: bool = False, stages: int = 15):
+                             check: bool = False, return_map: bool = False, return_lse: bool = False, stages: int = 15,
+                             return_stat: bool = False):
     """The causal forward with the online router inside it (quantised P.V, MXFP4/MXFP8 operands): no stand-alone
     statistic pass.  Tiles the router promotes are left out of the first pass and done in MXFP8 by a second one that
     merges into the output in place.  Same precision map as precision_map_online(router_statistic(...), tau=tau).
-    stages: mask of the launches to make (1 band map, 2 first pass, 4 conditional fallback, 8 second pass) - anything but
-    15 leaves the output incomplete and is for timing a stage alone."""
+    stages: mask of the launches to make (1 band map, 2 first pass, 8 second pass; 4 is ignored) - anything but 15 leaves
+    the output incomplete and is for timing a stage alone.  return_stat: also the router statistic of the MXFP4 tiles the
+    first pass visited (fp32 [B,Hq,nq,nk], zero elsewhere)."""
     if not isinstance(vq, QuantizedV):
         raise ValueError("the routed forward needs V quantised along the sequence (quantize_v_seq)")
     if qq.fp4_kind != "mxfp4" or kq.fp4_kind != "mxfp4":
@@ -604,8 +606,7 @@ def attention_forward_routed(qq: QuantizedOperand, kq: QuantizedOperand, vq: "Qu
     out = torch.empty((B, Hq, S, D), dtype=out_dtype, device=dev)
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
     lse_final = torch.empty((B, Hq, S), dtype=torch.float32, device=dev) if return_lse else None
-    stat = torch.empty((B, Hq, nq, nk), dtype=torch.float32, device=dev)
-    scratch = torch.empty((B, Hq, nq, nk, 4), dtype=torch.float32, device=dev)
+    stat = torch.zeros((B, Hq, nq, nk), dtype=torch.float32, device=dev) if return_stat else None
     flag = torch.zeros(1, dtype=torch.int32, device=dev)
     global _last_range_flag
     _last_range_flag = flag
@@ -617,7 +618,7 @@ def attention_forward_routed(qq: QuantizedOperand, kq: QuantizedOperand, vq: "Qu
             kq.fp8.data_ptr(), kq.fp8_sf.data_ptr(), kq.fp4.data_ptr(), kq.fp4_sf.data_ptr(),
             vq.vt8.data_ptr(), vq.v8_sf.data_ptr(), vq.vt4.data_ptr(), vq.v4_sf.data_ptr(),
             pm.data_ptr(), int(band), float(tau), out.data_ptr(), _OUT_DTYPE[out_dtype], lse.data_ptr(), _ptr(lse_final),
-            stat.data_ptr(), scratch.data_ptr(), B, Hq, Hkv, S, Skv, D, skv_pad, _FP8_DESC[qq.fp8_elem], int(stages), flag.data_ptr(),
+            _ptr(stat), None, B, Hq, Hkv, S, Skv, D, skv_pad, _FP8_DESC[qq.fp8_elem], int(stages), flag.data_ptr(),
             st.data_ptr(), _stream())
     _lib.check(rc)
     if check:
@@ -627,6 +628,8 @@ def attention_forward_routed(qq: QuantizedOperand, kq: QuantizedOperand, vq: "Qu
         res += (pm,)
     if return_lse:
         res += (lse_final,)
+    if return_stat:
+        res += (stat,)
     return res[0] if len(res) == 1 else res
 
 

@@ -64,8 +64,9 @@ def test_one_call_form_uses_the_router_inside_and_matches_the_stand_alone_form()
 
 
 def test_fallback_when_scores_leave_the_fixed_reference():
-    """Later keys 2^64 and more above the first tile's maximum: the first pass flags it, the stand-alone exact path runs
-    behind it, the second pass does nothing; the result still matches the oracle."""
+    """Later keys 2^64 and more above the first tile's maximum: the first pass flags it, and the second launch recomputes
+    the whole output with the exact kernel over the final map instead of merging; the result still matches the oracle,
+    and the map is the one the stand-alone router gives."""
     import mpsa
     from mpsa import ops
     q, k, v = O.make_qkv(9, 1, 4, 2, 1024, 128, outliers=3)
@@ -77,6 +78,8 @@ def test_fallback_when_scores_leave_the_fixed_reference():
                                            check=True, return_map=True)
     assert int(ops._last_range_flag.item()) == 1
     assert set(pm.unique().tolist()) <= {0, 1, 2}
+    stat = ops.router_statistic(qq, kq, 1, 4, 2, 1024, 1024, causal=True, check=True)
+    assert torch.equal(pm, ops.precision_map_online(stat, 1024, 1024, causal=True, band=1, tau=1.1))
     ref = O.attention_mxfp(q, k2, v, causal=True, prec_map=pm.cpu(), pv_mode="requant")
     m = O.parity_metrics(out.cpu(), ref)
     assert m["cos"] >= COS_MIN and m["rel_l2"] <= REL_L2_MAX, m
