@@ -70,10 +70,14 @@ constexpr int ATT_OFF_XSUM = ATT_OFF_XMAX + ATT_MAX_WG * 2 * ATT_MAX_SPLIT * 128
 constexpr int ATT_OFF_MROW = ATT_OFF_XSUM + ATT_MAX_WG * ATT_MAX_SPLIT * 128 * 4;       // float [3][128] running row max: per tile parity, and an unsynchronised hint
 constexpr int ATT_OFF_RMAX = ATT_OFF_MROW + 3 * 128 * 4;               // float [2 buffers][MAX_SPLIT][128]: slice maxima for the router
 constexpr int ATT_OFF_BAR = ATT_OFF_RMAX + 2 * ATT_MAX_SPLIT * 128 * 4;
-constexpr int ATT_OFF_MAP = ATT_OFF_BAR + 512;                        // this CTA's row of the precision map
+constexpr int ATT_BAR_BYTES = 1024;                                   // mbarriers, then the TMEM slot, the visit count and the router's words
+constexpr int ATT_NUM_BARS = 1 + 2 * ATT_KSTAGES + 2 * ATT_VSLOTS_MAX + 6 + ATT_MAX_WG * 8 + 8 + 4 + 6;
+static_assert(ATT_NUM_BARS * 8 + 4 + 4 + 16 <= ATT_BAR_BYTES, "the barrier block does not fit its share of shared memory");
+constexpr int ATT_OFF_MAP = ATT_OFF_BAR + ATT_BAR_BYTES;              // this CTA's row of the precision map
 constexpr int ATT_MAP_SMEM = 8192;                                    // longest row: 8192 key tiles (1M keys)
 constexpr int ATT_OFF_VLIST = ATT_OFF_MAP + ATT_MAP_SMEM;             // uint16 per visited tile
 constexpr int ATT_SMEM = ATT_OFF_VLIST + 2 * ATT_MAP_SMEM + 1024;
+static_assert(ATT_SMEM <= 232448, "more shared memory than a CTA can have");
 constexpr uint32_t ATT_TMEM_COLS = 512;
 constexpr uint32_t ATT_COL_S = 0, ATT_COL_O = 256, ATT_COL_SFQ8 = 384, ATT_COL_SFQ4 = 388, ATT_COL_SFK = 392;
 constexpr uint32_t ATT_COL_SFP = 400, ATT_COL_SFV = 408;
