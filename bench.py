@@ -41,8 +41,7 @@ import torch  # noqa: E402
 
 HQ, HKV, D = 32, 8, 128
 OUTLIERS = 5
-LAUNCHES_PER_STEP = 10     # quant Q, quant K, quant V, band map, first pass, second pass + the conditional fallback behind the
-                           # first pass (router statistic + its finish kernel, precision map, exact forward: they return at once)
+LAUNCHES_PER_STEP = 6      # quant Q, quant K, quant V, band map, first pass, second pass
 TAU = 1.1                  # online router: a tile is promoted to MXFP8 iff its statistic >= TAU x the first key tile's
 # DRAM bytes (read + written) of one launch of the fused forward at S=8192, from an ncu capture; every term of it
 # (Q, K, V codes and scales, the output) grows linearly with S
