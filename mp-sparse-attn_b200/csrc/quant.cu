@@ -362,6 +362,123 @@ __global__ void __launch_bounds__(kMxThreads, 2) quant_mx_kernel(const QuantPara
   }  // tiles of the CTA
 }
 
+// MXFP8 alone from 16-bit input, no rotary embedding, no centring: the case that has to run at memory speed.  Nothing is
+// unpacked to fp32 ahead of its use - the block maximum is taken on the packed 16-bit patterns (for non-negative
+// values their order as unsigned integers is their order as numbers, in bf16 and in fp16 alike), which leaves
+// registers for THREE tiles of packed loads in flight per CTA.  Same results as quant_mx_kernel: the maximum of the
+// rounded products |x|*s is the rounded product of the maximum (rounding is monotonic, s > 0).
+template <typename T> __device__ __forceinline__ float pattern_to_float(uint32_t h);
+template <> __device__ __forceinline__ float pattern_to_float<__nv_bfloat16>(uint32_t h) { return __uint_as_float(h << 16); }
+template <> __device__ __forceinline__ float pattern_to_float<__half>(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+template <typename T> __device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi);
+template <> __device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t w, float& lo, float& hi) {
+  lo = __uint_as_float(w << 16);
+  hi = __uint_as_float(w & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void unpack2<__half>(uint32_t w, float& lo, float& hi) {
+  const float2 f = __half22float2(*reinterpret_cast<__half2*>(&w));
+  lo = f.x;
+  hi = f.y;
+}
+constexpr int kMx8Tiles = 3;
+
+template <typename T>
+__global__ void __launch_bounds__(kMxThreads, 2) quant_mx8_kernel(const QuantParams p) {
+  constexpr int TPC = kMx8Tiles;
+  __shared__ __align__(16) uint8_t sf8s[TPC][512];
+  __shared__ __align__(16) uint8_t rm8s[TPC][512];
+  const int tile_d = blockIdx.y, bh = blockIdx.z;
+  const int b = bh / p.H, h = bh % p.H;
+  const int tid = threadIdx.x;
+  const int rl0 = tid >> 3;                      // rows rl0 and rl0 + 64 of a tile, 16 columns from c
+  const int c = tile_d * 128 + (tid & 7) * 16;
+  const T* xb = reinterpret_cast<const T*>(p.x) + (long long)b * p.xs_b + (long long)h * p.xs_h;
+  Raw16<T> raw[TPC][2];
+#pragma unroll
+  for (int tt = 0; tt < TPC; ++tt) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = (blockIdx.x * TPC + tt) * 128 + rl0 + 64 * i;
+      if (r < p.L && c < p.D) load_raw<T>(xb + (long long)r * p.xs_l + c, raw[tt][i]);
+    }
+  }
+  for (int i = tid; i < TPC * 256; i += kMxThreads) reinterpret_cast<uint16_t*>(&sf8s[0][0])[i] = 0x7f7f;   // padding: E8M0 1.0
+  __syncthreads();
+  const int nblk = p.D >> 5;
+  const bool scaled = (p.s != 1.0f);
+  const bool e4m3 = p.fp8_fmt == FMT_FP8_E4M3;
+#pragma unroll
+  for (int tt = 0; tt < TPC; ++tt) {
+    const int row0 = (blockIdx.x * TPC + tt) * 128;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int rl = rl0 + 64 * i, r = row0 + rl;
+      const bool live = r < p.L && c < p.D;
+      const uint4 qa = raw[tt][i].q[0], qb = raw[tt][i].q[1];
+      const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+      uint32_t m = 0;
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m = __vmaxu2(m, w[j] & 0x7fff7fffu);
+      }
+      m = max(m & 0xffffu, m >> 16);
+      float amax = pattern_to_float<T>(m);
+      if (scaled) amax = __fmul_rn(amax, p.s);
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      if (!live) continue;
+      const BlockScale bs = mx_block_scale(amax, e4m3 ? 8 : 7);
+      uint32_t o[4];
+      if (bs.zero) {
+        o[0] = o[1] = o[2] = o[3] = 0;            // the reference stores the NaN pattern of 0/0 here
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float x0, x1, x2, x3;
+          unpack2<T>(w[2 * j], x0, x1);
+          unpack2<T>(w[2 * j + 1], x2, x3);
+          if (scaled) { x0 = __fmul_rn(x0, p.s); x1 = __fmul_rn(x1, p.s); x2 = __fmul_rn(x2, p.s); x3 = __fmul_rn(x3, p.s); }
+          o[j] = e4m3 ? cvt_fp8x4_regs<true>(x0 * bs.inv_scale, x1 * bs.inv_scale, x2 * bs.inv_scale, x3 * bs.inv_scale)
+                      : cvt_fp8x4_regs<false>(x0 * bs.inv_scale, x1 * bs.inv_scale, x2 * bs.inv_scale, x3 * bs.inv_scale);
+        }
+      }
+      if (p.fp8_codes) {
+        uint8_t* dst = p.fp8_codes + (long long)b * p.o8_b + (long long)h * p.o8_h + (long long)r * p.o8_l + c;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      if ((tid & 1) == 0) {
+        const int kb = c >> 5;
+        sf8s[tt][(rl & 31) * 16 + (rl >> 5) * 4 + (kb & 3)] = bs.code;
+        rm8s[tt][rl * 4 + (kb & 3)] = bs.code;
+      }
+    }
+  }
+  __syncthreads();
+  const long long ntl = (p.L + 127) >> 7, ntd = (p.D + 127) >> 7;
+  for (int tt = 0; tt < TPC; ++tt) {
+    const int tile_l = blockIdx.x * TPC + tt, row0 = tile_l * 128;
+    if (row0 >= p.L) break;
+    if (tid < 32) {
+      if (p.fp8_scales_tiled) {
+        const long long tile_lin = (((long long)b * p.H + h) * ntl + tile_l) * ntd + tile_d;
+        reinterpret_cast<uint4*>(p.fp8_scales_tiled + tile_lin * 512)[tid] = reinterpret_cast<uint4*>(sf8s[tt])[tid];
+      }
+    } else if (tid >= 128 && tid < 256) {
+      // row-major scales (the reference's output format): one row of the tile per thread, its up to four codes in one store
+      const int rl = tid & 127, r = row0 + rl;
+      if (p.fp8_scales_rm && r < p.L) {
+        const uint8_t* src = rm8s[tt] + rl * 4;
+        const int kb0 = tile_d * 4, n = min(4, nblk - kb0);
+        uint8_t* dst = p.fp8_scales_rm + (((long long)b * p.H + h) * p.L + r) * nblk + kb0;
+        if (n == 4 && (nblk & 3) == 0) {
+          *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(src);
+        } else {
+          for (int j = 0; j < n; ++j) dst[j] = src[j];
+        }
+      }
+    }
+  }
+}
+
 // ---- per-32 int8 quantizer (ours/quant_mxint8.py:21-58) ------------------------------------
 struct QuantI8Params {
   const void* x; int in_dtype; int B, H, L, D;
@@ -503,6 +620,94 @@ __global__ void __launch_bounds__(256) quant_v_seq_kernel(const QuantVParams p) 
   }
 }
 
+
+// The same quantizer for 16-bit input whose rows are 16-byte aligned (the usual case): the whole 128-key tile goes
+// through shared memory in the input type with 16-byte loads, all issued up front; a unit of work is (head-dim index d,
+// 32-key block) with the block index fastest, so the four lanes of one d write 128 (MXFP8) or 64 (MXFP4) consecutive
+// bytes of a V^T row.  Rows of a 32-key block are skewed by 16 bytes per block in shared memory, which keeps the
+// column reads of the four blocks in different banks.  Same arithmetic, same results as quant_v_seq_kernel.
+template <typename T>
+__global__ void __launch_bounds__(256) quant_v_seq_vec_kernel(const QuantVParams p) {
+  constexpr int MAXD = 128;
+  constexpr int PITCH = MAXD * 2 + 16;             // bytes per key row
+  __shared__ __align__(16) uint8_t tile[128 * PITCH + 3 * 16];
+  __shared__ __align__(16) uint8_t s8[512];
+  __shared__ __align__(16) uint8_t s4[512];
+  const int kt = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int tid = threadIdx.x;
+  const int key0 = kt * 128;
+  const uint8_t* src = reinterpret_cast<const uint8_t*>(p.v) + ((long long)b * p.vs_b + (long long)h * p.vs_h) * 2;
+  const int vpr = p.D >> 3;                        // 16-byte vectors per key row
+  const int nvec = 128 * vpr;                      // 2048 (D=128) or 1024 (D=64): 8 or 4 per thread
+  uint4 ld[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int i = tid + j * 256;
+    ld[j] = make_uint4(0, 0, 0, 0);
+    if (i < nvec) {
+      const int kl = i / vpr, vc = i % vpr;
+      if (key0 + kl < p.Skv) ld[j] = __ldg(reinterpret_cast<const uint4*>(src + (long long)(key0 + kl) * p.vs_l * 2) + vc);
+    }
+  }
+  reinterpret_cast<uint16_t*>(s8)[tid] = 0x7f7f;
+  reinterpret_cast<uint16_t*>(s4)[tid] = 0x7f7f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int i = tid + j * 256;
+    if (i < nvec) {
+      const int kl = i / vpr, vc = i % vpr;
+      *reinterpret_cast<uint4*>(tile + kl * PITCH + (kl >> 5) * 16 + vc * 16) = ld[j];
+    }
+  }
+  __syncthreads();
+  // one unit = (head-dim index d, 32-key block), block index fastest
+  for (int u = tid; u < p.D * 4; u += 256) {
+    const int blk = u & 3, d = u >> 2;
+    float v[32], amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int kl = blk * 32 + i;
+      const T e = *reinterpret_cast<const T*>(tile + kl * PITCH + blk * 16 + d * 2);
+      v[i] = (float)e;
+      amax = fmaxf(amax, fabsf(v[i]));
+    }
+    const long long row = ((long long)bh * p.D + d);
+    const int sf_off = (d & 31) * 16 + (d >> 5) * 4 + blk;
+    if (p.vt8) {
+      BlockScale bs = mx_block_scale(amax, p.fp8_fmt == FMT_FP8_E4M3 ? 8 : 7);
+      uint32_t w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (bs.zero) w[j] = 0;
+        else if (p.fp8_fmt == FMT_FP8_E4M3)
+          w[j] = cvt_fp8x4_regs<true>(v[4 * j] * bs.inv_scale, v[4 * j + 1] * bs.inv_scale, v[4 * j + 2] * bs.inv_scale, v[4 * j + 3] * bs.inv_scale);
+        else
+          w[j] = cvt_fp8x4_regs<false>(v[4 * j] * bs.inv_scale, v[4 * j + 1] * bs.inv_scale, v[4 * j + 2] * bs.inv_scale, v[4 * j + 3] * bs.inv_scale);
+      }
+      uint4* o = reinterpret_cast<uint4*>(p.vt8 + row * p.Skv_pad + key0 + blk * 32);
+      o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      s8[sf_off] = bs.code;
+    }
+    if (p.vt4) {
+      BlockScale bs = mx_block_scale(amax, 2);
+      float y[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) y[i] = bs.zero ? 0.0f : v[i] * bs.inv_scale;
+      uint4 o4 = make_uint4(cvt_e2m1x8(y), cvt_e2m1x8(y + 8), cvt_e2m1x8(y + 16), cvt_e2m1x8(y + 24));
+      *reinterpret_cast<uint4*>(p.vt4 + row * (p.Skv_pad >> 1) + ((key0 + blk * 32) >> 1)) = o4;
+      s4[sf_off] = bs.code;
+    }
+  }
+  __syncthreads();
+  const long long nkt = p.Skv_pad >> 7;
+  const long long tile_lin = (long long)bh * nkt + kt;
+  if (tid < 32) {
+    if (p.sf8) reinterpret_cast<uint4*>(p.sf8 + tile_lin * 512)[tid] = reinterpret_cast<uint4*>(s8)[tid];
+  } else if (tid < 64) {
+    if (p.sf4) reinterpret_cast<uint4*>(p.sf4 + tile_lin * 512)[tid - 32] = reinterpret_cast<uint4*>(s4)[tid - 32];
+  }
+}
 
 // ---- NVFP4: 16-element blocks, E4M3 block scales, one fp32 tensor scale ------------------------------
 // The reference only has the GEMM mode string for this format (ours/block_scaled_matmul.py:321-324), no
@@ -701,6 +906,13 @@ static int quant_mx_launch(const void* x, int in_dtype, int B, int H, int L, int
   const bool w8 = p.fp8_codes || p.fp8_scales_rm || p.fp8_scales_tiled;
   const bool w4 = p.fp4_codes_unpacked || p.fp4_codes_packed || p.fp4_scales_rm || p.fp4_scales_tiled;
   if (!w8 && !w4) return set_error(MPSA_ERR_BAD_ARG, "quant_mx: no output requested");
+  if (w8 && !w4 && !p.rope_cos && !p.center && in_dtype != 2) {
+    // MXFP8 alone from bf16 / fp16: the memory-speed kernel, three tiles per CTA
+    const dim3 g8(((L + 127) / 128 + kMx8Tiles - 1) / kMx8Tiles, (D + 127) / 128, B * H);
+    if (in_dtype == 0) quant_mx8_kernel<__nv_bfloat16><<<g8, kMxThreads, 0, st>>>(p);
+    else quant_mx8_kernel<__half><<<g8, kMxThreads, 0, st>>>(p);
+    return check_launch("quant_mx");
+  }
 #define MPSA_QMX(T, ROPE)                                                                       \
   do {                                                                                          \
     if (w8 && w4) quant_mx_kernel<T, ROPE, true, true><<<grid, kMxThreads, 0, st>>>(p);         \
@@ -828,7 +1040,10 @@ extern "C" int mpsa_quant_v_seq(const void* v, int in_dtype, int B, int H, int S
   p.fp8_fmt = fp8_fmt; p.vt8 = (uint8_t*)vt8; p.vt4 = (uint8_t*)vt4; p.sf8 = (uint8_t*)v8_sf; p.sf4 = (uint8_t*)v4_sf;
   dim3 grid(Skv_pad / 128, B * H);
   cudaStream_t st = (cudaStream_t)stream;
-  if (in_dtype == 0) quant_v_seq_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  const bool vec = in_dtype != 2 && !((uintptr_t)v % 16) && !((vs_b * 2) % 16) && !((vs_h * 2) % 16) && !((vs_l * 2) % 16);
+  if (vec && in_dtype == 0) quant_v_seq_vec_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  else if (vec) quant_v_seq_vec_kernel<__half><<<grid, 256, 0, st>>>(p);
+  else if (in_dtype == 0) quant_v_seq_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
   else if (in_dtype == 1) quant_v_seq_kernel<__half><<<grid, 256, 0, st>>>(p);
   else quant_v_seq_kernel<float><<<grid, 256, 0, st>>>(p);
   return check_launch("quant_v_seq");
