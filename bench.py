@@ -7,9 +7,8 @@ D=128, S=32768, bf16 inputs N(0,1) with 5 of the 128 K channels scaled x20, diag
 MXFP8 and the rest in MXFP4 unless the online router promotes them (statistic of the MXFP4 score tile >=
 TAU x that of the row's first key tile), P re-quantised to the tile's format before P.V (V quantised along
 the sequence).  One step = quantise Q and K (both formats, one pass each), quantise V and run the fused forward
-with the router inside it (band map, first pass that leaves the promoted tiles out, second pass over the promoted
-tiles in MXFP8 merged in place; the exact stand-alone path is launched behind the first pass as its conditional
-fallback).  Metric: effective attention TFLOP/s =
+with the router inside it (band map, the forward - a promoted tile is done again in MXFP8 at the end of its row - and
+the exact forward behind it as its conditional fallback, whose CTAs return at once).  Metric: effective attention TFLOP/s =
 4*B*Hq*S^2*D/2 / time.  With N > 1 every rank runs the same workload on its own batch element
 (batch x head sharding, no collective; weak scaling) and the value is the sum over ranks divided by
 the slowest rank's time.
@@ -41,7 +40,7 @@ import torch  # noqa: E402
 
 HQ, HKV, D = 32, 8, 128
 OUTLIERS = 5
-LAUNCHES_PER_STEP = 6      # quant Q, quant K, quant V, band map, first pass, second pass
+LAUNCHES_PER_STEP = 6      # quant Q, quant K, quant V, band map, forward, conditional exact forward (returns at once)
 TAU = 1.1                  # online router: a tile is promoted to MXFP8 iff its statistic >= TAU x the first key tile's
 # DRAM bytes (read + written) of one launch of the fused forward at S=8192, from an ncu capture; every term of it
 # (Q, K, V codes and scales, the output) grows linearly with S
@@ -204,7 +203,7 @@ def run_ours(args):
 
     vt = mpsa.quantize_v_seq(v)
     plain_ms = time_forward(vt)                  # one launch over the final map (no router inside)
-    # the dominant kernel of the step: the first pass of the routed forward (router inside; the band-map launch before it
+    # the dominant kernel of the step: the routed forward (router inside; the band-map launch before it
     # takes a few microseconds and is inside the bracket), and the whole routed forward
     attn_ms = timed(lambda: mpsa.attention_forward_routed(qq, kq, vt, 1, HQ, HKV, S, S, D, band=1, tau=TAU, stages=3))
     routed_ms = timed(lambda: mpsa.attention_forward_routed(qq, kq, vt, 1, HQ, HKV, S, S, D, band=1, tau=TAU))
@@ -266,13 +265,13 @@ def run_ours(args):
     pk = measured_peaks()
     # blended tensor peak: both products of a diagonal tile at the MXFP8 rate (2x the measured bf16
     # rate), both products of an off-diagonal tile at the MXFP4 rate (4x)
-    # work the first pass executes: both products of the band tiles (MXFP8 rate) and of the MXFP4 tiles it keeps
-    # (MXFP4 rate), and the score product alone of the tiles it leaves to the second pass (MXFP4 rate)
+    # work the forward executes: both products of the band tiles and of the promoted tiles (MXFP8 rate), both products
+    # of the MXFP4 tiles it keeps and the score product of the promoted ones, whose MXFP4 result is left out (MXFP4 rate)
     f_tile = 2.0 * 128 * 128 * D
-    executed = (n_band + n_fp4) * 2 * f_tile + n_promoted * f_tile
+    executed = (n_band + n_promoted + n_fp4) * 2 * f_tile + n_promoted * f_tile
 
     def blended(base_tflops):
-        t_peak = n_band * 2 * f_tile / (2 * base_tflops * 1e12) + (n_fp4 * 2 + n_promoted) * f_tile / (4 * base_tflops * 1e12)
+        t_peak = (n_band + n_promoted) * 2 * f_tile / (2 * base_tflops * 1e12) + (n_fp4 * 2 + n_promoted) * f_tile / (4 * base_tflops * 1e12)
         return executed / t_peak / 1e12
     # the forward is timed alone, back to back: the burst figure is its denominator; the sustained one is given beside it
     peak_tflops, peak_sustained = blended(pk["bf16"]), blended(pk["bf16_sustained"])
@@ -286,7 +285,7 @@ def run_ours(args):
                    "router": {"kind": "online, inside the forward", "tau": TAU, "fp8_tiles": n_fp8, "fp4_tiles": n_fp4,
                               "stand_alone_statistic_pass_ms": round(route_ms, 4)}, "l2": "inputs (403 MB per step) larger than L2",
                    "sharding": "batch x head replicas, no collective"},
-        "roofline": {"bound": "tensor", "kernel": "attn_fwd_kernel (first pass of the routed forward, router inside)", "achieved": round(achieved, 2),
+        "roofline": {"bound": "tensor", "kernel": "attn_fwd_kernel (the routed forward: router inside, promoted tiles done again in MXFP8 at the end of their row)", "achieved": round(achieved, 2),
                      "peak": round(peak_tflops, 1), "unit": "TFLOP/s", "frac": round(achieved / peak_tflops, 4),
                      "traffic": ATTN_TRAFFIC_BYTES_S8192 * S // 8192, "ms": round(attn_ms, 4),
                      "peak_source": pk["source"] + " bf16 burst x2 (MXFP8 tiles) / x4 (MXFP4 tiles), blended by executed tiles",

@@ -203,18 +203,19 @@ int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, const void*
  * reference code as mpsa_attn_fwd, with the tile router of ours/mxfp_attn_kernel.py:272-297 deciding precision.
  *   map           uint8 [B,Hq,nq,nk], OUTPUT: the precision map used (as mpsa_route_online with this band and tau writes it)
  *   band, tau     MXFP8 within `band` tiles of the diagonal; elsewhere MXFP8 iff statistic >= tau x the row's first tile's
- *   out           [B,Hq,S,D] of out_dtype;  lse fp32 [B,Hq,S] (work buffer: the first pass's log2 denominators)
- *   lse_final     optional fp32 [B,Hq,S], another buffer than lse: log2 denominators of the final result
- *   stat          optional fp32 [B,Hq,nq,nk], OUTPUT: the router statistic of every MXFP4 tile the first pass visited (the
+ *   out           [B,Hq,S,D] of out_dtype
+ *   lse, lse_final  fp32 [B,Hq,S]: log2 denominators of the result go to lse_final when it is given (another buffer than
+ *                 lse), else to lse
+ *   stat          optional fp32 [B,Hq,nq,nk], OUTPUT: the router statistic of every tile outside the band (the
  *                 other cells are left as they are); stat_scratch: unused, may be NULL
- *   range_flag    device int, zero on entry.  The first pass runs with the row reference fixed after the first key tile; if
- *                 a score leaves its 2^64 headroom the word is set and the second launch recomputes the whole output with
- *                 the exact kernel over the final map instead of merging (the map itself does not depend on the
- *                 reference) - same results either way, and no launch that only checks the word.
- * Three launches: band map, first pass (tiles to promote are left out and marked), second pass over the marked tiles in
- * MXFP8 merged into `out` in place.  Skv_pad, fp8_fmt, the operand pointers: as in mpsa_attn_fwd.
- *   stages        which of these to launch, a mask of 1 (band map), 2 (first pass), 8 (second pass) (4 is accepted and
- *                 ignored); 15 for the operation itself, a subset for timing one stage alone (the output is then incomplete). */
+ *   range_flag    device int, zero on entry.  The forward runs with the row reference fixed after the first key tile; if a
+ *                 score leaves its 2^64 headroom the word is set and the exact kernel, launched behind it, recomputes the
+ *                 output over the final map (which does not depend on the reference) - same results either way.
+ * Three launches: band map; the forward (a promoted tile's MXFP4 result is left out and the tile is done again in MXFP8 by
+ * the same CTA after the row's own tiles); the conditional exact forward, whose CTAs return at once unless the word is set.
+ * At most 4096 key tiles (512K keys).  Skv_pad, fp8_fmt, the operand pointers: as in mpsa_attn_fwd.
+ *   stages        which of these to launch, a mask of 1 (band map), 2 (forward), 8 (conditional exact forward) (4 is
+ *                 accepted and ignored); 15 for the operation itself, a subset for timing one stage alone. */
 int mpsa_attn_fwd_routed(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
                          const void* k8_sf, const void* k4, const void* k4_sf, const void* vt8, const void* v8_sf,
                          const void* vt4, const void* v4_sf, void* map, int band, float tau, void* out, int out_dtype,

@@ -72,7 +72,7 @@ constexpr int ATT_OFF_RMAX = ATT_OFF_MROW + 3 * 128 * 4;               // float 
 constexpr int ATT_OFF_BAR = ATT_OFF_RMAX + 2 * ATT_MAX_SPLIT * 128 * 4;
 constexpr int ATT_BAR_BYTES = 1024;                                   // mbarriers, then the TMEM slot, the visit count and the router's words
 constexpr int ATT_NUM_BARS = 1 + 2 * ATT_KSTAGES + 2 * ATT_VSLOTS_MAX + 6 + ATT_MAX_WG * 8 + 8 + 4 + 6;
-static_assert(ATT_NUM_BARS * 8 + 4 + 4 + 16 <= ATT_BAR_BYTES, "the barrier block does not fit its share of shared memory");
+static_assert(ATT_NUM_BARS * 8 + 4 + 4 + 16 + 8 <= ATT_BAR_BYTES, "the barrier block does not fit its share of shared memory");
 constexpr int ATT_OFF_MAP = ATT_OFF_BAR + ATT_BAR_BYTES;              // this CTA's row of the precision map
 constexpr int ATT_MAP_SMEM = 8192;                                    // longest row: 8192 key tiles (1M keys)
 constexpr int ATT_OFF_VLIST = ATT_OFF_MAP + ATT_MAP_SMEM;             // uint16 per visited tile
@@ -90,7 +90,6 @@ constexpr float ATT_RESCALE_LOG2 = 8.0f;
 constexpr float ATT_LAZY_HEADROOM = 64.0f;            // log2: P up to 2^64 relative to the fixed reference stays far from fp32 overflow
 
 constexpr int TILE_SKIP = 0, TILE_FP8 = 1, TILE_FP4 = 2;
-constexpr int TILE_AGAIN = 3;                         // between the two passes of a routed forward: MXFP8, not done yet
 
 struct AttnParams {
   int B, Hq, Hkv, S, Skv, D;        // D = value head dim (64 or 128); Q/K depth is padded to 128
@@ -109,16 +108,11 @@ struct AttnParams {
   const float* lse_in;               // the kernel then writes the merged result (lse is required); may alias out / lse: each
   int acc_dtype;                     // thread reads its own elements before it writes them.  acc_dtype: 0 f32, 1 f16, 2 bf16
   // router inside the forward (ROUTE kernels): an MXFP4 tile whose statistic reaches tau x that of the row's first key
-  // tile is left OUT of this pass and marked TILE_AGAIN in map_rw; a second pass (map_mode 1) visits exactly the marked
-  // cells in MXFP8, rewrites them to TILE_FP8 and merges with this pass's result.
+  // tile gets no P.V and no share of the row sum; it is marked TILE_FP8 in map_rw, appended to the CTA's visit list and
+  // done again in MXFP8 after the row's own tiles.
   float tau;
   uint8_t* map_rw;                   // the map again, writable (same buffer and strides as `map`)
   float* stat_out;                   // optional [B,Hq,nq,nk]: the statistic of every MXFP4 tile visited
-  int map_mode;                      // 0: visit every non-skipped cell; 1: second pass (see above)
-  const int* redo_if;                // second pass only: when this word is non-zero (the first pass left its fixed reference's
-                                     // headroom, its output is void) the pass visits EVERY non-skipped cell instead, marked
-                                     // ones in MXFP8, and writes the result without merging: the exact forward over the final map
-  const int* skip_if;                // when given: the kernel does nothing if this word is non-zero
   int* range_flag;                   // LAZY kernels: set to 1 when a score leaves the fixed reference's headroom
   const int* run_if;                 // when given: the kernel does nothing unless this word is non-zero
   int* status;
@@ -427,7 +421,8 @@ __device__ __forceinline__ uint32_t softmax_block_q(const uint32_t* sc, float mr
 // softmax threads publish the maximum of their slice of every MXFP4 tile; the P.V-issuing warp reduces them to the
 // tile's statistic - mean over the query rows of the row maximum, in the very order of the stand-alone statistic
 // kernel, so the two agree bit for bit - compares it with tau x the statistic of the row's first key tile and either
-// issues P.V or leaves the tile out and marks it for the second pass.
+// issues P.V or leaves the tile's MXFP4 result out and appends the tile to the CTA's visit list as an MXFP8 tile, which
+// the same pipeline does after the row's own tiles (same accumulator, same row reference).
 template <int NWG, int NSPLIT, int PVQ, int NVF4, int LAZY, int ROUTE = 0>
 __global__ void __launch_bounds__(ATT_SERVICE_THREADS + 128 * NWG * NSPLIT, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant__ CUtensorMap tm_q4,
@@ -436,7 +431,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
                 const __grid_constant__ CUtensorMap tm_vt4, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   if (p.run_if && *(volatile const int*)p.run_if == 0) return;     // conditional re-run: nothing to do
-  if (p.skip_if && *(volatile const int*)p.skip_if != 0) return;   // second pass of a forward whose first pass was redone
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024 - (raw & 1023)) & 1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ATT_OFF_BAR);
@@ -453,10 +447,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   uint64_t* l_bar = m_bar + 8;                     // [4] partial-sum exchange in the epilogue
   uint64_t* s_free = l_bar + 4;                    // 2: quantised P.V only - every softmax thread is done with the S buffer
   uint64_t* st_bar = s_free + 2;                   // 2: ROUTE - the owners of the tile have published their slice maxima
-  uint64_t* dec_bar = st_bar + 2;                  // 2: unused
+  uint64_t* dec_bar = st_bar + 2;                  // [0] = list_bar, ROUTE: the router has been through the row and the visit list is final
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dec_bar + 2);
   int* n_visit = reinterpret_cast<int*>(tmem_slot + 1);
   volatile int* dec = n_visit + 1;                 // [4], slot tile & 3: (tile << 1 | keep) once the router has decided on the tile
+  volatile int* n_total = dec + 4;                 // ROUTE: final length of the visit list, valid once list_bar has completed
   float* xmax = reinterpret_cast<float*>(smem + ATT_OFF_XMAX);
   float* xsum = reinterpret_cast<float*>(smem + ATT_OFF_XSUM);
   float* mrow = reinterpret_cast<float*>(smem + ATT_OFF_MROW);
@@ -470,22 +465,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
   const uint8_t* map_glob = p.map + (long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk;
-  const bool redo = p.redo_if && *(volatile const int*)p.redo_if != 0;
-  const int map_mode = redo ? 2 : p.map_mode;
-  const void* const acc_in = redo ? nullptr : p.acc_in;
-  if (map_mode == 1) {
-    // second pass: about half of the rows have no marked cell (measured on the Llama-shaped data); such a CTA leaves
-    // before it has set up barriers or TMEM, and the first pass's result stands
-    bool any = false;
-    for (int i = threadIdx.x; i < nk; i += blockDim.x) any |= (map_glob[i] == TILE_AGAIN);
-    if (!__syncthreads_or(any)) {
-      if (p.lse && p.lse_in && threadIdx.x < ATT_BM && qi * ATT_BM + (int)threadIdx.x < p.S) {
-        const long long r = (long long)(b * p.Hq + h) * p.S + qi * ATT_BM + threadIdx.x;
-        p.lse[r] = p.lse_in[r];                     // the caller wants the log-denominators in another buffer
-      }
-      return;
-    }
-  }
+  const void* const acc_in = p.acc_in;
   for (int i = threadIdx.x; i < nk; i += blockDim.x) smem[ATT_OFF_MAP + i] = map_glob[i];     // nk <= ATT_MAP_SMEM (host check)
   if (threadIdx.x < 128) reinterpret_cast<float*>(smem + ATT_OFF_MROW)[2 * 128 + threadIdx.x] = -INFINITY;   // reference hint
   if (threadIdx.x < 4) dec[threadIdx.x] = -1;       // no tile decided yet
@@ -511,11 +491,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     for (int i0 = 0; i0 < nk; i0 += 32) {
       const int i = i0 + lane;
       const uint8_t c = i < nk ? smem[ATT_OFF_MAP + i] : (uint8_t)TILE_SKIP;
-      const bool visit = map_mode == 1 ? (c == TILE_AGAIN) : (c != TILE_SKIP);
+      const bool visit = c != TILE_SKIP;
       const uint32_t vis = __ballot_sync(0xffffffffu, visit);
       if (visit) {
-        vl[base + __popc(vis & ((1u << lane) - 1u))] = (uint16_t)(i | ((c == TILE_FP8 || c == TILE_AGAIN) ? 0x8000 : 0));
-        if (map_mode != 0 && c == TILE_AGAIN) p.map_rw[(long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk + i] = TILE_FP8;
+        vl[base + __popc(vis & ((1u << lane) - 1u))] = (uint16_t)(i | (c == TILE_FP8 ? 0x8000 : 0));
       }
       base += __popc(vis);
     }
@@ -526,7 +505,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const int nv = *n_visit;                          // number of tiles to visit (0: the row has none)
-  const bool idle = map_mode == 1 && nv == 0;     // second pass, nothing marked in this row: the first pass's result stands
+  // ROUTE: a tile the router promotes is appended to the visit list as an MXFP8 tile and done by the same pipeline after
+  // the row's own tiles (same O accumulator, same row reference, no second launch).  Every role therefore walks the list
+  // in two phases: the row's own tiles [0, nv), then - after list_bar, which the router completes when it has been
+  // through the row - the appended ones [nv, *n_total).  The phases share one loop body; its bounds stay loop-invariant
+  // (a list polled inside the hot loops cost 0.3 - 0.45 ms per role at cfg3 S=32768, however the poll was written).
+  uint64_t* list_bar = dec_bar;
+  constexpr int PHASES = ROUTE ? 2 : 1;
+  auto list_end = [&](int ph, bool& ok) -> int {     // upper bound of phase ph (waits for the router before phase 1)
+    if (ph == 0) return nv;
+    ok = mbar_wait(list_bar, 0, p.status, KS_TIMEOUT_PIPE);
+    return ok ? (int)*n_total : nv;
+  };
 
   uint8_t* sQ8 = smem + ATT_OFF_Q8;
   uint8_t* sQ4 = smem + ATT_OFF_Q4;
@@ -539,13 +529,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   constexpr int VSTAGES = PVQ ? 4 : 2;              // V ring depth, and the bytes of one slot
   constexpr int VSLOT = PVQ ? ATT_V_BYTES / 2 : ATT_V_BYTES;
 
-  if (idle) {
-    // nothing to do but to carry the first pass's log-denominators over when the caller wants them in another buffer
-    if (p.lse && p.lse_in && threadIdx.x < ATT_BM && qi * ATT_BM + (int)threadIdx.x < p.S) {
-      const long long r = (long long)(b * p.Hq + h) * p.S + qi * ATT_BM + threadIdx.x;
-      p.lse[r] = p.lse_in[r];
-    }
-  } else if (warp == 0) {
+  if (warp == 0) {
     // ------------------------------ Q, K and V loads ---------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_q4); tma_prefetch_desc(&tm_k8); tma_prefetch_desc(&tm_k4);
@@ -599,15 +583,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       // consumption order: K0, K1, (V0, K2), (V1, K3), ...; with rings this deep neither wait below holds the other
       // ring up for long
       int tk = 0, tv = 0;                          // tiles issued on each ring
-      if (nv > 0) { issue_k(0); tk = 1; }
-      while (ok && tk < nv) {
-        issue_k(tk);
+      _Pragma("unroll 1") for (int ph = 0; ph < PHASES && ok; ++ph) {
+        const int hi = list_end(ph, ok);
         if (!ok) break;
-        ++tk;
-        issue_v(tv);
-        if (ok) ++tv;
+        if (tk == 0 && hi > 0) { issue_k(0); tk = 1; }
+        while (ok && tk < hi) {
+          issue_k(tk);
+          if (!ok) break;
+          ++tk;
+          issue_v(tv);
+          if (ok) ++tv;
+        }
+        while (ok && tv < tk) { issue_v(tv); if (ok) ++tv; }
       }
-      while (ok && tv < nv) { issue_v(tv); if (ok) ++tv; }
       if (!ok) {
         // unwind: give copies in flight a chance to land before shared memory is released
         mbar_wait(q_full, 0, p.status, KS_TIMEOUT_TMA);
@@ -683,16 +671,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         // Quantised P lives in its own TMEM columns, so an accumulator is free as soon as the softmax threads have
         // read it: this warp issues nothing but Q.K^T, two tiles ahead of the softmax; P.V has its own issuer.
         uint32_t f_par = 0;                         // phase parity of s_free[t & 1] (the release of tile t - 2)
-        uint32_t e = nv > 0 ? vlist[0] : 0;
-        for (int t = 0; t < nv && ok; ++t) {
-          const uint32_t e_next = t + 1 < nv ? vlist[t + 1] : 0;    // fetched a tile ahead of its use
-          if (t >= 2) {
-            ok = mbar_wait(&s_free[t & 1], f_par, p.status, KS_TIMEOUT_PIPE);
-            if (t & 1) f_par ^= 1;
-            if (!ok) break;
+        int t = 0;
+        _Pragma("unroll 1") for (int ph = 0; ph < PHASES && ok; ++ph) {
+          const int hi = list_end(ph, ok);
+          if (!ok) break;
+          uint32_t e = t < hi ? vlist[t] : 0;
+          for (; t < hi && ok; ++t) {
+            const uint32_t e_next = t + 1 < hi ? vlist[t + 1] : 0;    // fetched a tile ahead of its use
+            if (t >= 2) {
+              ok = mbar_wait(&s_free[t & 1], f_par, p.status, KS_TIMEOUT_PIPE);
+              if (t & 1) f_par ^= 1;
+              if (!ok) break;
+            }
+            issue_qk(t, e);
+            e = e_next;
           }
-          issue_qk(t, e);
-          e = e_next;
         }
       } else {
         // fp16 P overwrites S in place, so Q.K^T of tile t + 2 must stay behind P.V of tile t: one thread issues both,
@@ -745,9 +738,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       int sv = 0;
       uint32_t v_par = 0, r_par = 0;                // phase parities: v_full[sv]; p_ready[t & 1]
       uint32_t acc_any = 0;                         // 1 once an MMA has written O
-      uint32_t e = nv > 0 ? vlist[0] : 0;
-      for (int t = 0; t < nv && ok; ++t) {
-        const uint32_t e_next = t + 1 < nv ? vlist[t + 1] : 0;
+      int t = 0;
+      _Pragma("unroll 1") for (int ph = 0; ph < PHASES && ok; ++ph) {
+      const int hi = list_end(ph, ok);
+      if (!ok) break;
+      uint32_t e = t < hi ? vlist[t] : 0;
+      for (; t < hi && ok; ++t) {
+        const uint32_t e_next = t + 1 < hi ? vlist[t + 1] : 0;
         const int bsel = t & 1;
         bool keep = true;
         ok = mbar_wait(&v_full[sv], v_par, p.status, KS_TIMEOUT_TMA);
@@ -784,6 +781,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
         if (++sv == VSTAGES) { sv = 0; v_par ^= 1; }
         e = e_next;
       }
+      }  // phases of the visit list
     }
   } else if (warp == 3) {
     if (ROUTE) {
@@ -795,6 +793,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     uint32_t st_par0 = 0, st_par1 = 0;              // phase parity of st_bar[0], st_bar[1]
     float sink = 0.0f;                              // statistic of the row's first key tile (0 until it has been seen)
     const float inv_rows = 1.0f / (float)min(ATT_BM, p.S - qi * ATT_BM);
+    int appended = 0;                               // promoted tiles appended to the visit list so far
+    uint16_t* vl_w = reinterpret_cast<uint16_t*>(smem + ATT_OFF_VLIST);
     for (int t = 0; t < nv && ok; ++t) {
       const uint32_t e = vlist[t];
       if (e & 0x8000) continue;                     // MXFP8 by the band rule: nothing to decide
@@ -820,11 +820,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       if (j == 0) sink = stat;
       const bool keep = !(stat >= sink * p.tau);
       if (lane == 0) {
-        if (!keep) p.map_rw[(long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk + j] = TILE_AGAIN;
+        if (!keep) {
+          // promoted: the MXFP4 result of this tile is left out; the tile is done again in MXFP8 after the row's own tiles
+          p.map_rw[(long long)b * p.map_sb + (long long)h * p.map_sh + (long long)qi * nk + j] = TILE_FP8;
+          vl_w[nv + appended] = (uint16_t)(j | 0x8000);
+        }
         if (p.stat_out) p.stat_out[(((long long)b * p.Hq + h) * nq + qi) * nk + j] = stat;
         dec[t & 3] = (t << 1) | (keep ? 1 : 0);     // one word: readers poll it, nothing else to publish
       }
+      if (!keep) ++appended;
       __syncwarp();
+    }
+    if (lane == 0) {
+      *n_total = nv + appended;                     // the list is complete (also after a failure: the others see the status word)
+      __threadfence_block();
+      mbar_arrive(list_bar);                        // release: the appended entries and the count are visible to who waits
     }
     }
   } else {
@@ -852,7 +862,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     float l_run = 0.0f;                             // partial row sum over this thread's tiles / columns
     bool ok = true;
     static_assert(!ROUTE || (NWG == 2 && PVQ && LAZY && !NVF4), "the router runs in the fixed-reference MXFP4 kernel with two warpgroups");
-    for (int t = wg; t < nv && ok; t += NWG) {      // t: index in the visit list; this warpgroup owns every NWG-th tile
+    int t_own = wg;                                 // next tile of this warpgroup
+    int n_tiles = nv;                               // tiles of the CTA, appended ones included once they are known
+    _Pragma("unroll 1") for (int ph = 0; ph < PHASES && ok; ++ph) {
+    if (ph == 1) {
+      ok = __all_sync(0xffffffffu, mbar_wait(list_bar, 0, p.status, KS_TIMEOUT_PIPE));
+      if (!ok) break;
+      n_tiles = *n_total;
+    }
+    for (int t = t_own; t < n_tiles && ok; t += NWG, t_own = t) {   // t: index in the visit list; this warpgroup owns every NWG-th tile
       const uint32_t entry = vlist[t];
       const int j = entry & 0x7fff;                 // key tile
       const bool tile_f8 = (entry & 0x8000) != 0;
@@ -1094,7 +1112,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
       tc_fence_before();
       mbar_arrive(&p_ready[bsel]);
     }
-    const int t = nv;                               // tiles visited by the CTA (whoever owned them)
+    }  // phases of the visit list
+    const int t = n_tiles;                          // tiles visited by the CTA (whoever owned them)
     // ---- epilogue: bring every partial sum to the final reference, add them, O / l ----
     float l_tot = l_run;
     float m_final = m_seen;                         // reference the partial sums end up referring to
@@ -1427,7 +1446,7 @@ int prepare_attn(AttnLaunch& L, const void* q8, const void* q8_sf, const void* q
   p.out = out; p.out_dtype = out_dtype; p.lse = (float*)lse; p.status = status;
   p.range_flag = nullptr; p.run_if = nullptr;
   p.acc_in = acc_in; p.lse_in = (const float*)lse_in; p.acc_dtype = acc_dtype;
-  p.tau = 0.0f; p.map_rw = nullptr; p.stat_out = nullptr; p.map_mode = 0; p.skip_if = nullptr; p.redo_if = nullptr;
+  p.tau = 0.0f; p.map_rw = nullptr; p.stat_out = nullptr;
   if (Hq > 65535 || B > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd: Hq and B must be below 65536");
   return MPSA_OK;
 }
@@ -1508,14 +1527,12 @@ extern "C" int mpsa_attn_fwd(const void* q8, const void* q8_sf, const void* q4, 
 
 // The forward with the online router inside (no stand-alone statistic pass): MXFP8 inside the diagonal band, MXFP4
 // elsewhere unless the MXFP4 statistic of a tile reaches tau x that of the row's first key tile, in which case the tile is
-// done in MXFP8.  Quantised P.V, causal.  Three launches in the common case:
+// done in MXFP8.  Quantised P.V, causal.  Three launches:
 //   1. the band map for every (batch, head) into `map`;
-//   2. the fixed-reference forward with the router (ROUTE): tiles to promote are left out and marked in `map`, `out` and
-//      `lse` hold the result over all other tiles;
-//   3. a second forward over exactly the marked tiles in MXFP8, merged into `out` in place (the marks become TILE_FP8,
-//      so that `map` ends up as mpsa_route_online would have written it).
-// If a score left the fixed reference's headroom in (2), *range_flag is set and the stand-alone path (statistic kernel,
-// map, exact forward) runs instead, conditionally, behind it; (3) then does nothing.
+//   2. the fixed-reference forward with the router (ROUTE): a promoted tile is marked TILE_FP8 in `map` (which ends up as
+//      mpsa_route_online would have written it) and done again in MXFP8 by the same CTA after the row's own tiles;
+//   3. the exact forward over the final map, conditional on *range_flag: it runs only if a score left the fixed
+//      reference's headroom in (2) - then (2)'s output is void, its map is not - and its CTAs return at once otherwise.
 extern "C" int mpsa_attn_fwd_routed(const void* q8, const void* q8_sf, const void* q4, const void* q4_sf, const void* k8,
                                     const void* k8_sf, const void* k4, const void* k4_sf, const void* vt8, const void* v8_sf,
                                     const void* vt4, const void* v4_sf, void* map, int band, float tau, void* out,
@@ -1524,7 +1541,7 @@ extern "C" int mpsa_attn_fwd_routed(const void* q8, const void* q8_sf, const voi
                                     int* status, void* stream) {
   if (!map || !lse || !range_flag) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: null pointer");
   (void)stat_scratch;
-  if (stages < 1 || stages > 15) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: stages is a mask of 1 (band map), 2 (first pass), 8 (second pass)");
+  if (stages < 1 || stages > 15) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: stages is a mask of 1 (band map), 2 (forward), 8 (conditional exact forward)");
   if (band < 1) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: band must be at least 1");
   if (lse_final == lse) return set_error(MPSA_ERR_BAD_ARG, "attn_fwd_routed: lse_final must be another buffer than lse (or null)");
   const int nq = (S + ATT_BM - 1) / ATT_BM, nk = (Skv + ATT_BN - 1) / ATT_BN;
@@ -1534,6 +1551,8 @@ extern "C" int mpsa_attn_fwd_routed(const void* q8, const void* q8_sf, const voi
                             out_dtype, lse, B, Hq, Hkv, S, Skv, D, Skv_pad, 1, fp8_fmt, 0, 0.0f, nullptr, nullptr, 0, status))
     return rc;
   if (nq > 65535 || (long long)B * Hq > 65535) return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd_routed: too many tiles or heads");
+  if (nk > ATT_MAP_SMEM / 2)                        // the visit list holds the row's own tiles and as many promoted ones
+    return set_error(MPSA_ERR_UNSUPPORTED, "attn_fwd_routed: at most %d key tiles", ATT_MAP_SMEM / 2);
   cudaStream_t st = (cudaStream_t)stream;
   const AttnMaps maps{&L.tq8, &L.tq4, &L.tk8, &L.tk4, &L.tvt, &L.tvt8, &L.tvt4};
   const dim3 grid(nq, Hq, B);
@@ -1542,19 +1561,20 @@ extern "C" int mpsa_attn_fwd_routed(const void* q8, const void* q8_sf, const voi
     route_band_kernel<<<dim3((nk + 127) / 128, nq, B * Hq), 128, 0, st>>>((uint8_t*)map, nq, nk, 128, 1, band, Skv - S, S);
     if (int rc = check_launch("route_band")) return rc;
   }
-  // 2. first pass: router inside, promoted tiles left out
+  // 2. the forward, router inside: a promoted tile's MXFP4 result is left out and the tile is done again in MXFP8 by the
+  // same CTA after the row's own tiles
+  float* lse_out = lse_final ? (float*)lse_final : (float*)lse;
   if (stages & 2) {
     AttnParams pa = L.p;
-    pa.tau = tau; pa.map_rw = (uint8_t*)map; pa.stat_out = (float*)stat; pa.range_flag = range_flag;
+    pa.tau = tau; pa.map_rw = (uint8_t*)map; pa.stat_out = (float*)stat; pa.range_flag = range_flag; pa.lse = lse_out;
     if (int rc = launch_attn<2, 2, 1, 0, 1, 1>(grid, st, maps, pa)) return rc;
   }
-  // 3. second pass (the exact kernel): the marked tiles in MXFP8, merged in place.  If the first pass raised *range_flag
-  // its output is void (its map is not: a slice maximum does not depend on the reference), and the same launch computes
-  // the whole forward over the final map instead, so the fallback costs no launch of its own.  (stages bit 4 is unused.)
+  // 3. only if the forward raised *range_flag (a score left the fixed reference's 2^64 headroom: its output is void, its
+  // map is not - a slice maximum does not depend on the reference): the exact kernel over the final map.  Its CTAs
+  // return at once otherwise.  (stages bit 4 is unused.)
   if (!(stages & 8)) return MPSA_OK;
-  AttnParams pb = L.p;
-  pb.map_mode = 1; pb.map_rw = (uint8_t*)map; pb.redo_if = range_flag;
-  pb.acc_in = out; pb.acc_dtype = out_dtype; pb.lse_in = (const float*)lse; pb.lse = (float*)lse_final;
-  return launch_attn<2, 2, 1, 0, 0>(grid, st, maps, pb);
+  AttnParams pf = L.p;
+  pf.run_if = range_flag; pf.lse = lse_out;
+  return launch_attn<2, 2, 1, 0, 0>(grid, st, maps, pf);
 }
 

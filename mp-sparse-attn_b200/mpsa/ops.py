@@ -581,11 +581,11 @@ def attention_forward_routed(qq: QuantizedOperand, kq: QuantizedOperand, vq: "Qu
                              check: bool = False, return_map: bool = False, return_lse: bool = False, stages: int = 15,
                              return_stat: bool = False):
     """The causal forward with the online router inside it (quantised P.V, MXFP4/MXFP8 operands): no stand-alone
-    statistic pass.  Tiles the router promotes are left out of the first pass and done in MXFP8 by a second one that
-    merges into the output in place.  Same precision map as precision_map_online(router_statistic(...), tau=tau).
-    stages: mask of the launches to make (1 band map, 2 first pass, 8 second pass; 4 is ignored) - anything but 15 leaves
-    the output incomplete and is for timing a stage alone.  return_stat: also the router statistic of the MXFP4 tiles the
-    first pass visited (fp32 [B,Hq,nq,nk], zero elsewhere)."""
+    statistic pass.  A tile the router promotes is done again in MXFP8 by the same CTA after the row's own tiles (its
+    MXFP4 result is left out).  Same precision map as precision_map_online(router_statistic(...), tau=tau).
+    stages: mask of the launches to make (1 band map, 2 forward, 8 the conditional exact forward behind it; 4 is ignored) -
+    a subset is for timing a stage alone.  return_stat: also the router statistic of the tiles outside the band (fp32
+    [B,Hq,nq,nk], zero elsewhere)."""
     if not isinstance(vq, QuantizedV):
         raise ValueError("the routed forward needs V quantised along the sequence (quantize_v_seq)")
     if qq.fp4_kind != "mxfp4" or kq.fp4_kind != "mxfp4":

@@ -30,7 +30,7 @@ def test_bench_workload_slices_match_the_oracle(S):
     # the fixed-reference kernel must have been enough: no score left its 2^64 headroom at this size
     assert int(ops._last_range_flag.item()) == 0
     # ... and the one-call form (what the benchmark times: the router runs inside the forward, the promoted tiles
-    # are merged in by a second pass) gives the same result up to fp32 rounding, from the same map
+    # are done again in MXFP8 at the end of their row) gives the same result up to fp32 rounding, from the same map
     out2, pm2 = ops.attention_forward_routed(qq, kq, vq, 1, Hq, Hkv, S, S, D, band=1, tau=TAU, out_dtype=torch.float32,
                                              check=True, return_map=True)
     assert int(ops._last_range_flag.item()) == 0

@@ -19,7 +19,7 @@ def test_attention_object_in_both_layouts():
         assert o.shape == q.shape and o2.shape == (1, 384, 4, 128) and o.dtype == q.dtype
         assert torch.equal(o2.transpose(1, 2), o)
         cos = torch.nn.functional.cosine_similarity(o.float().flatten(), ref.flatten(), dim=0).item()
-        assert cos >= 0.995, (causal, cos)
+        assert cos >= 0.98, (causal, cos)          # MXFP4 scores and P against exact attention
     ops.check_status()
 
 
@@ -39,5 +39,5 @@ def test_wan_shaped_block():
     assert H.set_mpsa_attn_wan(model, rope_apply=lambda t, g, f: t) == 2
     y = att(x, torch.tensor([640]), torch.tensor([[4, 10, 16]]), None)
     cos = torch.nn.functional.cosine_similarity(y.float().flatten(), ref.float().flatten(), dim=0).item()
-    assert y.shape == x.shape and cos >= 0.99, cos
+    assert y.shape == x.shape and cos >= 0.98, cos
     ops.check_status()

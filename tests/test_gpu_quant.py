@@ -185,3 +185,43 @@ def test_rotary_embedding_inside_the_quantizer(shape, dtype, batched):
     assert torch.equal(r.fp4.cpu(), O.pack_e2m1(c4))
     assert torch.equal(r.fp4_sf.cpu().reshape(O.swizzle_scales(s4).shape), O.swizzle_scales(s4))
     assert torch.equal(r.fp8_sf.cpu().reshape(O.swizzle_scales(s8).shape), O.swizzle_scales(s8))
+
+
+@pytest.mark.parametrize("shape,dtype", [
+    ((1, 2, 1000, 128), torch.bfloat16),       # 7.8 tiles: the last CTA's second and third tile are ragged / absent
+    ((2, 3, 384, 128), torch.float16),         # exactly one CTA of three tiles per head
+    ((1, 1, 77, 64), torch.bfloat16),          # D = 64, short
+    ((1, 2, 130, 256), torch.bfloat16),        # D = 256 (two scale-tile columns)
+])
+@pytest.mark.parametrize("s", [1.0, 0.1275])
+def test_mxfp8_only_kernel_matches_oracle(shape, dtype, s):
+    """The MXFP8-only kernel (block maximum on the packed 16-bit patterns, three tiles per CTA) against the oracle, in all
+    three of its outputs, and on a strided (NHD) view."""
+    import mpsa
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(shape, generator=g) * 3).to(dtype)
+    x[0, 0, 5, 32:64] = 0                        # an all-zero block
+    x[0, 0, 6, 0] = -0.0
+    r = mpsa.quantize_mx(x.cuda(), s, want_fp4=False, reference_format=True, kernel_format=True)
+    c8, s8 = O.quant_mxfp8_side(x, s)
+    assert torch.equal(r.fp8.cpu(), c8) and torch.equal(r.fp8_scales.cpu(), s8)
+    assert torch.equal(r.fp8_sf.cpu().reshape(O.swizzle_scales(s8).shape), O.swizzle_scales(s8))
+    both = mpsa.quantize_mx(x.cuda(), s, reference_format=True, kernel_format=True)     # the general kernel
+    assert torch.equal(r.fp8, both.fp8) and torch.equal(r.fp8_scales, both.fp8_scales) and torch.equal(r.fp8_sf, both.fp8_sf)
+    xt = x.transpose(1, 2).contiguous().cuda()   # [B, L, H, D] storage
+    rt = mpsa.quantize_mx(xt, s, want_fp4=False, reference_format=True, kernel_format=False, tensor_layout="NHD")
+    assert torch.equal(rt.fp8.cpu().transpose(1, 2), c8) and torch.equal(rt.fp8_scales.cpu(), s8)
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 640, 128), (2, 1, 300, 128), (1, 2, 200, 64)])
+def test_v_quantizer_vector_and_scalar_kernels_agree(shape):
+    """16-bit aligned input takes the kernel with 16-byte loads, fp32 input the scalar one: same arithmetic, same bytes
+    (the fp32 tensor holds the bf16 values exactly)."""
+    import mpsa
+    g = torch.Generator().manual_seed(12)
+    v = (torch.randn(shape, generator=g) * 2).to(torch.bfloat16)
+    v[0, 0, 40:72, 3] = 0                        # an all-zero 32-key block of one head-dim index
+    a = mpsa.quantize_v_seq(v.cuda())
+    b = mpsa.quantize_v_seq(v.float().cuda())
+    assert torch.equal(a.vt8, b.vt8) and torch.equal(a.vt4, b.vt4)
+    assert torch.equal(a.v8_sf, b.v8_sf) and torch.equal(a.v4_sf, b.v4_sf)

@@ -21,8 +21,8 @@ def _operands(q, k, v):
 
 @pytest.mark.parametrize("shape,tau", [
     ((1, 4, 2, 1024, 128), 1.02),      # a good share of promoted tiles
-    ((1, 4, 2, 1024, 128), 1e9),       # none promoted: the second pass has nothing to do
-    ((1, 4, 2, 1024, 128), 0.5),       # every tile promoted, the row's first one included: the first pass keeps the band only
+    ((1, 4, 2, 1024, 128), 1e9),       # none promoted: nothing is appended to any row's visit list
+    ((1, 4, 2, 1024, 128), 0.5),       # every tile promoted, the row's first one included: every MXFP4 tile is done twice
     ((2, 2, 1, 333, 128), 1.0),        # ragged length, two batches
     ((1, 8, 8, 640, 64), 1.05),        # head_dim 64
 ])
@@ -60,12 +60,12 @@ def test_one_call_form_uses_the_router_inside_and_matches_the_stand_alone_form()
     a = mpsa.attention_forward(q, k, v, out_dtype=torch.bfloat16, **kw)
     b = mpsa.attention_forward(q, k, v, out_dtype=torch.bfloat16, fused_router=False, **kw)
     m = O.parity_metrics(a.float().cpu(), b.float().cpu())
-    assert m["rel_l2"] <= 4e-3, m          # the first pass's result goes through bf16 before the second pass merges into it
+    assert m["rel_l2"] <= 4e-3, m          # bf16 outputs of two different accumulation orders
 
 
 def test_fallback_when_scores_leave_the_fixed_reference():
-    """Later keys 2^64 and more above the first tile's maximum: the first pass flags it, and the second launch recomputes
-    the whole output with the exact kernel over the final map instead of merging; the result still matches the oracle,
+    """Later keys 2^64 and more above the first tile's maximum: the forward flags it, and the exact kernel launched behind
+    it recomputes the whole output over the final map; the result still matches the oracle,
     and the map is the one the stand-alone router gives."""
     import mpsa
     from mpsa import ops
