@@ -18,8 +18,12 @@ def test_attention_object_in_both_layouts():
                  is_causal=causal, tensor_layout="NHD")
         assert o.shape == q.shape and o2.shape == (1, 384, 4, 128) and o.dtype == q.dtype
         assert torch.equal(o2.transpose(1, 2), o)
+        # the object adds nothing of its own: same bytes as the reference-named entry point with the same settings
+        from ours.mxfp_attn_kernel import mxfp_attn_kernel
+        direct = mxfp_attn_kernel(q, k, v, is_causal=causal, smooth_k=True, output_dtype=q.dtype, block_scale_type="diag_requant")
+        assert torch.equal(o, direct)
         cos = torch.nn.functional.cosine_similarity(o.float().flatten(), ref.flatten(), dim=0).item()
-        assert cos >= 0.98, (causal, cos)          # MXFP4 scores and P against exact attention
+        assert cos >= 0.95, (causal, cos)          # MXFP4 scores, P and V on unstructured N(0,1) data against exact attention
     ops.check_status()
 
 
@@ -39,5 +43,5 @@ def test_wan_shaped_block():
     assert H.set_mpsa_attn_wan(model, rope_apply=lambda t, g, f: t) == 2
     y = att(x, torch.tensor([640]), torch.tensor([[4, 10, 16]]), None)
     cos = torch.nn.functional.cosine_similarity(y.float().flatten(), ref.float().flatten(), dim=0).item()
-    assert y.shape == x.shape and cos >= 0.98, cos
+    assert y.shape == x.shape and cos >= 0.95, cos
     ops.check_status()
