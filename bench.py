@@ -44,7 +44,7 @@ LAUNCHES_PER_STEP = 6      # quant Q, quant K, quant V, band map, forward, condi
 TAU = 1.1                  # online router: a tile is promoted to MXFP8 iff its statistic >= TAU x the first key tile's
 # DRAM bytes (read + written) of one launch of the fused forward at S=8192, from an ncu capture; every term of it
 # (Q, K, V codes and scales, the output) grows linearly with S
-ATTN_TRAFFIC_BYTES_S8192 = 108_672_512
+ATTN_TRAFFIC_BYTES_S8192 = 107_451_904
 
 
 def attn_flops(B, Hq, S, Dh, causal=True):
