@@ -9,7 +9,9 @@ pytestmark = pytest.mark.gpu
 def test_attention_object_in_both_layouts():
     from mpsa import model_hooks as H, ops
     g = torch.Generator().manual_seed(5)
-    q, k, v = (torch.randn(1, 4, 384, 128, generator=g).to(torch.bfloat16).cuda() for _ in range(3))
+    q, k, v = (torch.randn(1, 4, 384, 128, generator=g) for _ in range(3))
+    v = v + 2.0                                    # values with a mean: zero-mean V under a flat softmax leaves only noise to compare
+    q, k, v = (t.to(torch.bfloat16).cuda() for t in (q, k, v))
     att = H.MixedPrecisionAttention(block_scale_type="diag_requant", smooth_k=True)
     for causal in (True, False):
         ref = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), is_causal=causal)
@@ -23,7 +25,7 @@ def test_attention_object_in_both_layouts():
         direct = mxfp_attn_kernel(q, k, v, is_causal=causal, smooth_k=True, output_dtype=q.dtype, block_scale_type="diag_requant")
         assert torch.equal(o, direct)
         cos = torch.nn.functional.cosine_similarity(o.float().flatten(), ref.flatten(), dim=0).item()
-        assert cos >= 0.95, (causal, cos)          # MXFP4 scores, P and V on unstructured N(0,1) data against exact attention
+        assert cos >= 0.98, (causal, cos)          # MXFP4 scores, P and V against exact attention
     ops.check_status()
 
 
