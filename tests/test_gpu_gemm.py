@@ -39,6 +39,8 @@ def _quant_pair(a, b, mode):
     ("mxfp8", 128, 256, 128), ("mxfp8", 128, 256, 256), ("mxfp8", 256, 512, 1024), ("mxfp8", 200, 300, 384),
     ("mxfp4", 128, 256, 256), ("mxfp4", 256, 256, 1152), ("mxfp4", 130, 100, 128),
     ("nvfp4", 128, 256, 256), ("nvfp4", 256, 384, 832),
+    # several tiles in both directions, ragged M and N, a K that ends inside a stage (MXFP4: 384 = 256 + 128)
+    ("mxfp8", 512, 1000, 256), ("mxfp4", 300, 900, 384), ("mxfp8", 257, 225, 128), ("mxfp4", 640, 1120, 1024),
 ])
 def test_gemm_matches_emulation(mode, M, N, K):
     import mpsa
