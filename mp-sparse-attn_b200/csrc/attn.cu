@@ -27,7 +27,8 @@
 // P.V; with fp16 P.V warp 1 issues both products, in order, because P then overwrites S), warp 3 router (ROUTE
 // kernels), warps 4.. softmax / correction / epilogue (a warp reaches the TMEM lane quarter warp % 4, so any four
 // consecutive warps cover the 128 rows).  Every role walks the CTA's visit list - the non-skipped cells of its map row,
-// compacted once into shared memory.  The issuing threads' loops hold nothing but their waits, the scale copies, the
+// compacted once into shared memory; in ROUTE kernels the router appends the tiles it promotes, as MXFP8 tiles, and the
+// roles walk those in a second phase once the router has been through the row.  The issuing threads' loops hold nothing but their waits, the scale copies, the
 // MMAs and the commits (measured: 64 cycles per MXFP4 MMA, ~48 per scale copy, ~44 per commit; a loop that also
 // searched the map and derived ring slots by division took ~2000 cycles per tile and bound the whole kernel).  S is
 // double-buffered in TMEM so that Q.K^T of tile t+2 overlaps the softmax of tile t.  NWG softmax
