@@ -113,7 +113,7 @@ gemm_block_scaled_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   // FP4 modes: the scale-tile copies are issued by threads of their own (see the MMA issuer); MXFP8 has one scale tile
   // per stage and row tile and keeps its three copies in the issuing thread (a hop less per stage: 2186 against 2140 TFLOP/s)
   constexpr bool SPLIT = MODE != 0;
-  constexpr int NCOP = MODE == 2 ? 4 : (MODE == 1 ? 1 : 0);   // copying threads: one per scale tile of a stage (NVFP4), one (MXFP4)
+  constexpr int NCOP = MODE == 2 ? 4 : (MODE == 1 ? 2 : 0);   // copying threads: one per scale tile of a stage
   const int KT = (p.K + K_STAGE - 1) / K_STAGE;
   const int n_row_tiles = (p.N + 127) / 128;
   const bool two_b = n_row_tiles - (int)blockIdx.y * 2 >= 2;   // the CTA's second 128-row tile of B exists
