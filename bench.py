@@ -18,7 +18,8 @@ cores, on a bounded sample of the same workload.
 
 Other workloads (their own JSON line, not the headline): `--workload ring [--layout zigzag|contiguous]
 [--exchange gather|ring]` - one causal sequence of 131072 tokens sharded over the ranks (strong scaling);
-`--workload gemm [--size 8192]` - the stand-alone block-scaled GEMM in MXFP8, MXFP4 and NVFP4;
+`--workload gemm [--size 8192]` - the stand-alone block-scaled GEMM in MXFP8, MXFP4 and NVFP4 (the default line carries
+the same figures in its `gemm` object);
 `--workload refcmp --reference-dir DIR` - the reference's own Triton kernels (imported unmodified from DIR, a
 checkout of the reference project) timed beside this library's on the same GPU and the same operands.
 """
@@ -303,6 +304,10 @@ def run_ours(args):
     }
     if seq_par is not None:
         line["seq_parallel"] = seq_par
+    # the stand-alone block-scaled GEMM (cfg2, M=N=K=8192) beside the headline: 20 launches per variant after 3 warm-up
+    # launches, outside every timed region above; fractions are of 2x (MXFP8) / 4x (FP4) the measured bf16 burst peak
+    gres, _ = gemm_variants(dev, 8192, 20, 3)
+    line["gemm"] = {"workload": "cfg2 GEMM M=N=K=8192, operands quantised along K, bf16 out", "variants": gres}
     line["cpu_baseline"] = cpu_baseline(steps=1, warmup=0, budget_s=20.0)
     print(json.dumps(line))
     if dist is not None:
@@ -496,15 +501,10 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def run_gemm(args):
-    """Standalone block-scaled GEMM C[M,N] = A[M,K] . B[N,K]^T, M = N = K = --size (default 8192), bf16 N(0,1)
-    operands from seed 1 quantised along K three ways; prints one JSON line with the three variants and the
-    library bf16 GEMM of the same shape beside them."""
+def gemm_variants(dev, n, K, W):
+    """The three block-scaled GEMM variants and the library bf16 GEMM at M = N = K = n: bf16 N(0,1) operands from seed 1
+    quantised along K, K timed launches each after max(W, 3) warm-up launches, CUDA events."""
     import mpsa
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
-    n = args.size
-    K, W = args.steps, args.warmup
     g = torch.Generator(device=dev).manual_seed(1)
     a = torch.randn(n, n, generator=g, device=dev).to(torch.bfloat16)
     b = torch.randn(n, n, generator=g, device=dev).to(torch.bfloat16)
@@ -516,13 +516,13 @@ def run_gemm(args):
     def timed(fn):
         for _ in range(max(W, 3)):
             fn()
-        torch.cuda.synchronize()
+        torch.cuda.synchronize(dev)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(K):
             fn()
         e1.record()
-        torch.cuda.synchronize()
+        torch.cuda.synchronize(dev)
         return e0.elapsed_time(e1) / K
 
     variants = {
@@ -541,6 +541,17 @@ def run_gemm(args):
     mpsa.check_status(dev)
     ms = timed(lambda: a @ b.T)
     res["library_bf16"] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1)}
+    return res, pk
+
+
+def run_gemm(args):
+    """Standalone block-scaled GEMM C[M,N] = A[M,K] . B[N,K]^T, M = N = K = --size (default 8192); prints one JSON
+    line with the three variants and the library bf16 GEMM of the same shape beside them."""
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    n = args.size
+    K, W = args.steps, args.warmup
+    res, pk = gemm_variants(dev, n, K, W)
     print(json.dumps({"metric": "block-scaled GEMM TFLOPS", "unit": "TFLOP/s", "value": res["mxfp8"]["tflops"], "n_gpus": 1,
                       "steps": K, "warmup": max(W, 3), "higher_is_better": True, "dtype": "mxfp8 / mxfp4 / nvfp4 (fp32 accumulate)",
                       "data": "synthetic", "config": {"workload": f"cfg2 GEMM M=N=K={n}, operands quantised along K, bf16 out"},
