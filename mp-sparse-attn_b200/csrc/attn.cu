@@ -482,6 +482,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
     for (int s = 0; s < 8; ++s) mbar_init(&m_bar[s], NSPLIT);
     for (int s = 0; s < 4; ++s) mbar_init(&l_bar[s], NSPLIT * NWG);
     fence_mbar_init();
+    // The Q tile does not depend on the visit list: the thread that has just initialised q_full requests it now, so
+    // that it travels while the CTA builds its list (this thread is also the loader of the K and V rings below).
+    tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_q4); tma_prefetch_desc(&tm_k8); tma_prefetch_desc(&tm_k4);
+    tma_prefetch_desc(&tm_vt); tma_prefetch_desc(&tm_vt8); tma_prefetch_desc(&tm_vt4);
+    constexpr int SF4Q = NVF4 ? 1024 : 512;           // bytes of FP4 scales per 128 rows
+    const int q_row = (b * p.Hq + h) * p.S + qi * ATT_BM;
+    const long long qsf = ((long long)(b * p.Hq + h) * nq + qi) * 512;
+    uint8_t* sSFq = smem + ATT_OFF_SF;
+    mbar_arrive_expect_tx(q_full, ATT_Q8_BYTES + ATT_Q4_BYTES + 512 + SF4Q);
+    tma_load_2d(smem + ATT_OFF_Q8, &tm_q8, q_full, 0, q_row);
+    tma_load_2d(smem + ATT_OFF_Q4, &tm_q4, q_full, 0, q_row);
+    bulk_load(sSFq, p.q8_sf + qsf, 512, q_full);
+    bulk_load(sSFq + 512, p.q4_sf + (NVF4 ? 2 * qsf : qsf), SF4Q, q_full);
   }
   if (warp == 1) tmem_alloc(tmem_slot, ATT_TMEM_COLS);
   __syncthreads();
@@ -533,19 +546,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8, const __grid_constant
   if (warp == 0) {
     // ------------------------------ Q, K and V loads ---------------------------
     if (lane == 0) {
-      tma_prefetch_desc(&tm_q8); tma_prefetch_desc(&tm_q4); tma_prefetch_desc(&tm_k8); tma_prefetch_desc(&tm_k4);
-      const int q_row = (b * p.Hq + h) * p.S + qi * ATT_BM;
-      const long long qsf = ((long long)(b * p.Hq + h) * nq + qi) * 512;
-      mbar_arrive_expect_tx(q_full, ATT_Q8_BYTES + ATT_Q4_BYTES + 512 + SF4);
-      tma_load_2d(sQ8, &tm_q8, q_full, 0, q_row);
-      tma_load_2d(sQ4, &tm_q4, q_full, 0, q_row);
-      bulk_load(sSF, p.q8_sf + qsf, 512, q_full);
-      bulk_load(sSF + 512, p.q4_sf + (NVF4 ? 2 * qsf : qsf), SF4, q_full);
-
       const int k_row0 = (b * p.Hkv + hk) * p.Skv;
       const uint8_t* k8sf = p.k8_sf + (long long)(b * p.Hkv + hk) * nk * 512;
       const uint8_t* k4sf = p.k4_sf + (long long)(b * p.Hkv + hk) * nk * SF4;
-      tma_prefetch_desc(&tm_vt); tma_prefetch_desc(&tm_vt8); tma_prefetch_desc(&tm_vt4);
       const long long vsf0 = (long long)(b * p.Hkv + hk) * p.v_tiles * 512;
       const int v_row = (b * p.Hkv + hk) * p.D;
       bool ok = true;
